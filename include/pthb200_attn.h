@@ -1,0 +1,216 @@
+/*
+ * pthb200_attn.h - C ABI of libpthb200_attn.so, the sm_100a (B200) implementation of
+ * paged int8_per_token_head attention forward.
+ *
+ * This is the drop-in boundary: a plain-C interface (pointers, sizes, byte
+ * strides; no torch types) that an engine binds through ctypes / cffi / dlsym.
+ * The two launch structs are binary-compatible with the structs the reference
+ * project passes to its own launcher, so a caller that fills the reference's
+ * structs can call this library unchanged:
+ *
+ *   PthAttnArgs / PthAttnStream / PthAttnCombineArgs
+ *       replace  csrc/pth_attn/attn_args.h:65-171  (same field order and types,
+ *       ABI version 2; ctypes mirror python/pth_testing/ref_capi.py:38-119).
+ *   pthb200_attention / pthb200_combine / pthb200_last_error
+ *       replace  launch_attention / launch_combine / last_launch_error
+ *       (csrc/pth_attn/attn_launch.h:46-52) and their C wrappers
+ *       pth_attn_attention / pth_attn_combine / pth_attn_last_error
+ *       (csrc/pth_attn/attn_capi.h:98-103).
+ *   pthb200_abi_version / *_bytes getters
+ *       replace  pth_attn_abi_version etc. (csrc/pth_attn/attn_capi.h:80-87).
+ *   pthb200_attention_ex + PthB200Options
+ *       replaces pth_attn_attention_ex + PthAttnOptions (attn_capi.h:32-39,
+ *       100-101); the option block additionally carries the final
+ *       log-sum-exp output this implementation can produce.
+ *   pthb200_check_call
+ *       replaces the host-side argument checks of the op
+ *       (csrc/pth_attn/launch.cu:315-346,380-399): tile height from (wm, G,
+ *       max_query_len) and alignment rules, without touching a device.
+ *
+ * Units: every stride is in BYTES except block_table_row_stride (int32
+ * ELEMENTS).  All pointers are device pointers.  No entry point allocates
+ * device memory, copies to the host or synchronises; a launch only enqueues
+ * kernels on `stream`, so it can be captured in a CUDA graph.
+ *
+ * Semantics (identical to the reference, attn_args.h:20-51): query token i of
+ * request r (q_len = qsl[r+1]-qsl[r], L = seq_lens[r], both read on the device)
+ * sits at KV position p = L - q_len + i and sees keys [lo, hi] with
+ *   lo = window > 0 ? max(0, p - window + 1) : 0
+ *   hi = causal ? p : (window > 0 ? min(L-1, p + window - 1) : L-1).
+ * Query head h reads KV head h / (num_q_heads / num_kv_heads).  The result is
+ * softmax(softmax_scale * q . k_scale*k) applied to v_scale*v.
+ *   num_splits == 1: out[token, head, :] is written (out_dtype).
+ *   num_splits  > 1: ws_o[s, token, head, :] (fp32, the split's own normalised
+ *       output) and ws_lse[s, token, head] (log2-sum-exp of the split's scaled
+ *       scores; -inf for a split without keys, whose ws_o must not be read)
+ *       are written for every s < num_splits; `out` is written by the combine.
+ * Rows >= qsl[num_reqs] are never written.  How the keys of a row are divided
+ * among the splits is this library's choice (any disjoint cover is valid input
+ * to the combine).
+ */
+#ifndef PTHB200_ATTN_H_
+#define PTHB200_ATTN_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PTH_ATTN_ABI_VERSION 2
+
+/* q / out element types. */
+enum { PTH_ATTN_F32 = 0, PTH_ATTN_F16 = 1, PTH_ATTN_BF16 = 2 };
+
+/* Return codes. */
+enum {
+  PTH_ATTN_OK = 0,
+  PTH_ATTN_EINVAL = -1,  /* an argument check failed; see pthb200_last_error() */
+  PTH_ATTN_ECUDA = -2,   /* a CUDA runtime call or the launch failed */
+  PTH_ATTN_ENOCUDA = -3  /* kept for code compatibility; never returned here */
+};
+
+/* A cache stream: logical [num_blocks, block_size, num_kv_heads, row], row
+ * contiguous (head_size int8 for K/V, one fp32 for a scale). */
+typedef struct PthAttnStream {
+  const void* data;
+  int64_t stride_block;
+  int64_t stride_slot;
+  int64_t stride_head;
+} PthAttnStream;
+
+typedef struct PthAttnArgs {
+  int32_t abi_version;  /* PTH_ATTN_ABI_VERSION */
+  int32_t struct_bytes; /* sizeof(PthAttnArgs) of the caller */
+
+  const void* q; /* [num_tokens, num_q_heads, head_size] */
+  int32_t q_dtype;
+  int64_t q_stride_token;
+  int64_t q_stride_head;
+
+  void* out; /* [num_tokens, num_q_heads, head_size]; num_splits == 1 */
+  int32_t out_dtype;
+  int64_t out_stride_token;
+  int64_t out_stride_head;
+
+  PthAttnStream k_cache;
+  PthAttnStream v_cache;
+  PthAttnStream k_scale;
+  PthAttnStream v_scale;
+  int32_t num_blocks;
+  int32_t block_size;
+  int32_t num_kv_heads;
+  int32_t head_size; /* 64, 128 or 256 */
+
+  const int32_t* block_table; /* [>= num_reqs, *] physical block ids */
+  int64_t block_table_row_stride;
+  const int32_t* seq_lens;        /* [num_reqs] */
+  const int32_t* query_start_loc; /* [num_reqs + 1] */
+
+  int32_t num_reqs;
+  int32_t num_tokens;
+  int32_t num_q_heads;
+  int32_t bq;          /* query tokens per row tile, >= 1 */
+  int32_t num_q_tiles; /* 0 = num_tokens / bq + num_reqs */
+  int32_t num_splits;
+  float softmax_scale;
+
+  float* ws_o; /* [>= num_splits, >= num_tokens, num_q_heads, head_size] */
+  int64_t ws_o_stride_split;
+  int64_t ws_o_stride_token;
+  int64_t ws_o_stride_head;
+  float* ws_lse; /* [>= num_splits, >= num_tokens, num_q_heads] */
+  int64_t ws_lse_stride_split;
+  int64_t ws_lse_stride_token;
+  int64_t ws_lse_stride_head;
+
+  int32_t window; /* 0 = none */
+  int32_t causal; /* 1 = bottom-right causal, 0 = non-causal */
+} PthAttnArgs;
+
+typedef struct PthAttnCombineArgs {
+  int32_t abi_version;
+  int32_t struct_bytes;
+
+  const float* ws_o;
+  int64_t ws_o_stride_split;
+  int64_t ws_o_stride_token;
+  int64_t ws_o_stride_head;
+  const float* ws_lse;
+  int64_t ws_lse_stride_split;
+  int64_t ws_lse_stride_token;
+  int64_t ws_lse_stride_head;
+
+  void* out;
+  int32_t out_dtype;
+  int64_t out_stride_token;
+  int64_t out_stride_head;
+
+  const int32_t* query_start_loc;
+  int32_t num_reqs;
+  int32_t num_tokens;
+  int32_t num_q_heads;
+  int32_t head_size;
+  int32_t num_splits;
+} PthAttnCombineArgs;
+
+/* Kernel family of pthb200_attention_ex. */
+enum {
+  PTHB200_KERNEL_AUTO = 0,   /* the shipped choice */
+  PTHB200_KERNEL_SCALAR = 1, /* CUDA-core kernel: every head size, layout, dtype */
+  PTHB200_KERNEL_UMMA = 2    /* tcgen05 kernel; EINVAL where it does not apply */
+};
+
+/* Options of the _ex entry points.  Zero-initialise, then set abi_version and
+ * struct_bytes.  lse_out (optional) receives the natural-log log-sum-exp of the
+ * scaled scores per (token, head), -inf for a row without keys: from the
+ * attention launch when num_splits == 1, from the combine otherwise. */
+typedef struct PthB200Options {
+  int32_t abi_version;
+  int32_t struct_bytes;
+  int32_t kernel;
+  int32_t reserved;
+  float* lse_out; /* [num_tokens, num_q_heads] fp32 or NULL */
+  int64_t lse_stride_token;
+  int64_t lse_stride_head;
+} PthB200Options;
+
+/* Library identity for binding layers. */
+int32_t pthb200_abi_version(void);
+int32_t pthb200_attn_args_bytes(void);
+int32_t pthb200_combine_args_bytes(void);
+int32_t pthb200_options_bytes(void);
+int32_t pthb200_has_cuda(void); /* always 1 */
+/* Message of the calling thread's last failed call ("" after a success). */
+const char* pthb200_last_error(void);
+
+/* Enqueue the attention kernel(s) on `stream` (a cudaStream_t). */
+int32_t pthb200_attention(const PthAttnArgs* args, void* stream);
+int32_t pthb200_attention_ex(const PthAttnArgs* args, const PthB200Options* options,
+                             void* stream);
+/* Enqueue the split combine on `stream`. */
+int32_t pthb200_combine(const PthAttnCombineArgs* args, void* stream);
+int32_t pthb200_combine_ex(const PthAttnCombineArgs* args, const PthB200Options* options,
+                           void* stream);
+
+/* Host-only helpers of the op layer (no device access).
+ * pthb200_tile_tokens: query tokens per row tile for a launch planned with `wm`
+ * (1, 2 or 4), group size G and host bound max_query_len; returns -1 if wm is
+ * not the tile height those rows need (the op's "wm is not the tile height"
+ * refusal). */
+int32_t pthb200_tile_tokens(int32_t wm, int32_t group, int32_t max_query_len);
+/* Validates a filled PthAttnArgs exactly as pthb200_attention would, without
+ * launching.  Returns PTH_ATTN_OK or PTH_ATTN_EINVAL (+ last error). */
+int32_t pthb200_check_call(const PthAttnArgs* args);
+
+/* Work a launch will enqueue, for callers that account for launches:
+ * *attention_kernels and *combine_kernels receive the number of kernels
+ * pthb200_attention + pthb200_combine enqueue for these arguments. */
+int32_t pthb200_launch_count(const PthAttnArgs* args, int32_t* attention_kernels,
+                             int32_t* combine_kernels);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* PTHB200_ATTN_H_ */
