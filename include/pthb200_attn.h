@@ -209,6 +209,20 @@ int32_t pthb200_check_call(const PthAttnArgs* args);
 int32_t pthb200_launch_count(const PthAttnArgs* args, int32_t* attention_kernels,
                              int32_t* combine_kernels);
 
+/* ---- test hooks (counterparts of the reference's fragment unit tests,
+ * csrc/pth_attn/attn_capi.h:41-78,102-105) ---------------------------------- */
+
+/* One CTA runs the tensor-core building blocks on one 128-key tile:
+ *   s_out[key][n] = sum_d k[key][d] * q[n][d]      (fp32 [128][16])
+ *   o_out[d][n]   = sum_key v[key][d] * pm[key][n] (fp32 [128][16])
+ * k, v: int8 [128][128]; q: bf16 [16][128]; pm: bf16 [128][16]; all dense on the
+ * device.  padded != 0 uses the operand image of the attention kernel. */
+int32_t pthb200_test_tile(const void* k, const void* q, const void* v, const void* pm,
+                          float* s_out, float* o_out, int32_t padded, void* stream);
+/* Synchronises the device, returns and clears the status word in which a
+ * kernel records a bounded wait that gave up (0 = none). */
+int32_t pthb200_device_status(int32_t* status);
+
 #ifdef __cplusplus
 }
 #endif

@@ -127,6 +127,8 @@ EXPORTED_SYMBOLS = (
     "pthb200_tile_tokens",
     "pthb200_check_call",
     "pthb200_launch_count",
+    "pthb200_test_tile",
+    "pthb200_device_status",
 )
 
 
@@ -170,6 +172,10 @@ class B200Lib:
         lib.pthb200_launch_count.restype = ctypes.c_int32
         lib.pthb200_launch_count.argtypes = [ap, ctypes.POINTER(ctypes.c_int32),
                                              ctypes.POINTER(ctypes.c_int32)]
+        lib.pthb200_test_tile.restype = ctypes.c_int32
+        lib.pthb200_test_tile.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int32, ctypes.c_void_p]
+        lib.pthb200_device_status.restype = ctypes.c_int32
+        lib.pthb200_device_status.argtypes = [ctypes.POINTER(ctypes.c_int32)]
         if lib.pthb200_abi_version() != ABI_VERSION:
             raise RuntimeError(f"{path}: ABI {lib.pthb200_abi_version()} != mirror {ABI_VERSION}")
         if lib.pthb200_attn_args_bytes() != ctypes.sizeof(PthAttnArgs):
@@ -204,6 +210,13 @@ class B200Lib:
 
     def check_call(self, args: PthAttnArgs) -> int:
         return int(self.lib.pthb200_check_call(ctypes.byref(args)))
+
+    def device_status(self) -> int:
+        v = ctypes.c_int32(0)
+        rc = self.lib.pthb200_device_status(ctypes.byref(v))
+        if rc != OK:
+            raise RuntimeError("pthb200_device_status failed")
+        return v.value
 
     def launch_count(self, args: PthAttnArgs) -> tuple[int, int]:
         a, c = ctypes.c_int32(0), ctypes.c_int32(0)

@@ -1,0 +1,308 @@
+// Host launcher and C ABI of libpthb200_attn.so (include/pthb200_attn.h).
+//
+// Every entry point validates its arguments (each failure names the field),
+// converts the caller's struct into kernel parameters, chooses the kernel
+// family and enqueues on the caller's stream.  Nothing here allocates device
+// memory, reads device memory or synchronises.
+#include <cmath>
+#include <cstdio>
+#include <string>
+
+#include "params.cuh"
+
+namespace pthb200 {
+namespace {
+
+thread_local std::string g_last_error;
+
+int32_t fail(int32_t code, const std::string& msg) {
+  g_last_error = msg;
+  return code;
+}
+
+#define PTHB_REQUIRE(cond, msg)                      \
+  do {                                               \
+    if (!(cond)) return fail(PTH_ATTN_EINVAL, (msg)); \
+  } while (0)
+
+bool aligned(const void* ptr, int64_t a) { return reinterpret_cast<uintptr_t>(ptr) % (uintptr_t)a == 0; }
+
+bool is_head_size(int32_t d) { return d == 64 || d == 128 || d == 256; }
+
+int32_t check_stream(const PthAttnStream& s, const char* name) {
+  PTHB_REQUIRE(s.data != nullptr, std::string(name) + ".data is NULL");
+  PTHB_REQUIRE(aligned(s.data, 4), std::string(name) + ".data must be 4-byte aligned");
+  PTHB_REQUIRE(s.stride_block >= 0 && s.stride_slot >= 0 && s.stride_head >= 0,
+               std::string(name) + " strides must be >= 0");
+  PTHB_REQUIRE(s.stride_block % 4 == 0 && s.stride_slot % 4 == 0 && s.stride_head % 4 == 0,
+               std::string(name) + " byte strides must be multiples of 4");
+  return PTH_ATTN_OK;
+}
+
+StreamParams to_stream(const PthAttnStream& s) {
+  return StreamParams{static_cast<const uint8_t*>(s.data), s.stride_block, s.stride_slot, s.stride_head};
+}
+
+int32_t check_options(const PthB200Options* o) {
+  if (o == nullptr) return PTH_ATTN_OK;
+  PTHB_REQUIRE(o->abi_version == PTH_ATTN_ABI_VERSION, "options.abi_version does not match the library");
+  PTHB_REQUIRE(o->struct_bytes == (int32_t)sizeof(PthB200Options), "options.struct_bytes != sizeof(PthB200Options)");
+  PTHB_REQUIRE(o->kernel >= PTHB200_KERNEL_AUTO && o->kernel <= PTHB200_KERNEL_UMMA, "options.kernel is not a kernel family");
+  if (o->lse_out != nullptr) {
+    PTHB_REQUIRE(aligned(o->lse_out, 4), "options.lse_out must be 4-byte aligned");
+    PTHB_REQUIRE(o->lse_stride_token % 4 == 0 && o->lse_stride_head % 4 == 0 && o->lse_stride_token >= 0 &&
+                     o->lse_stride_head >= 0,
+                 "options.lse strides must be non-negative multiples of 4");
+  }
+  return PTH_ATTN_OK;
+}
+
+// Argument checks of an attention launch; fills *kp on success.
+int32_t build_attention(const PthAttnArgs* a, const PthB200Options* opt, KernelParams* kp) {
+  PTHB_REQUIRE(a != nullptr, "args is NULL");
+  PTHB_REQUIRE(a->abi_version == PTH_ATTN_ABI_VERSION, "args.abi_version does not match the library");
+  PTHB_REQUIRE(a->struct_bytes == (int32_t)sizeof(PthAttnArgs), "args.struct_bytes != sizeof(PthAttnArgs)");
+  if (int32_t rc = check_options(opt)) return rc;
+
+  PTHB_REQUIRE(is_head_size(a->head_size), "head_size must be 64, 128 or 256");
+  PTHB_REQUIRE(a->num_kv_heads >= 1 && a->num_q_heads >= 1 && a->num_q_heads % a->num_kv_heads == 0,
+               "num_q_heads must be a positive multiple of num_kv_heads");
+  const int32_t group = a->num_q_heads / a->num_kv_heads;
+  PTHB_REQUIRE(group <= 64, "num_q_heads / num_kv_heads must be <= 64");
+  PTHB_REQUIRE(a->num_reqs >= 1, "num_reqs must be >= 1");
+  PTHB_REQUIRE(a->num_tokens >= 1, "num_tokens must be >= 1");
+  PTHB_REQUIRE(a->bq >= 1, "bq must be >= 1");
+  PTHB_REQUIRE(a->num_q_tiles >= 0, "num_q_tiles must be >= 0");
+  PTHB_REQUIRE(a->num_splits >= 1 && a->num_splits <= 65535, "num_splits must be in [1, 65535]");
+  PTHB_REQUIRE(a->num_kv_heads <= 65535, "num_kv_heads must be <= 65535");
+  PTHB_REQUIRE(a->block_size >= 1, "block_size must be >= 1");
+  PTHB_REQUIRE(a->num_blocks >= 1, "num_blocks must be >= 1");
+  PTHB_REQUIRE(std::isfinite(a->softmax_scale) && a->softmax_scale > 0.f, "softmax_scale must be finite and > 0");
+  PTHB_REQUIRE(a->window >= 0, "window must be >= 0");
+  PTHB_REQUIRE(a->causal == 0 || a->causal == 1, "causal must be 0 or 1");
+  PTHB_REQUIRE(a->q_dtype == PTH_ATTN_F16 || a->q_dtype == PTH_ATTN_BF16, "q_dtype must be F16 or BF16");
+
+  PTHB_REQUIRE(a->q != nullptr, "q is NULL");
+  PTHB_REQUIRE(aligned(a->q, 16), "q must be 16-byte aligned");
+  PTHB_REQUIRE(a->q_stride_token % 16 == 0 && a->q_stride_head % 16 == 0 && a->q_stride_token >= 0 &&
+                   a->q_stride_head >= 0,
+               "q byte strides must be non-negative multiples of 16");
+  if (int32_t rc = check_stream(a->k_cache, "k_cache")) return rc;
+  if (int32_t rc = check_stream(a->v_cache, "v_cache")) return rc;
+  if (int32_t rc = check_stream(a->k_scale, "k_scale")) return rc;
+  if (int32_t rc = check_stream(a->v_scale, "v_scale")) return rc;
+  PTHB_REQUIRE(a->block_table != nullptr && a->seq_lens != nullptr && a->query_start_loc != nullptr,
+               "block_table, seq_lens and query_start_loc must not be NULL");
+  PTHB_REQUIRE(a->block_table_row_stride >= 0, "block_table_row_stride must be >= 0");
+
+  if (a->num_splits == 1) {
+    PTHB_REQUIRE(a->out != nullptr, "out is NULL (num_splits == 1 writes out)");
+    PTHB_REQUIRE(a->out_dtype == PTH_ATTN_F32 || a->out_dtype == PTH_ATTN_F16 || a->out_dtype == PTH_ATTN_BF16,
+                 "out_dtype must be F32, F16 or BF16");
+    PTHB_REQUIRE(aligned(a->out, 16), "out must be 16-byte aligned");
+    PTHB_REQUIRE(a->out_stride_token % 16 == 0 && a->out_stride_head % 16 == 0 && a->out_stride_token >= 0 &&
+                     a->out_stride_head >= 0,
+                 "out byte strides must be non-negative multiples of 16");
+  } else {
+    PTHB_REQUIRE(a->ws_o != nullptr && a->ws_lse != nullptr, "ws_o and ws_lse must not be NULL when num_splits > 1");
+    PTHB_REQUIRE(aligned(a->ws_o, 16), "ws_o must be 16-byte aligned");
+    PTHB_REQUIRE(a->ws_o_stride_split % 16 == 0 && a->ws_o_stride_token % 16 == 0 && a->ws_o_stride_head % 16 == 0 &&
+                     a->ws_o_stride_split >= 0 && a->ws_o_stride_token >= 0 && a->ws_o_stride_head >= 0,
+                 "ws_o byte strides must be non-negative multiples of 16");
+    PTHB_REQUIRE(aligned(a->ws_lse, 4), "ws_lse must be 4-byte aligned");
+    PTHB_REQUIRE(a->ws_lse_stride_split % 4 == 0 && a->ws_lse_stride_token % 4 == 0 && a->ws_lse_stride_head % 4 == 0 &&
+                     a->ws_lse_stride_split >= 0 && a->ws_lse_stride_token >= 0 && a->ws_lse_stride_head >= 0,
+                 "ws_lse byte strides must be non-negative multiples of 4");
+  }
+
+  KernelParams& p = *kp;
+  p = KernelParams{};
+  p.q = static_cast<const uint8_t*>(a->q);
+  p.q_stride_token = a->q_stride_token;
+  p.q_stride_head = a->q_stride_head;
+  p.out = static_cast<uint8_t*>(a->out);
+  p.out_stride_token = a->out_stride_token;
+  p.out_stride_head = a->out_stride_head;
+  p.k = to_stream(a->k_cache);
+  p.v = to_stream(a->v_cache);
+  p.ks = to_stream(a->k_scale);
+  p.vs = to_stream(a->v_scale);
+  p.block_table = a->block_table;
+  p.block_table_row_stride = a->block_table_row_stride;
+  p.seq_lens = a->seq_lens;
+  p.query_start_loc = a->query_start_loc;
+  p.ws_o = a->ws_o;
+  p.ws_o_stride_split = a->ws_o_stride_split;
+  p.ws_o_stride_token = a->ws_o_stride_token;
+  p.ws_o_stride_head = a->ws_o_stride_head;
+  p.ws_lse = a->ws_lse;
+  p.ws_lse_stride_split = a->ws_lse_stride_split;
+  p.ws_lse_stride_token = a->ws_lse_stride_token;
+  p.ws_lse_stride_head = a->ws_lse_stride_head;
+  if (opt != nullptr && opt->lse_out != nullptr && a->num_splits == 1) {
+    p.lse_out = opt->lse_out;
+    p.lse_stride_token = opt->lse_stride_token;
+    p.lse_stride_head = opt->lse_stride_head;
+  }
+  p.q_dtype = a->q_dtype;
+  p.out_dtype = a->out_dtype;
+  p.block_size = a->block_size;
+  p.block_shift = -1;
+  for (int sh = 0; sh < 31; ++sh)
+    if ((1 << sh) == a->block_size) p.block_shift = sh;
+  p.num_kv_heads = a->num_kv_heads;
+  p.head_size = a->head_size;
+  p.num_reqs = a->num_reqs;
+  p.num_tokens = a->num_tokens;
+  p.num_q_heads = a->num_q_heads;
+  p.group = group;
+  p.bq = a->bq;
+  p.num_q_tiles = a->num_tokens / a->bq + a->num_reqs;
+  p.num_splits = a->num_splits;
+  p.window = a->window;
+  p.causal = a->causal;
+  p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
+  return PTH_ATTN_OK;
+}
+
+// Kernel family for these parameters: 1 = scalar, 2 = tcgen05.
+int32_t choose_family(const KernelParams& p, const PthB200Options* opt, int32_t* family) {
+  const int32_t want = opt ? opt->kernel : PTHB200_KERNEL_AUTO;
+  const char* why = "";
+  const bool umma_ok = umma_supports(p, &why);
+  if (want == PTHB200_KERNEL_UMMA) {
+    PTHB_REQUIRE(umma_ok, std::string("options.kernel = UMMA does not apply: ") + why);
+    *family = PTHB200_KERNEL_UMMA;
+  } else if (want == PTHB200_KERNEL_SCALAR) {
+    *family = PTHB200_KERNEL_SCALAR;
+  } else {
+    *family = umma_ok ? PTHB200_KERNEL_UMMA : PTHB200_KERNEL_SCALAR;
+  }
+  return PTH_ATTN_OK;
+}
+
+int32_t attention_impl(const PthAttnArgs* a, const PthB200Options* opt, void* stream, bool launch) {
+  g_last_error.clear();
+  KernelParams p;
+  if (int32_t rc = build_attention(a, opt, &p)) return rc;
+  int32_t family = 0;
+  if (int32_t rc = choose_family(p, opt, &family)) return rc;
+  if (!launch) return PTH_ATTN_OK;
+  cudaError_t err;
+  if (family == PTHB200_KERNEL_UMMA) {
+    err = launch_umma_attention(p, static_cast<cudaStream_t>(stream));
+  } else {
+    PTHB_REQUIRE((int64_t)p.num_q_tiles <= 0x7fffffff, "too many row tiles");
+    err = launch_scalar_attention(p, static_cast<cudaStream_t>(stream));
+  }
+  if (err != cudaSuccess) return fail(PTH_ATTN_ECUDA, std::string("attention launch failed: ") + cudaGetErrorString(err));
+  return PTH_ATTN_OK;
+}
+
+int32_t combine_impl(const PthAttnCombineArgs* a, const PthB200Options* opt, void* stream) {
+  g_last_error.clear();
+  PTHB_REQUIRE(a != nullptr, "args is NULL");
+  PTHB_REQUIRE(a->abi_version == PTH_ATTN_ABI_VERSION, "args.abi_version does not match the library");
+  PTHB_REQUIRE(a->struct_bytes == (int32_t)sizeof(PthAttnCombineArgs), "args.struct_bytes != sizeof(PthAttnCombineArgs)");
+  if (int32_t rc = check_options(opt)) return rc;
+  PTHB_REQUIRE(is_head_size(a->head_size), "head_size must be 64, 128 or 256");
+  PTHB_REQUIRE(a->num_reqs >= 1 && a->num_tokens >= 1 && a->num_q_heads >= 1, "num_reqs, num_tokens and num_q_heads must be >= 1");
+  PTHB_REQUIRE(a->num_splits >= 1, "num_splits must be >= 1");
+  PTHB_REQUIRE(a->ws_o != nullptr && a->ws_lse != nullptr && a->out != nullptr && a->query_start_loc != nullptr,
+               "ws_o, ws_lse, out and query_start_loc must not be NULL");
+  PTHB_REQUIRE(a->out_dtype == PTH_ATTN_F32 || a->out_dtype == PTH_ATTN_F16 || a->out_dtype == PTH_ATTN_BF16,
+               "out_dtype must be F32, F16 or BF16");
+  PTHB_REQUIRE(aligned(a->ws_o, 16) && aligned(a->out, 16), "ws_o and out must be 16-byte aligned");
+  PTHB_REQUIRE(a->ws_o_stride_split % 16 == 0 && a->ws_o_stride_token % 16 == 0 && a->ws_o_stride_head % 16 == 0,
+               "ws_o byte strides must be multiples of 16");
+  PTHB_REQUIRE(a->out_stride_token % 16 == 0 && a->out_stride_head % 16 == 0, "out byte strides must be multiples of 16");
+  PTHB_REQUIRE(aligned(a->ws_lse, 4) && a->ws_lse_stride_split % 4 == 0 && a->ws_lse_stride_token % 4 == 0 &&
+                   a->ws_lse_stride_head % 4 == 0,
+               "ws_lse must be 4-byte aligned with strides that are multiples of 4");
+  PTHB_REQUIRE(a->ws_o_stride_split >= 0 && a->ws_o_stride_token >= 0 && a->ws_o_stride_head >= 0 &&
+                   a->ws_lse_stride_split >= 0 && a->ws_lse_stride_token >= 0 && a->ws_lse_stride_head >= 0 &&
+                   a->out_stride_token >= 0 && a->out_stride_head >= 0,
+               "strides must be >= 0");
+  CombineParams c{};
+  c.ws_o = a->ws_o;
+  c.ws_o_stride_split = a->ws_o_stride_split;
+  c.ws_o_stride_token = a->ws_o_stride_token;
+  c.ws_o_stride_head = a->ws_o_stride_head;
+  c.ws_lse = a->ws_lse;
+  c.ws_lse_stride_split = a->ws_lse_stride_split;
+  c.ws_lse_stride_token = a->ws_lse_stride_token;
+  c.ws_lse_stride_head = a->ws_lse_stride_head;
+  c.out = static_cast<uint8_t*>(a->out);
+  c.out_stride_token = a->out_stride_token;
+  c.out_stride_head = a->out_stride_head;
+  if (opt != nullptr && opt->lse_out != nullptr) {
+    c.lse_out = opt->lse_out;
+    c.lse_stride_token = opt->lse_stride_token;
+    c.lse_stride_head = opt->lse_stride_head;
+  }
+  c.query_start_loc = a->query_start_loc;
+  c.out_dtype = a->out_dtype;
+  c.num_reqs = a->num_reqs;
+  c.num_tokens = a->num_tokens;
+  c.num_q_heads = a->num_q_heads;
+  c.head_size = a->head_size;
+  c.num_splits = a->num_splits;
+  const cudaError_t err = launch_combine_kernel(c, static_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) return fail(PTH_ATTN_ECUDA, std::string("combine launch failed: ") + cudaGetErrorString(err));
+  return PTH_ATTN_OK;
+}
+
+int32_t wm_for_rows(int32_t rows) {
+  int32_t wm = 1;
+  while (wm < 4 && rows > 16 * wm) wm *= 2;
+  return wm;
+}
+
+}  // namespace
+}  // namespace pthb200
+
+extern "C" {
+
+int32_t pthb200_abi_version(void) { return PTH_ATTN_ABI_VERSION; }
+int32_t pthb200_attn_args_bytes(void) { return (int32_t)sizeof(PthAttnArgs); }
+int32_t pthb200_combine_args_bytes(void) { return (int32_t)sizeof(PthAttnCombineArgs); }
+int32_t pthb200_options_bytes(void) { return (int32_t)sizeof(PthB200Options); }
+int32_t pthb200_has_cuda(void) { return 1; }
+const char* pthb200_last_error(void) { return pthb200::g_last_error.c_str(); }
+
+int32_t pthb200_attention(const PthAttnArgs* args, void* stream) {
+  return pthb200::attention_impl(args, nullptr, stream, true);
+}
+int32_t pthb200_attention_ex(const PthAttnArgs* args, const PthB200Options* options, void* stream) {
+  return pthb200::attention_impl(args, options, stream, true);
+}
+int32_t pthb200_combine(const PthAttnCombineArgs* args, void* stream) {
+  return pthb200::combine_impl(args, nullptr, stream);
+}
+int32_t pthb200_combine_ex(const PthAttnCombineArgs* args, const PthB200Options* options, void* stream) {
+  return pthb200::combine_impl(args, options, stream);
+}
+
+// Rows of a tile planned with `wm`: 16 * wm.  The tile holds floor(16 wm / G)
+// tokens, or max_query_len tokens when that is fewer and still needs this wm.
+int32_t pthb200_tile_tokens(int32_t wm, int32_t group, int32_t max_query_len) {
+  if (!(wm == 1 || wm == 2 || wm == 4) || group < 1 || group > 16 * wm) return -1;
+  const int32_t capacity = 16 * wm / group;
+  int32_t bq = capacity;
+  if (max_query_len >= 1 && max_query_len < capacity && pthb200::wm_for_rows(max_query_len * group) == wm) {
+    bq = max_query_len;
+  }
+  return pthb200::wm_for_rows(bq * group) == wm ? bq : -1;
+}
+
+int32_t pthb200_check_call(const PthAttnArgs* args) { return pthb200::attention_impl(args, nullptr, nullptr, false); }
+
+int32_t pthb200_launch_count(const PthAttnArgs* args, int32_t* attention_kernels, int32_t* combine_kernels) {
+  const int32_t rc = pthb200::attention_impl(args, nullptr, nullptr, false);
+  if (rc != PTH_ATTN_OK) return rc;
+  if (attention_kernels) *attention_kernels = 1;
+  if (combine_kernels) *combine_kernels = args->num_splits > 1 ? 1 : 0;
+  return PTH_ATTN_OK;
+}
+
+}  // extern "C"

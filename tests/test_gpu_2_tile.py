@@ -1,0 +1,36 @@
+"""Unit test of the tcgen05 building blocks: widening, operand images, both MMA chains."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import paged_int8_attention as orc
+from pth_flash_attn_b200 import capi
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("padded", [1, 0])
+def test_umma_tile(padded):
+    lib = capi.load_library()
+    rng = np.random.default_rng(3)
+    k = rng.integers(-128, 128, size=(128, 128), dtype=np.int8)
+    v = rng.integers(-128, 128, size=(128, 128), dtype=np.int8)
+    k[0, :4] = [-128, 127, 0, -1]
+    q = orc.round_to_bf16(rng.standard_normal((16, 128), dtype=np.float32))
+    pm = orc.round_to_bf16(rng.random((128, 16), dtype=np.float32))
+    dev = "cuda"
+    kt, vt = torch.from_numpy(k).to(dev), torch.from_numpy(v).to(dev)
+    qt = torch.from_numpy(q).to(dev).to(torch.bfloat16)
+    pt = torch.from_numpy(pm).to(dev).to(torch.bfloat16)
+    s_out = torch.full((128, 16), float("nan"), dtype=torch.float32, device=dev)
+    o_out = torch.full((128, 16), float("nan"), dtype=torch.float32, device=dev)
+    rc = lib.lib.pthb200_test_tile(kt.data_ptr(), qt.data_ptr(), vt.data_ptr(), pt.data_ptr(),
+                                   s_out.data_ptr(), o_out.data_ptr(), padded, None)
+    assert rc == capi.OK
+    assert lib.device_status() == 0, "a bounded wait gave up"
+    s_want = k.astype(np.float64) @ q.astype(np.float64).T          # [key][n]
+    o_want = v.astype(np.float64).T @ pm.astype(np.float64)         # [d][n]
+    s_got, o_got = s_out.cpu().numpy(), o_out.cpu().numpy()
+    # products are exact in fp32; only the accumulation order differs
+    np.testing.assert_allclose(s_got, s_want, rtol=1e-5, atol=1e-2)
+    np.testing.assert_allclose(o_got, o_want, rtol=1e-5, atol=1e-2)

@@ -1,0 +1,87 @@
+"""GPU parity of the tcgen05 kernel family (head size 128, bf16 queries)."""
+import numpy as np
+import pytest
+
+from oracle import paged_int8_attention as orc
+from pth_flash_attn_b200 import capi
+from tests.helpers import check_lse, check_out, load_golden
+from tests.test_gpu_1_scalar import cache_from_golden
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN_D128 = ["attn_decode", "attn_verify4", "attn_window_causal", "attn_window_noncausal",
+               "attn_noncausal", "attn_mixed"]
+
+
+@pytest.mark.parametrize("name", GOLDEN_D128)
+def test_golden_attention_umma(name):
+    from tests.gpu_util import run_case
+
+    g = load_golden(name)
+    Hq, Hkv, D, window, causal = (int(v) for v in g["meta"])
+    G = Hq // Hkv
+    q = orc.f32_from_bf16_bits(g["q_bits"])
+    c = cache_from_golden(g)
+    bq = max(1, min(64 // G, int(np.diff(g["qsl"]).max())))
+    res = run_case(c, q, g["qsl"], float(g["softmax_scale"]), bq=bq, window=window,
+                   causal=bool(causal), kernel=capi.KERNEL_UMMA)
+    assert capi.load_library().device_status() == 0
+    valid = g["valid"]
+    check_out(res["out"], g["out"], valid, what=name)
+    assert res["tail_intact"]
+    assert (res["out_bytes"][~valid] == 0xFF).all(), "rows of no request were written"
+    check_lse(np.where(valid[:, None], res["lse"], -np.inf), g["lse"], what=name)
+
+
+def _seeded(lens, qlens, Hq, Hkv, seed, **kw):
+    c = orc.make_paged_cache(lens, Hkv, 128, 16, seed=seed, **kw)
+    rng = np.random.default_rng(seed + 1)
+    T = sum(qlens)
+    q = orc.round_to_bf16(rng.standard_normal((T, Hq, 128), dtype=np.float32))
+    qsl = np.concatenate([[0], np.cumsum(qlens)]).astype(np.int64)
+    return c, q, qsl
+
+
+@pytest.mark.parametrize("S", [1, 2, 5])
+@pytest.mark.parametrize("qlen,G,bq", [(1, 4, 1), (4, 4, 4), (16, 4, 16), (4, 8, 4), (40, 8, 8)])
+def test_seeded_shapes(S, qlen, G, bq):
+    """Decode, verify, drafter and a short prefill chunk, with and without split-KV."""
+    from tests.gpu_util import run_case
+
+    lens = [1000, 257, 128, qlen + 2]
+    qlens = [qlen] * 4
+    c, q, qsl = _seeded(lens, qlens, 2 * G, 2, seed=50 + qlen + G)
+    scale = 128 ** -0.5
+    ref = orc.ref_attention_paged(q, c, qsl, scale)
+    res = run_case(c, q, qsl, scale, bq=bq, num_splits=S, kernel=capi.KERNEL_UMMA)
+    assert capi.load_library().device_status() == 0
+    check_out(res["out"], ref.out, what=f"S{S} q{qlen} G{G}")
+    check_lse(res["lse"], ref.lse, what=f"S{S} q{qlen} G{G}")
+    if S > 1:
+        o, l2 = orc.combine_partials(res["ws_o"], res["ws_lse"])
+        check_out(o, ref.out, max_tol=1e-2, mean_tol=1e-3, what="partials")
+
+
+def test_matches_scalar_kernel_on_device():
+    """The two kernel families agree on a case too large for a comfortable CPU oracle."""
+    from tests.gpu_util import run_case
+
+    lens = [20000, 4097, 33]
+    c, q, qsl = _seeded(lens, [4, 4, 4], 32, 8, seed=77)
+    scale = 128 ** -0.5
+    a = run_case(c, q, qsl, scale, bq=4, num_splits=3, kernel=capi.KERNEL_UMMA)
+    b = run_case(c, q, qsl, scale, bq=4, num_splits=1, kernel=capi.KERNEL_SCALAR, out_dtype=__import__("torch").float32)
+    check_out(a["out"], b["out"], what="umma vs scalar")
+    check_lse(a["lse"], b["lse"], what="umma vs scalar")
+
+
+def test_window_drafter_long():
+    from tests.gpu_util import run_case
+
+    lens = [9000, 5000]
+    c, q, qsl = _seeded(lens, [16, 16], 8, 2, seed=91)
+    scale = 128 ** -0.5
+    ref = orc.ref_attention_paged(q, c, qsl, scale, window=4096)
+    res = run_case(c, q, qsl, scale, bq=16, num_splits=4, window=4096, kernel=capi.KERNEL_UMMA)
+    check_out(res["out"], ref.out, what="window 4096")
+    check_lse(res["lse"], ref.lse, what="window 4096")
