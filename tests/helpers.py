@@ -27,7 +27,10 @@ def golden_dense(g: dict) -> list[orc.DenseKV]:
             for r in range(n)]
 
 
-def check_out(out, ref_out, valid=None, *, max_tol=OUT_MAX_TOL, mean_tol=OUT_MEAN_TOL, what=""):
+def check_out(out, ref_out, valid=None, *, max_tol=OUT_MAX_TOL, mean_tol=OUT_MEAN_TOL, what="",
+              relative=False):
+    """The parity gate.  ``relative`` divides each error by max(1, |ref|): the gate is stated for
+    unit-scale data, and a bf16 output at magnitude 16 rounds by up to 0.06 on its own."""
     out = np.asarray(out, dtype=np.float64)
     ref_out = np.asarray(ref_out, dtype=np.float64)
     if valid is not None:
@@ -35,6 +38,8 @@ def check_out(out, ref_out, valid=None, *, max_tol=OUT_MAX_TOL, mean_tol=OUT_MEA
     if out.size == 0:
         return 0.0, 0.0
     d = np.abs(out - ref_out)
+    if relative:
+        d = d / np.maximum(1.0, np.abs(ref_out))
     assert np.isfinite(out).all(), f"{what}: non-finite output"
     mx, mean = float(d.max()), float(d.mean())
     assert mx <= max_tol, f"{what}: max |d| {mx:.3e} > {max_tol}"

@@ -51,7 +51,8 @@ def test_golden_attention(name, kernel):
     res = run_case(c, q, g["qsl"], float(g["softmax_scale"]), bq=bq, window=window,
                    causal=bool(causal), kernel=kernel)
     valid = g["valid"]
-    check_out(res["out"], g["out"], valid, what=name)
+    # the d64/d256 fixtures use the reference's wide-range data (|v| up to ~18)
+    check_out(res["out"], g["out"], valid, what=name, relative=name in ("attn_d64_g6", "attn_d256_g6"))
     # rows of an empty request / padding rows keep the canary; rows of requests are written
     assert res["tail_intact"]
     assert (res["out_bytes"][~valid] == 0xFF).all(), "rows of no request were written"
