@@ -103,6 +103,7 @@ class DeviceLaunch:
         from pth_flash_attn_b200 import host, planner
 
         self.torch = torch
+        self.flags = 0
         g = torch.Generator(device="cpu").manual_seed(seed)
         lens, qlens = launch["seq_lens"], launch["q_lens"]
         R, T = len(lens), int(sum(qlens))
@@ -164,7 +165,7 @@ class DeviceLaunch:
         s = self.sets[which % len(self.sets)]
         host.attention_forward(self.q, self.out, s["views"], s["bt"], self.lens, self.qsl, bq=self.bq,
                                num_splits=self.S, softmax_scale=D ** -0.5, ws_o=self.ws_o, ws_lse=self.ws_lse,
-                               window=self.window, causal=self.causal)
+                               window=self.window, causal=self.causal, flags=self.flags)
 
     def launch_attention_only(self, which=0):
         """Only the attention kernel (for the per-kernel roofline timing)."""
@@ -175,7 +176,8 @@ class DeviceLaunch:
                                 num_splits=self.S, softmax_scale=D ** -0.5, ws_o=self.ws_o, ws_lse=self.ws_lse,
                                 window=self.window, causal=self.causal)
         lib = capi.load_library()
-        rc = lib.attention(a, stream=self.torch.cuda.current_stream().cuda_stream)
+        rc = lib.attention(a, options=capi.make_options(capi.KERNEL_AUTO, self.flags),
+                           stream=self.torch.cuda.current_stream().cuda_stream)
         if rc != 0:
             raise RuntimeError(lib.last_error())
 
@@ -346,6 +348,8 @@ def main():
     ap.add_argument("--splits", type=int, default=0, help="override the planner's split count (exploration)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="three eager passes over the workload and exit (the command to run under ncu)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -394,6 +398,13 @@ def main():
     for d in dls:
         d.launch(0)
     torch.cuda.synchronize()
+    if args.profile:
+        for i in range(2):
+            for d in dls:
+                d.launch(i)
+        torch.cuda.synchronize()
+        print(json.dumps({"profile": args.config, "launches_per_pass": kernels_per_step, "passes": 3}))
+        return
     graphs = []
     if not args.no_graph:
         side = torch.cuda.Stream()

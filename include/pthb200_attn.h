@@ -169,7 +169,7 @@ typedef struct PthB200Options {
   int32_t abi_version;
   int32_t struct_bytes;
   int32_t kernel;
-  int32_t reserved;
+  int32_t flags; /* reserved, 0 */
   float* lse_out; /* [num_tokens, num_q_heads] fp32 or NULL */
   int64_t lse_stride_token;
   int64_t lse_stride_head;
@@ -216,9 +216,10 @@ int32_t pthb200_launch_count(const PthAttnArgs* args, int32_t* attention_kernels
  *   s_out[key][n] = sum_d k[key][d] * q[n][d]      (fp32 [128][16])
  *   o_out[d][n]   = sum_key v[key][d] * pm[key][n] (fp32 [128][16])
  * k, v: int8 [128][128]; q: bf16 [16][128]; pm: bf16 [128][16]; all dense on the
- * device.  padded != 0 uses the operand image of the attention kernel. */
+ * device.  variant bit 0: the padded operand image of the attention kernel (else
+ * dense). */
 int32_t pthb200_test_tile(const void* k, const void* q, const void* v, const void* pm,
-                          float* s_out, float* o_out, int32_t padded, void* stream);
+                          float* s_out, float* o_out, int32_t variant, void* stream);
 /* Synchronises the device, returns and clears the status word in which a
  * kernel records a bounded wait that gave up (0 = none). */
 int32_t pthb200_device_status(int32_t* status);

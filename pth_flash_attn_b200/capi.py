@@ -105,7 +105,7 @@ class PthB200Options(ctypes.Structure):
         ("abi_version", ctypes.c_int32),
         ("struct_bytes", ctypes.c_int32),
         ("kernel", ctypes.c_int32),
-        ("reserved", ctypes.c_int32),
+        ("flags", ctypes.c_int32),
         ("lse_out", ctypes.c_void_p),
         ("lse_stride_token", ctypes.c_int64),
         ("lse_stride_head", ctypes.c_int64),
@@ -237,11 +237,12 @@ def load_library() -> B200Lib:
     return _LIB
 
 
-def make_options(kernel: int = KERNEL_AUTO) -> PthB200Options:
+def make_options(kernel: int = KERNEL_AUTO, flags: int = 0) -> PthB200Options:
     o = PthB200Options()
     o.abi_version = ABI_VERSION
     o.struct_bytes = ctypes.sizeof(PthB200Options)
     o.kernel = kernel
+    o.flags = flags
     return o
 
 

@@ -6,12 +6,14 @@
 // kernel stays bound by the HBM reads of the cache.
 //
 // One CTA (128 threads) = one work item (row tile, KV head, split).  Per tile:
+//   0. thread t resolves key t of the tile after next through the block table
+//      into one byte offset (shared by the four cache streams) in shared memory;
 //   1. the raw cell bytes of the tile, prefetched one tile ahead into registers
-//      with coalesced 8-byte (K) and 4-byte (V) loads through the block table,
-//      are widened int8 -> bf16 and stored as MMA operand images (umma_tile.cuh);
+//      with coalesced 8-byte (K) and 4-byte (V) loads, are widened int8 -> bf16
+//      and stored as MMA operand images (umma_tile.cuh);
 //   2. thread 0 issues S^T = K Q^T into TMEM; thread t then owns key t: it reads
-//      its NPAD scores, applies k_scale[t] * softmax_scale * log2(e) and the
-//      visibility mask;
+//      the scores of the live rows, applies k_scale[t] * softmax_scale * log2(e)
+//      and, on tiles that touch a row's range boundary, the visibility mask;
 //   3. the running row maxima are agreed through warp reductions + shared
 //      memory; p = exp2(s - m); P[t, :] = bf16(p * v_scale[t]) goes to the P image,
 //      the unscaled p is summed per thread;
@@ -40,7 +42,8 @@ struct SmemLayout {
   static constexpr int vw = kw + kWideBytes;
   static constexpr int qs = vw + kWideBytes;
   static constexpr int ps = qs + NPAD * 256;
-  static constexpr int wred = ps + NPAD * 256;        // float [4][NPAD]
+  static constexpr int offs = ps + NPAD * 256;        // int64 [2][128] key offsets
+  static constexpr int wred = offs + 2 * 128 * 8;     // float [4][NPAD]
   static constexpr int mrun = wred + 4 * NPAD * 4;    // float [NPAD]
   static constexpr int rlo = mrun + NPAD * 4;         // int [NPAD]
   static constexpr int rhi = rlo + NPAD * 4;          // int [NPAD]
@@ -61,6 +64,12 @@ __device__ __forceinline__ int float_key(float f) {
 }
 __device__ __forceinline__ float key_float(int k) { return __int_as_float(k ^ ((k >> 31) & 0x7fffffff)); }
 
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct RawTile {
   uint2 k[16];
   uint2 v[16];
@@ -78,8 +87,10 @@ __device__ __forceinline__ uint32_t ldg4(const uint8_t* p) {
   return r;
 }
 
-// Byte offset of (block, slot) of KV position `pos` in a stream, without the head term.
-__device__ __forceinline__ void locate(const KernelParams& p, const int32_t* bt, int pos, int64_t* blk, int64_t* slot) {
+// Byte offset of KV position `pos` (block and slot terms; -1 if pos is outside [kv_lo, kv_hi)).
+// The four cache streams share their block and slot strides (checked on the host).
+__device__ __forceinline__ int64_t key_offset(const KernelParams& p, const int32_t* bt, int pos, int kv_lo, int kv_hi) {
+  if (pos < kv_lo || pos >= kv_hi) return -1;
   int page, s;
   if (p.block_shift >= 0) {
     page = pos >> p.block_shift;
@@ -88,39 +99,30 @@ __device__ __forceinline__ void locate(const KernelParams& p, const int32_t* bt,
     page = pos / p.block_size;
     s = pos - page * p.block_size;
   }
-  *blk = __ldg(bt + page);
-  *slot = s;
+  return (int64_t)__ldg(bt + page) * p.k.stride_block + (int64_t)s * p.k.stride_slot;
 }
 
 // Thread (tsub = tid / 16, c = tid % 16) fetches chunk c of keys tsub, tsub + 8, ...: the 16
 // lanes of a half warp read one key's 128 K bytes (and 128 V bytes) contiguously.
-__device__ __forceinline__ void load_tile(const KernelParams& p, const int32_t* bt, int kvh, int tile, int kv_lo,
-                                          int kv_hi, int tid, RawTile& r) {
-  const int c = tid & 15, tsub = tid >> 4;
-  const int base = tile * kTileKeys;
-  const uint8_t* kb = p.k.data + (int64_t)kvh * p.k.stride_head + c * 8;
-  const uint8_t* vb = p.v.data + (int64_t)kvh * p.v.stride_head + c * 8;
+__device__ __forceinline__ void load_tile(const int64_t* offs, const uint8_t* kb, const uint8_t* vb,
+                                          const uint8_t* ksb, const uint8_t* vsb, int tid, RawTile& r) {
+  const int tsub = tid >> 4;
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
-    const int pos = base + tsub + 8 * i;
-    if (pos >= kv_lo && pos < kv_hi) {
-      int64_t blk, slot;
-      locate(p, bt, pos, &blk, &slot);
-      r.k[i] = ldg8(kb + blk * p.k.stride_block + slot * p.k.stride_slot);
-      const uint8_t* vp = vb + blk * p.v.stride_block + slot * p.v.stride_slot;
-      r.v[i].x = ldg4(vp);
-      r.v[i].y = ldg4(vp + 4);
+    const int64_t off = offs[tsub + 8 * i];
+    if (off >= 0) {
+      r.k[i] = ldg8(kb + off);
+      r.v[i].x = ldg4(vb + off);
+      r.v[i].y = ldg4(vb + off + 4);
     } else {
       r.k[i] = make_uint2(0u, 0u);
       r.v[i] = make_uint2(0u, 0u);
     }
   }
-  const int pos = base + tid;
-  if (pos >= kv_lo && pos < kv_hi) {
-    int64_t blk, slot;
-    locate(p, bt, pos, &blk, &slot);
-    r.ks = __uint_as_float(ldg4(p.ks.data + blk * p.ks.stride_block + slot * p.ks.stride_slot + (int64_t)kvh * p.ks.stride_head));
-    r.vs = __uint_as_float(ldg4(p.vs.data + blk * p.vs.stride_block + slot * p.vs.stride_slot + (int64_t)kvh * p.vs.stride_head));
+  const int64_t off = offs[tid];
+  if (off >= 0) {
+    r.ks = __uint_as_float(ldg4(ksb + off));
+    r.vs = __uint_as_float(ldg4(vsb + off));
   } else {
     r.ks = 0.f;
     r.vs = 0.f;
@@ -129,19 +131,12 @@ __device__ __forceinline__ void load_tile(const KernelParams& p, const int32_t* 
 
 __device__ __forceinline__ void store_tile(uint8_t* kw, uint8_t* vw, int tid, const RawTile& r) {
   const int c = tid & 15, tsub = tid >> 4;
+  const int base = c * kChunkStride + tsub * 16;
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
-    const int off = c * kChunkStride + (tsub + 8 * i) * 16;
-    *reinterpret_cast<uint4*>(kw + off) = widen8_bf16(r.k[i]);
-    *reinterpret_cast<uint4*>(vw + off) = widen8_bf16(r.v[i]);
+    *reinterpret_cast<uint4*>(kw + base + i * 128) = widen8_bf16(r.k[i]);
+    *reinterpret_cast<uint4*>(vw + base + i * 128) = widen8_bf16(r.v[i]);
   }
-}
-
-template <int NPAD>
-__device__ __forceinline__ void tmem_load_cols(uint32_t taddr, uint32_t* r) {
-#pragma unroll
-  for (int g = 0; g < NPAD / 16; ++g) tc::tmem_ld16(taddr + g * 16, r + g * 16);
-  tc::tmem_ld_wait();
 }
 
 // Rows of this work item: row n < rows is (token tok0 + n / G, head kvh * G + n % G).
@@ -159,6 +154,7 @@ umma_attention_kernel(const __grid_constant__ KernelParams p) {
   uint8_t* vw = smem + L::vw;
   uint8_t* qs = smem + L::qs;
   uint8_t* ps = smem + L::ps;
+  int64_t* offs = reinterpret_cast<int64_t*>(smem + L::offs);
   float* wred = reinterpret_cast<float*>(smem + L::wred);
   float* mrun = reinterpret_cast<float*>(smem + L::mrun);
   int* rlo = reinterpret_cast<int*>(smem + L::rlo);
@@ -204,8 +200,13 @@ umma_attention_kernel(const __grid_constant__ KernelParams p) {
   }
 
   const int32_t* bt = p.block_table + (int64_t)t.req * p.block_table_row_stride;
+  const int c = tid & 15;
+  const uint8_t* kb = p.k.data + (int64_t)kvh * p.k.stride_head + c * 8;
+  const uint8_t* vb = p.v.data + (int64_t)kvh * p.v.stride_head + c * 8;
+  const uint8_t* ksb = p.ks.data + (int64_t)kvh * p.ks.stride_head;
+  const uint8_t* vsb = p.vs.data + (int64_t)kvh * p.vs.stride_head;
 
-  // ---- set-up: row ranges, barriers, TMEM, Q image --------------------------
+  // ---- set-up: row ranges, barriers, TMEM, Q image, zeroed P image, key offsets ----
   if (tid < NPAD) {
     int lo = 0, hi = -1;
     if (tid < rows) visible_range(p, t, t.first_idx + tid / p.group, &lo, &hi);
@@ -223,19 +224,27 @@ umma_attention_kernel(const __grid_constant__ KernelParams p) {
     tc::tmem_relinquish();
   }
   for (int idx = tid; idx < NPAD * kChunks; idx += kThreads) {
-    const int n = idx >> 4, c = idx & 15;
+    const int n = idx >> 4, cc = idx & 15;
     uint4 val = make_uint4(0u, 0u, 0u, 0u);
     if (n < rows) {
       int token, head;
       row_target(p, t, kvh, n, &token, &head);
       val = *reinterpret_cast<const uint4*>(p.q + (int64_t)token * p.q_stride_token + (int64_t)head * p.q_stride_head +
-                                            c * 16);
+                                            cc * 16);
     }
-    *reinterpret_cast<uint4*>(qs + c * (NPAD * 16) + n * 16) = val;
+    *reinterpret_cast<uint4*>(qs + cc * (NPAD * 16) + n * 16) = val;
   }
-
-  RawTile raw;
-  load_tile(p, bt, kvh, tile_begin, range_begin, range_end, tid, raw);
+#pragma unroll
+  for (int j = 0; j < NPAD / 8; ++j)
+    *reinterpret_cast<uint4*>(ps + j * kPGroupStride + tid * 16) = make_uint4(0u, 0u, 0u, 0u);
+  offs[tid] = key_offset(p, bt, tile_begin * kTileKeys + tid, range_begin, range_end);
+  offs[128 + tid] =
+      tile_begin + 1 < tile_end ? key_offset(p, bt, (tile_begin + 1) * kTileKeys + tid, range_begin, range_end) : -1;
+  // Tiles whose keys every live row sees need no mask: [mask_lo, mask_hi] is the
+  // position range visible to all rows (lo and hi do not decrease with the row).
+  int mask_lo, mask_hi, tmp;
+  visible_range(p, t, t.first_idx + t.ntok - 1, &mask_lo, &tmp);
+  visible_range(p, t, t.first_idx, &tmp, &mask_hi);
 
   tc::fence_before_sync();
   tc::fence_async_smem();
@@ -246,6 +255,9 @@ umma_attention_kernel(const __grid_constant__ KernelParams p) {
   const uint32_t o_tmem = tmem_base + NPAD;   // columns [NPAD, 2 NPAD)
   const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
   const uint32_t kw_s = tc::smem_u32(kw), vw_s = tc::smem_u32(vw), qs_s = tc::smem_u32(qs), ps_s = tc::smem_u32(ps);
+
+  RawTile raw;
+  load_tile(offs, kb, vb, ksb, vsb, tid, raw);
 
   float l_part[NPAD];
 #pragma unroll
@@ -261,74 +273,90 @@ umma_attention_kernel(const __grid_constant__ KernelParams p) {
     }
     store_tile(kw, vw, tid, raw);
     const float ks_cur = raw.ks, vs_cur = raw.vs;
-    if (tile + 1 < tile_end) load_tile(p, bt, kvh, tile + 1, range_begin, range_end, tid, raw);
+    if (tile + 1 < tile_end) load_tile(offs + ((it + 1) & 1) * 128, kb, vb, ksb, vsb, tid, raw);
 
     tc::fence_async_smem();
-    __syncthreads();  // (A) operand images complete
+    __syncthreads();  // (A) operand images complete; the offsets of tile + 1 have been consumed
     if (tid == 0) {
       tc::fence_after_sync();
       issue_qk<NPAD>(s_tmem, kw_s, qs_s, kChunkStride);
       tc::mma_commit(bar_s);
     }
+    // Offsets of the tile after next go where this tile's offsets were.
+    if (tile + 2 < tile_end) offs[(it & 1) * 128 + tid] = key_offset(p, bt, (tile + 2) * kTileKeys + tid, range_begin, range_end);
+
     ok &= tc::mbar_wait_bounded(bar_s, it & 1);
     tc::fence_after_sync();
 
     uint32_t sr[NPAD];
-    tmem_load_cols<NPAD>(s_tmem + lane_addr, sr);
+#pragma unroll
+    for (int g = 0; g < NPAD / 16; ++g)
+      if (g * 16 < rows) tc::tmem_ld16(s_tmem + lane_addr + g * 16, sr + g * 16);
+    tc::tmem_ld_wait();
     const int pos = tile * kTileKeys + tid;
+    const bool interior = tile * kTileKeys >= mask_lo && tile * kTileKeys + (kTileKeys - 1) <= mask_hi;
     const float mult = ks_cur * p.scale_log2;
     float s[NPAD];
 #pragma unroll
     for (int n = 0; n < NPAD; ++n) {
-      const bool vis = pos >= rlo[n] && pos <= rhi[n];
-      s[n] = vis ? __uint_as_float(sr[n]) * mult : -INFINITY;
-      const int key = __reduce_max_sync(0xffffffffu, float_key(s[n]));
-      if (lane == (n & 31)) wred[warp * NPAD + n] = key_float(key);
+      if (n < rows) {
+        const bool vis = interior || (pos >= rlo[n] && pos <= rhi[n]);
+        s[n] = vis ? __uint_as_float(sr[n]) * mult : -INFINITY;
+        const int key = __reduce_max_sync(0xffffffffu, float_key(s[n]));
+        if (lane == (n & 31)) wred[warp * NPAD + n] = key_float(key);
+      }
     }
     __syncthreads();  // (B) per-warp maxima visible
 
     bool grew = false;
-    uint32_t pk[NPAD / 2];
 #pragma unroll
     for (int n = 0; n < NPAD; ++n) {
-      const float m_old = mrun[n];
-      const float m_tile = fmaxf(fmaxf(wred[n], wred[NPAD + n]), fmaxf(wred[2 * NPAD + n], wred[3 * NPAD + n]));
-      const float m_new = fmaxf(m_old, m_tile);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float a = exp2f(m_old - m_use);
-      const float pr = exp2f(s[n] - m_use);
-      l_part[n] = l_part[n] * a + pr;
-      grew |= (m_new > m_old) && (m_old > -INFINITY);
-      s[n] = pr * vs_cur;
-    }
-#pragma unroll
-    for (int n = 0; n < NPAD; n += 2) {
-      const __nv_bfloat162 b = __floats2bfloat162_rn(s[n], s[n + 1]);
-      pk[n / 2] = *reinterpret_cast<const uint32_t*>(&b);
+      if (n < rows) {
+        const float m_old = mrun[n];
+        const float m_tile = fmaxf(fmaxf(wred[n], wred[NPAD + n]), fmaxf(wred[2 * NPAD + n], wred[3 * NPAD + n]));
+        const float m_new = fmaxf(m_old, m_tile);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float a = fast_exp2(m_old - m_use);
+        const float pr = fast_exp2(s[n] - m_use);
+        l_part[n] = l_part[n] * a + pr;
+        grew |= (m_new > m_old) && (m_old > -INFINITY);
+        s[n] = pr * vs_cur;
+      } else {
+        s[n] = 0.f;
+      }
     }
 #pragma unroll
     for (int j = 0; j < NPAD / 8; ++j) {
-      *reinterpret_cast<uint4*>(ps + j * kPGroupStride + tid * 16) =
-          make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+      if (j * 8 < rows) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const __nv_bfloat162 b = __floats2bfloat162_rn(s[j * 8 + 2 * e], s[j * 8 + 2 * e + 1]);
+          pk[e] = *reinterpret_cast<const uint32_t*>(&b);
+        }
+        *reinterpret_cast<uint4*>(ps + j * kPGroupStride + tid * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
     }
 
     // A grown maximum rescales the accumulated O^T columns (thread = lane d of O^T).
     if (it > 0 && grew) {
 #pragma unroll
       for (int g = 0; g < NPAD / 16; ++g) {
-        uint32_t o[16];
-        tc::tmem_ld16(o_tmem + lane_addr + g * 16, o);
-        tc::tmem_ld_wait();
+        if (g * 16 < rows) {
+          uint32_t o[16];
+          tc::tmem_ld16(o_tmem + lane_addr + g * 16, o);
+          tc::tmem_ld_wait();
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const int n = g * 16 + e;
-          const float m_old = mrun[n];
-          const float m_tile = fmaxf(fmaxf(wred[n], wred[NPAD + n]), fmaxf(wred[2 * NPAD + n], wred[3 * NPAD + n]));
-          const float m_new = fmaxf(m_old, m_tile);
-          const float a = (m_new == -INFINITY) ? 1.f : exp2f(m_old - m_new);
-          o[e] = __float_as_uint(__uint_as_float(o[e]) * a);
+          for (int e = 0; e < 16; ++e) {
+            const int n = g * 16 + e;
+            const float m_old = mrun[n];
+            const float m_tile = fmaxf(fmaxf(wred[n], wred[NPAD + n]), fmaxf(wred[2 * NPAD + n], wred[3 * NPAD + n]));
+            const float m_new = fmaxf(m_old, m_tile);
+            const float a = (m_new == -INFINITY || n >= rows) ? 1.f : fast_exp2(m_old - m_new);
+            o[e] = __float_as_uint(__uint_as_float(o[e]) * a);
+          }
+          tc::tmem_st16(o_tmem + lane_addr + g * 16, o);
         }
-        tc::tmem_st16(o_tmem + lane_addr + g * 16, o);
       }
       tc::tmem_st_wait();
     }
@@ -336,7 +364,7 @@ umma_attention_kernel(const __grid_constant__ KernelParams p) {
     tc::fence_before_sync();
     tc::fence_async_smem();
     __syncthreads();  // (C) P image and O^T rescale complete; mrun/wred reads done
-    if (tid < NPAD) {
+    if (tid < rows) {
       const float m_tile =
           fmaxf(fmaxf(wred[tid], wred[NPAD + tid]), fmaxf(wred[2 * NPAD + tid], wred[3 * NPAD + tid]));
       mrun[tid] = fmaxf(mrun[tid], m_tile);
@@ -351,18 +379,23 @@ umma_attention_kernel(const __grid_constant__ KernelParams p) {
   // ---- epilogue -------------------------------------------------------------
   ok &= tc::mbar_wait_bounded(bar_o, (it - 1) & 1);
   tc::fence_after_sync();
-  __syncthreads();  // wred free for the row sums (last reads were before the mrun update)
+  __syncthreads();  // wred free for the row sums (its last readers are past barrier C)
 #pragma unroll
   for (int n = 0; n < NPAD; ++n) {
-    float v = l_part[n];
+    if (n < rows) {
+      float v = l_part[n];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    if (lane == (n & 31)) wred[warp * NPAD + n] = v;
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == (n & 31)) wred[warp * NPAD + n] = v;
+    }
   }
   __syncthreads();
 
   uint32_t ot[NPAD];
-  tmem_load_cols<NPAD>(o_tmem + lane_addr, ot);
+#pragma unroll
+  for (int g = 0; g < NPAD / 16; ++g)
+    if (g * 16 < rows) tc::tmem_ld16(o_tmem + lane_addr + g * 16, ot + g * 16);
+  tc::tmem_ld_wait();
 #pragma unroll
   for (int n = 0; n < NPAD; ++n) {
     if (n < rows) {
@@ -401,7 +434,7 @@ umma_attention_kernel(const __grid_constant__ KernelParams p) {
 }
 
 template <int NPAD>
-cudaError_t launch_npad(const KernelParams& p, cudaStream_t stream) {
+cudaError_t launch_variant(const KernelParams& p, cudaStream_t stream) {
   constexpr int smem = SmemLayout<NPAD>::total;
   static bool configured[64] = {};
   int dev = 0;
@@ -415,6 +448,11 @@ cudaError_t launch_npad(const KernelParams& p, cudaStream_t stream) {
   const dim3 grid(p.num_q_tiles, p.num_kv_heads, p.num_splits);
   umma_attention_kernel<NPAD><<<grid, kThreads, smem, stream>>>(p);
   return cudaGetLastError();
+}
+
+template <int NPAD>
+cudaError_t launch_npad(const KernelParams& p, cudaStream_t stream) {
+  return launch_variant<NPAD>(p, stream);
 }
 
 }  // namespace
@@ -433,6 +471,13 @@ bool umma_supports(const KernelParams& p, const char** why) {
       !mult8(p.k.stride_head)) {
     *why = "k_cache rows are not 8-byte aligned";
     return false;
+  }
+  const StreamParams* others[3] = {&p.v, &p.ks, &p.vs};
+  for (const StreamParams* s : others) {
+    if (s->stride_block != p.k.stride_block || s->stride_slot != p.k.stride_slot) {
+      *why = "the cache streams do not share their block and slot strides";
+      return false;
+    }
   }
   *why = "";
   return true;

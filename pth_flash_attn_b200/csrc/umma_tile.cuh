@@ -1,6 +1,8 @@
 // Building blocks of the tcgen05 attention kernels at head size 128: the
 // shared-memory image of a widened KV tile, the exact int8 -> bf16 widening,
-// and the two MMA chains over one 128-key tile.
+// and the two MMA chains over one 128-key tile.  Both operands of a
+// tcgen05.mma.kind::f16 must have the same format: an fp16 A operand with a bf16
+// B operand raises an illegal-instruction fault on B200, so everything is bf16.
 //
 // "Token-major" orientation (keys on the MMA M dimension, query rows on N):
 //   S^T[key, row] = sum_d K[key, d] * Q[row, d]      A = K tile (K-major), B = Q (K-major)

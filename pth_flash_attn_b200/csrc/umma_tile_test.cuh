@@ -3,8 +3,8 @@
 // the attention kernel and returns the raw accumulators:
 //   s_out[key][n] = sum_d K[key][d] * Q[n][d]        (128 x 16 fp32)
 //   o_out[d][n]   = sum_key V[key][d] * P[key][n]    (128 x 16 fp32)
-// `padded` selects the chunk stride of the widened image (2064 bytes as the
-// attention kernel uses, or the dense 2048), so a test can tell a layout
+// Bit 0 of `variant` selects the chunk stride of the widened image (2064 bytes as
+// the attention kernel uses, or the dense 2048), so a test can tell a layout
 // mistake from a padding mistake.
 // Included at the end of umma_kernel.cu (it shares that file's status word).
 #pragma once
@@ -79,15 +79,16 @@ __global__ void __launch_bounds__(128) umma_tile_test_kernel(const int8_t* k, co
 }  // namespace pthb200
 
 extern "C" int32_t pthb200_test_tile(const void* k, const void* q, const void* v, const void* pm, float* s_out,
-                                     float* o_out, int32_t padded, void* stream) {
+                                     float* o_out, int32_t variant, void* stream) {
   using namespace pthb200;
   using namespace pthb200::tile_test;
   const int smem = 2 * kWideBytes + 2 * NPAD * 256 + 64;
-  cudaError_t err = cudaFuncSetAttribute(umma_tile_test_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  auto* fn = umma_tile_test_kernel;
+  cudaError_t err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (err != cudaSuccess) return PTH_ATTN_ECUDA;
-  umma_tile_test_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(
+  fn<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const int8_t*>(k), static_cast<const __nv_bfloat16*>(q), static_cast<const int8_t*>(v),
-      static_cast<const __nv_bfloat16*>(pm), s_out, o_out, padded ? kChunkStride : 2048);
+      static_cast<const __nv_bfloat16*>(pm), s_out, o_out, (variant & 1) ? kChunkStride : 2048);
   return cudaGetLastError() == cudaSuccess ? PTH_ATTN_OK : PTH_ATTN_ECUDA;
 }
 

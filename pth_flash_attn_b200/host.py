@@ -95,14 +95,14 @@ def fill_combine_args(a: capi.PthAttnArgs) -> capi.PthAttnCombineArgs:
 
 def attention_forward(q, out, cache: CacheViews, block_table, seq_lens, query_start_loc, *, bq: int,
                       num_splits: int, softmax_scale: float, ws_o=None, ws_lse=None, window: int = 0,
-                      causal: bool = True, lse_out=None, kernel: int = capi.KERNEL_AUTO,
+                      causal: bool = True, lse_out=None, kernel: int = capi.KERNEL_AUTO, flags: int = 0,
                       lib: capi.B200Lib | None = None) -> None:
     """Attention (+ combine when ``num_splits > 1``) on the current stream; raises on a refusal."""
     lib = lib or capi.load_library()
     a = fill_attn_args(q, out, cache, block_table, seq_lens, query_start_loc, bq=bq,
                        num_splits=num_splits, softmax_scale=softmax_scale, ws_o=ws_o, ws_lse=ws_lse,
                        window=window, causal=causal)
-    opt = capi.make_options(kernel)
+    opt = capi.make_options(kernel, flags)
     if lse_out is not None:
         opt.lse_out = lse_out.data_ptr()
         opt.lse_stride_token, opt.lse_stride_head = lse_out.stride(0) * 4, lse_out.stride(1) * 4

@@ -31,7 +31,7 @@ def q_to_device(q_f32: np.ndarray, dtype=torch.bfloat16, device="cuda"):
 
 def run_case(c: orc.PagedInt8Cache, q_f32: np.ndarray, qsl, softmax_scale: float, *, bq: int,
              num_splits: int = 1, window: int = 0, causal: bool = True,
-             kernel: int = capi.KERNEL_AUTO, out_dtype=torch.bfloat16, q_dtype=torch.bfloat16,
+             kernel: int = capi.KERNEL_AUTO, flags: int = 0, out_dtype=torch.bfloat16, q_dtype=torch.bfloat16,
              pad_tokens: int = 0):
     """Run one launch; returns dict(out fp32 numpy, lse numpy, canaries intact flags, ws)."""
     dev = "cuda"
@@ -50,7 +50,7 @@ def run_case(c: orc.PagedInt8Cache, q_f32: np.ndarray, qsl, softmax_scale: float
         ws_lse = torch.full((num_splits, T, Hq), float("nan"), dtype=torch.float32, device=dev)
     host.attention_forward(q, out, views, bt, lens, qsl_t, bq=bq, num_splits=num_splits,
                            softmax_scale=softmax_scale, ws_o=ws_o, ws_lse=ws_lse, window=window,
-                           causal=causal, lse_out=lse, kernel=kernel)
+                           causal=causal, lse_out=lse, kernel=kernel, flags=flags)
     torch.cuda.synchronize()
     tail = out_buf[T * Hq * D * esz:]
     res = dict(
