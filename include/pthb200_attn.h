@@ -158,7 +158,9 @@ typedef struct PthAttnCombineArgs {
 enum {
   PTHB200_KERNEL_AUTO = 0,   /* the shipped choice */
   PTHB200_KERNEL_SCALAR = 1, /* CUDA-core kernel: every head size, layout, dtype */
-  PTHB200_KERNEL_UMMA = 2    /* tcgen05 kernel; EINVAL where it does not apply */
+  PTHB200_KERNEL_UMMA = 2,   /* tcgen05 int8 kernel (kind::i8, cache bytes used as stored);
+                                EINVAL where it does not apply */
+  PTHB200_KERNEL_UMMA_BF16 = 3 /* tcgen05 kernel that widens the cache to bf16 (kind::f16) */
 };
 
 /* Options of the _ex entry points.  Zero-initialise, then set abi_version and
@@ -220,6 +222,11 @@ int32_t pthb200_launch_count(const PthAttnArgs* args, int32_t* attention_kernels
  * dense). */
 int32_t pthb200_test_tile(const void* k, const void* q, const void* v, const void* pm,
                           float* s_out, float* o_out, int32_t variant, void* stream);
+/* The integer counterpart: k, v int8 [128][128]; q int8 [32][128] (rows 0-15 high
+ * digits, 16-31 low digits); pm int8 [128][48]; s_out int32 [128][32],
+ * o_out int32 [128][48]. */
+int32_t pthb200_test_tile_i8(const void* k, const void* q, const void* v, const void* pm,
+                             int32_t* s_out, int32_t* o_out, void* stream);
 /* Synchronises the device, returns and clears the status word in which a
  * kernel records a bounded wait that gave up (0 = none). */
 int32_t pthb200_device_status(int32_t* status);

@@ -17,7 +17,7 @@ from pathlib import Path
 ABI_VERSION = 2
 F32, F16, BF16 = 0, 1, 2
 OK, EINVAL, ECUDA, ENOCUDA = 0, -1, -2, -3
-KERNEL_AUTO, KERNEL_SCALAR, KERNEL_UMMA = 0, 1, 2
+KERNEL_AUTO, KERNEL_SCALAR, KERNEL_UMMA, KERNEL_UMMA_BF16 = 0, 1, 2, 3
 
 LIBRARY_PATH = Path(__file__).with_name("libpthb200_attn.so")
 
@@ -128,6 +128,7 @@ EXPORTED_SYMBOLS = (
     "pthb200_check_call",
     "pthb200_launch_count",
     "pthb200_test_tile",
+    "pthb200_test_tile_i8",
     "pthb200_device_status",
 )
 
@@ -174,6 +175,8 @@ class B200Lib:
                                              ctypes.POINTER(ctypes.c_int32)]
         lib.pthb200_test_tile.restype = ctypes.c_int32
         lib.pthb200_test_tile.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int32, ctypes.c_void_p]
+        lib.pthb200_test_tile_i8.restype = ctypes.c_int32
+        lib.pthb200_test_tile_i8.argtypes = [ctypes.c_void_p] * 7
         lib.pthb200_device_status.restype = ctypes.c_int32
         lib.pthb200_device_status.argtypes = [ctypes.POINTER(ctypes.c_int32)]
         if lib.pthb200_abi_version() != ABI_VERSION:

@@ -47,7 +47,7 @@ int32_t check_options(const PthB200Options* o) {
   if (o == nullptr) return PTH_ATTN_OK;
   PTHB_REQUIRE(o->abi_version == PTH_ATTN_ABI_VERSION, "options.abi_version does not match the library");
   PTHB_REQUIRE(o->struct_bytes == (int32_t)sizeof(PthB200Options), "options.struct_bytes != sizeof(PthB200Options)");
-  PTHB_REQUIRE(o->kernel >= PTHB200_KERNEL_AUTO && o->kernel <= PTHB200_KERNEL_UMMA, "options.kernel is not a kernel family");
+  PTHB_REQUIRE(o->kernel >= PTHB200_KERNEL_AUTO && o->kernel <= PTHB200_KERNEL_UMMA_BF16, "options.kernel is not a kernel family");
   if (o->lse_out != nullptr) {
     PTHB_REQUIRE(aligned(o->lse_out, 4), "options.lse_out must be 4-byte aligned");
     PTHB_REQUIRE(o->lse_stride_token % 4 == 0 && o->lse_stride_head % 4 == 0 && o->lse_stride_token >= 0 &&
@@ -165,14 +165,14 @@ int32_t build_attention(const PthAttnArgs* a, const PthB200Options* opt, KernelP
   return PTH_ATTN_OK;
 }
 
-// Kernel family for these parameters: 1 = scalar, 2 = tcgen05.
+// Kernel family for these parameters (a PTHB200_KERNEL_* value other than AUTO).
 int32_t choose_family(const KernelParams& p, const PthB200Options* opt, int32_t* family) {
   const int32_t want = opt ? opt->kernel : PTHB200_KERNEL_AUTO;
   const char* why = "";
   const bool umma_ok = umma_supports(p, &why);
-  if (want == PTHB200_KERNEL_UMMA) {
+  if (want == PTHB200_KERNEL_UMMA || want == PTHB200_KERNEL_UMMA_BF16) {
     PTHB_REQUIRE(umma_ok, std::string("options.kernel = UMMA does not apply: ") + why);
-    *family = PTHB200_KERNEL_UMMA;
+    *family = want;
   } else if (want == PTHB200_KERNEL_SCALAR) {
     *family = PTHB200_KERNEL_SCALAR;
   } else {
@@ -190,6 +190,8 @@ int32_t attention_impl(const PthAttnArgs* a, const PthB200Options* opt, void* st
   if (!launch) return PTH_ATTN_OK;
   cudaError_t err;
   if (family == PTHB200_KERNEL_UMMA) {
+    err = launch_umma_i8_attention(p, static_cast<cudaStream_t>(stream));
+  } else if (family == PTHB200_KERNEL_UMMA_BF16) {
     err = launch_umma_attention(p, static_cast<cudaStream_t>(stream));
   } else {
     PTHB_REQUIRE((int64_t)p.num_q_tiles <= 0x7fffffff, "too many row tiles");

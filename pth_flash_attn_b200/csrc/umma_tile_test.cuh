@@ -99,6 +99,9 @@ extern "C" int32_t pthb200_device_status(int32_t* status) {
   if (cudaDeviceSynchronize() != cudaSuccess) return PTH_ATTN_ECUDA;
   if (cudaMemcpyFromSymbol(&v, pthb200::g_umma_status, sizeof(v)) != cudaSuccess) return PTH_ATTN_ECUDA;
   if (cudaMemcpyToSymbol(pthb200::g_umma_status, &zero, sizeof(zero)) != cudaSuccess) return PTH_ATTN_ECUDA;
+  unsigned int w = 0;
+  if (pthb200::read_i8_status(&w) != cudaSuccess) return PTH_ATTN_ECUDA;
+  v |= w;
   if (status) *status = (int32_t)v;
   return PTH_ATTN_OK;
 }

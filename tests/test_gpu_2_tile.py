@@ -34,3 +34,25 @@ def test_umma_tile(padded):
     # products are exact in fp32; only the accumulation order differs
     np.testing.assert_allclose(s_got, s_want, rtol=1e-5, atol=1e-2)
     np.testing.assert_allclose(o_got, o_want, rtol=1e-5, atol=1e-2)
+
+
+def test_umma_tile_int8():
+    """Raw int8 operand images, both integer MMA chains, int32 accumulators: exact."""
+    lib = capi.load_library()
+    rng = np.random.default_rng(8)
+    k = rng.integers(-128, 128, size=(128, 128), dtype=np.int8)
+    v = rng.integers(-128, 128, size=(128, 128), dtype=np.int8)
+    q = rng.integers(-128, 128, size=(32, 128), dtype=np.int8)
+    pm = rng.integers(0, 128, size=(128, 48), dtype=np.int8)
+    dev = "cuda"
+    kt, vt, qt, pt = (torch.from_numpy(a).to(dev) for a in (k, v, q, pm))
+    s_out = torch.full((128, 32), -7, dtype=torch.int32, device=dev)
+    o_out = torch.full((128, 48), -7, dtype=torch.int32, device=dev)
+    rc = lib.lib.pthb200_test_tile_i8(kt.data_ptr(), qt.data_ptr(), vt.data_ptr(), pt.data_ptr(),
+                                      s_out.data_ptr(), o_out.data_ptr(), None)
+    assert rc == capi.OK
+    assert lib.device_status() == 0, "a bounded wait gave up"
+    s_want = k.astype(np.int64) @ q.astype(np.int64).T
+    o_want = v.astype(np.int64).T @ pm.astype(np.int64)
+    assert np.array_equal(s_out.cpu().numpy(), s_want)
+    assert np.array_equal(o_out.cpu().numpy(), o_want)

@@ -13,8 +13,12 @@ GOLDEN_D128 = ["attn_decode", "attn_verify4", "attn_window_causal", "attn_window
                "attn_noncausal", "attn_mixed"]
 
 
+KERNELS = [capi.KERNEL_UMMA, capi.KERNEL_UMMA_BF16]
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
 @pytest.mark.parametrize("name", GOLDEN_D128)
-def test_golden_attention_umma(name):
+def test_golden_attention_umma(name, kernel):
     from tests.gpu_util import run_case
 
     g = load_golden(name)
@@ -24,7 +28,7 @@ def test_golden_attention_umma(name):
     c = cache_from_golden(g)
     bq = max(1, min(64 // G, int(np.diff(g["qsl"]).max())))
     res = run_case(c, q, g["qsl"], float(g["softmax_scale"]), bq=bq, window=window,
-                   causal=bool(causal), kernel=capi.KERNEL_UMMA)
+                   causal=bool(causal), kernel=kernel)
     assert capi.load_library().device_status() == 0
     valid = g["valid"]
     check_out(res["out"], g["out"], valid, what=name)
@@ -42,9 +46,10 @@ def _seeded(lens, qlens, Hq, Hkv, seed, **kw):
     return c, q, qsl
 
 
+@pytest.mark.parametrize("kernel", KERNELS)
 @pytest.mark.parametrize("S", [1, 2, 5])
 @pytest.mark.parametrize("qlen,G,bq", [(1, 4, 1), (4, 4, 4), (16, 4, 16), (4, 8, 4), (40, 8, 8)])
-def test_seeded_shapes(S, qlen, G, bq):
+def test_seeded_shapes(S, qlen, G, bq, kernel):
     """Decode, verify, drafter and a short prefill chunk, with and without split-KV."""
     from tests.gpu_util import run_case
 
@@ -53,7 +58,7 @@ def test_seeded_shapes(S, qlen, G, bq):
     c, q, qsl = _seeded(lens, qlens, 2 * G, 2, seed=50 + qlen + G)
     scale = 128 ** -0.5
     ref = orc.ref_attention_paged(q, c, qsl, scale)
-    res = run_case(c, q, qsl, scale, bq=bq, num_splits=S, kernel=capi.KERNEL_UMMA)
+    res = run_case(c, q, qsl, scale, bq=bq, num_splits=S, kernel=kernel)
     assert capi.load_library().device_status() == 0
     check_out(res["out"], ref.out, what=f"S{S} q{qlen} G{G}")
     check_lse(res["lse"], ref.lse, what=f"S{S} q{qlen} G{G}")
