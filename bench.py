@@ -57,6 +57,8 @@ def workload_launches(name: str, seed: int = 1001):
         return [dict(seq_lens=[131072], q_lens=[1], Hq=32, Hkv=8)]
     if name == "long_decode_b64":
         return [dict(seq_lens=[8192] * 64, q_lens=[1] * 64, Hq=32, Hkv=8)]
+    if name == "decode_h1":  # one KV head per GPU (the 8-GPU shard shape), same bytes as long_decode_b64
+        return [dict(seq_lens=[8192] * 512, q_lens=[1] * 512, Hq=4, Hkv=1)]
     if name == "verify4":  # BASELINE config 2a
         return [dict(seq_lens=rng.integers(16384, 32769, size=32).tolist(), q_lens=[4] * 32, Hq=32, Hkv=8)]
     if name == "drafter16":  # BASELINE config 2b
@@ -99,7 +101,7 @@ class DeviceLaunch:
     """One launch with everything resident on the device, plus pinned host copies of the
     per-step inputs for the end-to-end leg."""
 
-    def __init__(self, torch, launch, hkv_local, hq_local, device, seed, num_sms, sets=1, splits=None):
+    def __init__(self, torch, launch, hkv_local, hq_local, device, seed, num_sms, sets=1, splits=None, layout="NHD"):
         from pth_flash_attn_b200 import host, planner
 
         self.torch = torch
@@ -131,14 +133,14 @@ class DeviceLaunch:
             scale = torch.rand((need, BS, hkv_local), device=device) * 0.02 + 0.01
             words[..., D // 4] = scale
             words[..., CELL // 4 - 1] = scale
-            perm = torch.randperm(need, generator=g).to(torch.int32)
+            perm = (torch.arange(need) if os.environ.get("BENCH_SEQUENTIAL_BLOCKS") else torch.randperm(need, generator=g)).to(torch.int32)
             bt = torch.zeros((R, max(nblk)), dtype=torch.int32)
             k = 0
             for r, nb in enumerate(nblk):
                 bt[r, :nb] = perm[k:k + nb]
                 k += nb
             base = storage.data_ptr()
-            slot, head = hkv_local * CELL, CELL
+            slot, head = (hkv_local * CELL, CELL) if layout == "NHD" else (CELL, BS * CELL)
             views = host.CacheViews((base, page, slot, head), (base + D + 4, page, slot, head),
                                     (base + D, page, slot, head), (base + 2 * D + 4, page, slot, head),
                                     need, BS, hkv_local, D)
@@ -346,6 +348,7 @@ def main():
     ap.add_argument("--config", default="long_decode")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--splits", type=int, default=0, help="override the planner's split count (exploration)")
+    ap.add_argument("--layout", default="NHD", choices=["NHD", "HND"], help="physical order inside a page")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--profile", action="store_true",
@@ -384,7 +387,7 @@ def main():
     sets = 1 if step_bytes_local >= 4 * l2_bytes else int(-(-4 * l2_bytes // step_bytes_local))
     sets = min(sets, 64)
     dls = [DeviceLaunch(torch, l, l["Hkv"] // world, l["Hq"] // world, device, 1234 + 100 * i + rank, num_sms,
-                        sets=sets, splits=args.splits) for i, l in enumerate(launches)]
+                        sets=sets, splits=args.splits, layout=args.layout) for i, l in enumerate(launches)]
     step_bytes_total = sum(kv_bytes(l, l["Hkv"]) for l in launches)
     step_flops_total = sum(attn_flops(l, l["Hq"]) for l in launches)
     kernels_per_step = sum(d.kernels for d in dls)

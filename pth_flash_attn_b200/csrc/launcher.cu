@@ -147,6 +147,7 @@ int32_t build_attention(const PthAttnArgs* a, const PthB200Options* opt, KernelP
   p.q_dtype = a->q_dtype;
   p.out_dtype = a->out_dtype;
   p.block_size = a->block_size;
+  p.num_blocks = a->num_blocks;
   p.block_shift = -1;
   for (int sh = 0; sh < 31; ++sh)
     if ((1 << sh) == a->block_size) p.block_shift = sh;
@@ -169,14 +170,19 @@ int32_t build_attention(const PthAttnArgs* a, const PthB200Options* opt, KernelP
 int32_t choose_family(const KernelParams& p, const PthB200Options* opt, int32_t* family) {
   const int32_t want = opt ? opt->kernel : PTHB200_KERNEL_AUTO;
   const char* why = "";
+  const char* why_i8 = "";
   const bool umma_ok = umma_supports(p, &why);
-  if (want == PTHB200_KERNEL_UMMA || want == PTHB200_KERNEL_UMMA_BF16) {
-    PTHB_REQUIRE(umma_ok, std::string("options.kernel = UMMA does not apply: ") + why);
+  const bool i8_ok = umma_i8_supports(p, &why_i8);
+  if (want == PTHB200_KERNEL_UMMA) {
+    PTHB_REQUIRE(i8_ok, std::string("options.kernel = UMMA does not apply: ") + why_i8);
+    *family = want;
+  } else if (want == PTHB200_KERNEL_UMMA_BF16) {
+    PTHB_REQUIRE(umma_ok, std::string("options.kernel = UMMA_BF16 does not apply: ") + why);
     *family = want;
   } else if (want == PTHB200_KERNEL_SCALAR) {
     *family = PTHB200_KERNEL_SCALAR;
   } else {
-    *family = umma_ok ? PTHB200_KERNEL_UMMA : PTHB200_KERNEL_SCALAR;
+    *family = i8_ok ? PTHB200_KERNEL_UMMA : umma_ok ? PTHB200_KERNEL_UMMA_BF16 : PTHB200_KERNEL_SCALAR;
   }
   return PTH_ATTN_OK;
 }

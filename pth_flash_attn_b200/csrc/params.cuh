@@ -50,6 +50,9 @@ struct KernelParams {
   int32_t bq, num_q_tiles, num_splits;
   int32_t window, causal;
   float scale_log2;  // softmax_scale * log2(e)
+  // integer kernel: how the raw cache bytes are fetched (set by its launcher)
+  int32_t raw_mode;        // 1 = tiled TMA box per page, 2 = bulk copy per contiguous page run
+  int32_t num_blocks;      // blocks in the cache views
 };
 
 // A row tile resolved on the device.
@@ -166,5 +169,7 @@ cudaError_t read_i8_status(unsigned int* v);
 cudaError_t launch_combine_kernel(const CombineParams& p, cudaStream_t stream);
 // True if the tcgen05 kernel handles these parameters.
 bool umma_supports(const KernelParams& p, const char** why);
+// True if the integer tcgen05 kernel handles these parameters.
+bool umma_i8_supports(const KernelParams& p, const char** why);
 
 }  // namespace pthb200
