@@ -63,14 +63,16 @@ namespace {
 constexpr int kGroupThreads = 128;                      // one softmax warpgroup
 constexpr int kSoftmaxThreads = 2 * kGroupThreads;      // warps 0-3 and 4-7
 constexpr int kProducerThreads = 128;                   // warps 8-11
-constexpr int kMmaWarp = 12;
-constexpr int kThreads = kSoftmaxThreads + kProducerThreads + 32;
+constexpr int kQkWarp = 12;                             // lane 0 issues the S^T = K Q^T MMAs
+constexpr int kPvWarp = 13;                             // lane 0 issues the O^T = V^T P MMAs
+constexpr int kLoadWarp = 14;                           // issues the page copies
+constexpr int kThreads = kSoftmaxThreads + kProducerThreads + 96;
 constexpr int kStageScales = 2 * kKeys * 4;                 // k_scale[128], v_scale[128]
 constexpr int kStageBytes = 2 * kImgBytes + kStageScales;   // 34,048 B
 constexpr int kRawRow = 272;                                // aligned bytes that cover a 264-byte cell
 constexpr int kRawStageBytes = kKeys * kRawRow;             // 34,816 B
 
-template <int NPAD, int PD, int NS, int NR>
+template <int NPAD, int PD, int NS, int NR, int SB>
 struct Layout {
   static constexpr int stages = 0;
   static constexpr int qimg = stages + NS * kStageBytes;            // [8][2 NPAD][16]
@@ -84,26 +86,28 @@ struct Layout {
   static constexpr int rlo = sq + NPAD * 4;                         // int [NPAD]
   static constexpr int rhi = rlo + NPAD * 4;                        // int [NPAD]
   static constexpr int bars = (rhi + NPAD * 4 + 7) / 8 * 8;         // uint64 [2 NS + 10 + NR]
-  static constexpr int misc = bars + (2 * NS + 10 + NR) * 8; // abort flag, TMEM slot
+  static constexpr int misc = bars + (2 * NS + 14 + 2 * NR) * 8;    // abort flag, TMEM slot
   static constexpr int total = misc + 16;
   static constexpr int s_cols = 2 * NPAD;
   static constexpr int o_cols = PD * NPAD;
-  static constexpr int tmem_need = 2 * s_cols + 2 * o_cols;
+  static constexpr int s_total = 2 * SB * s_cols;                   // [2 groups][SB] S^T buffers
+  static constexpr int tmem_need = s_total + 2 * o_cols;
   static constexpr int tmem_alloc = tmem_need <= 32 ? 32 : tmem_need <= 64 ? 64 : tmem_need <= 128 ? 128
                                     : tmem_need <= 256 ? 256 : 512;
 };
 
 // Barrier indices inside the barrier array.
-template <int NS>
+template <int NS, int NR>
 struct Bars {
   static constexpr int full = 0;             // [NS] producers -> MMA, 128 arrivals
   static constexpr int empty = NS;           // [NS] MMA (tcgen05.commit) -> producers
-  static constexpr int s_ready = 2 * NS;     // [2] MMA -> softmax
-  static constexpr int s_free = 2 * NS + 2;  // [2] softmax -> MMA, 128 arrivals
-  static constexpr int o_ready = 2 * NS + 4; // [2] MMA -> softmax
-  static constexpr int o_free = 2 * NS + 6;  // [2] softmax -> MMA, 128 arrivals
-  static constexpr int p_ready = 2 * NS + 8; // [2] softmax -> MMA, 128 arrivals
-  static constexpr int raw_full = 2 * NS + 10;// [NR] bulk copies -> producers, 128 arrivals + bytes
+  static constexpr int s_ready = 2 * NS;      // [2 groups][2] MMA -> softmax
+  static constexpr int s_free = 2 * NS + 4;   // [2 groups][2] softmax -> MMA, 128 arrivals
+  static constexpr int o_ready = 2 * NS + 8;  // [2] MMA -> softmax
+  static constexpr int o_free = 2 * NS + 10;  // [2] softmax -> MMA, 128 arrivals
+  static constexpr int p_ready = 2 * NS + 12; // [2] softmax -> MMA, 128 arrivals
+  static constexpr int raw_full = 2 * NS + 14;// [NR] page copies -> producers
+  static constexpr int raw_free = 2 * NS + 14 + NR;  // [NR] producers -> loader, 128 arrivals
 };
 
 __device__ __forceinline__ void named_barrier(int id, int count) {
@@ -146,11 +150,11 @@ __device__ __forceinline__ void row_target(const KernelParams& p, const RowTile&
   *head = kvh * p.group + n % p.group;
 }
 
-template <int NPAD, int PD, int NS, int NR>
+template <int NPAD, int PD, int NS, int NR, int SB>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_constant__ CUtensorMap tmap) {
-  using L = Layout<NPAD, PD, NS, NR>;
-  using B = Bars<NS>;
+  using L = Layout<NPAD, PD, NS, NR, SB>;
+  using B = Bars<NS, NR>;
   constexpr int kRawStages = NR;
   constexpr int XMAX = (1 << (7 * PD)) - 1;
   static_assert(NS >= 2, "two image stages: one feeding the MMAs, one being filled");
@@ -223,13 +227,18 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       tc::mbar_init(&bars[B::empty + s], 1);
     }
     for (int b = 0; b < 2; ++b) {
-      tc::mbar_init(&bars[B::s_ready + b], 1);
-      tc::mbar_init(&bars[B::s_free + b], kGroupThreads);
+      for (int k = 0; k < 2; ++k) {
+        tc::mbar_init(&bars[B::s_ready + 2 * b + k], 1);
+        tc::mbar_init(&bars[B::s_free + 2 * b + k], kGroupThreads);
+      }
       tc::mbar_init(&bars[B::o_ready + b], 1);
       tc::mbar_init(&bars[B::o_free + b], kGroupThreads);
       tc::mbar_init(&bars[B::p_ready + b], kGroupThreads);
     }
-    for (int s = 0; s < kRawStages; ++s) tc::mbar_init(&bars[B::raw_full + s], kKeys >> p.block_shift);
+    for (int s = 0; s < kRawStages; ++s) {
+      tc::mbar_init(&bars[B::raw_full + s], kKeys >> p.block_shift);
+      tc::mbar_init(&bars[B::raw_free + s], kProducerThreads);
+    }
     *abort_flag = 0;
     tc::mbar_init_fence();
   }
@@ -294,55 +303,19 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
   const uint32_t tmem_base = *tslot;
   bool ok = true;
 
-  if (warp >= 8 && warp < kMmaWarp) {
+  if (warp >= 8 && warp < kQkWarp) {
     // =========================== producers ====================================
     const int pt = tid - kSoftmaxThreads;  // key of the tile this thread resolves
-    const int32_t* bt = p.block_table + (int64_t)t.req * p.block_table_row_stride;
-    const uint8_t* kb = p.k.data + (int64_t)kvh * p.k.stride_head;
-    // The raw bytes of a tile arrive PAGE BY PAGE through TMA: one copy per KV page and head,
-    // issued by lane `page` of the first producer warp, completing on the stage's mbarrier.
-    //   raw_mode 1 (slot stride a multiple of 16, e.g. NHD with several heads): a tiled
-    //     tensor-map copy of a [block_size slots] x [272 bytes] box whose inner start is the
-    //     cell address rounded down to 16 bytes;
-    //   raw_mode 2 (cells of a page contiguous: HND, or one KV head): a plain bulk copy of the
-    //     run, again from the 16-byte boundary below it.
-    // TMA writes shared memory directly (no L1 staging) and a handful of 4 KB copies per tile
-    // keeps tens of KB in flight per SM.  When a raw tile has landed, producer thread t moves
-    // the words of key t into the operand images: with delta = (cell address mod 16) in {0, 8},
-    // word w of K block j is raw word delta / 4 + 4 j + w, of V block j raw word
-    // delta / 4 + 33 + 4 j + w; the scales are raw words delta / 4 + 32 and + 65.
+    // The raw bytes of a tile are brought in by the loader warp (below), page by page; when a
+    // raw tile has landed, producer thread t moves the words of key t into the operand
+    // images: with delta = (cell address mod 16) in {0, 8}, word w of K block j is raw word
+    // delta / 4 + 4 j + w, of V block j raw word delta / 4 + 33 + 4 j + w; the scales are raw
+    // words delta / 4 + 32 and + 65.
     STAT_DECL
     const int bs = p.block_size;
-    const int pages_per_tile = kKeys >> p.block_shift;
+    const uint8_t* kb = p.k.data + (int64_t)kvh * p.k.stride_head;
     const uint32_t delta = (uint32_t)(reinterpret_cast<uintptr_t>(kb) & 15);
     const int row_pitch = p.raw_mode == 1 ? kRawRow : 2 * kHeadDimI8 + 8;
-    // inner coordinate (4-byte elements) of this head's box: the tensor map starts at the
-    // 16-byte boundary below head 0's first cell
-    const int tma_x = (int)((reinterpret_cast<uintptr_t>(kb) - delta -
-                             (reinterpret_cast<uintptr_t>(p.k.data) & ~(uintptr_t)15)) >> 2);
-    const uint32_t raw_s = tc::smem_u32(smem + L::raw);
-    auto issue_raw = [&](int tile) {
-      if (pt < pages_per_tile) {
-        uint64_t* bar = &bars[B::raw_full + tile % kRawStages];
-        const int pos0 = (tile_begin + tile) * kKeys + pt * bs;  // first key of this page
-        if (pos0 < range_end && pos0 + bs > range_begin) {
-          const int blk = __ldg(bt + (pos0 >> p.block_shift));
-          const uint32_t dst = raw_s + (tile % kRawStages) * kRawStageBytes + pt * bs * kRawRow;
-          if (p.raw_mode == 1) {
-            mbar_arrive_expect_tx(bar, bs * kRawRow);
-            tma_load_3d(dst, &tmap, tma_x, 0, blk, bar);
-          } else {
-            const uint8_t* src = kb + (int64_t)blk * p.k.stride_block - delta;
-            const uint32_t bytes = (delta + bs * (2 * kHeadDimI8 + 8) + 15u) & ~15u;
-            mbar_arrive_expect_tx(bar, bytes);
-            bulk_copy_g2s(dst, src, bytes, bar);
-          }
-        } else {
-          mbar_arrive(bar);
-        }
-      }
-    };
-    for (int s = 0; s < kRawStages && s < n_tiles; ++s) issue_raw(s);
     const int my_page = pt >> p.block_shift, my_slot = pt & (bs - 1);
     const uint32_t cell_off = my_page * bs * kRawRow + my_slot * row_pitch + delta;  // inside a raw stage
     const bool odd = (cell_off & 8u) != 0;
@@ -352,6 +325,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       const int pos = (tile_begin + j) * kKeys + pt;
       const bool valid = pos >= range_begin && pos < range_end;
       STAT_WAIT(2, ok &= wait_or_abort(&bars[B::raw_full + rs], (j / kRawStages) & 1, abort_flag))
+      STAT_T(tP0_)
       uint32_t w[kRawRow / 4];
       if (valid) {
         const uint4* row = reinterpret_cast<const uint4*>(smem + L::raw + rs * kRawStageBytes + (cell_off & ~15u));
@@ -367,12 +341,13 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
 #pragma unroll
         for (int c = 0; c < kRawRow / 4; ++c) w[c] = 0u;
       }
-      // every producer has its row in registers: the stage can be refilled
-      tc::fence_async_smem();
-      named_barrier(3, kProducerThreads);
-      if (j + kRawStages < n_tiles) issue_raw(j + kRawStages);
+      STAT_ADD(3, clock64() - tP0_)
+      // this thread's row is in registers (the arrive orders the loads before it): once all
+      // 128 producers have arrived the loader may refill the raw stage
+      mbar_arrive(&bars[B::raw_free + rs]);
       const int st = j % NS;
       if (j >= NS) STAT_WAIT(0, ok &= wait_or_abort(&bars[B::empty + st], ((j / NS) - 1) & 1, abort_flag))
+      STAT_T(tP4_)
       uint8_t* stage = smem + L::stages + st * kStageBytes;
       uint8_t* krow = stage + pt * 16;
       uint8_t* vrow = stage + kImgBytes + pt * 16;
@@ -396,40 +371,102 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
         *reinterpret_cast<uint32_t*>(stage + 2 * kImgBytes + pt * 4) = w[34];
         *reinterpret_cast<uint32_t*>(stage + 2 * kImgBytes + kKeys * 4 + pt * 4) = w[67];
       }
+      STAT_ADD(7, clock64() - tP4_)
+      STAT_T(tP5_)
       tc::fence_async_smem();
       mbar_arrive(&bars[B::full + st]);
+      STAT_ADD(8, clock64() - tP5_)
     }
     if (pt == 0) { STAT_FLUSH(0) }
-  } else if (warp == kMmaWarp) {
-    // =========================== MMA issuer ===================================
-    // Tile i belongs to softmax group g = i & 1 and uses that group's TMEM buffers
-    // (S^T g, O^T g) and P image g.  Order of issue: QK(0), QK(1), then PV(i), QK(i + 2).
+  } else if (warp == kLoadWarp) {
+    // =========================== loader =======================================
+    // The raw bytes of a tile arrive PAGE BY PAGE through TMA: one copy per KV page and head,
+    // issued by lane `page` of this warp, completing on the raw stage's mbarrier.
+    //   raw_mode 1 (slot stride a multiple of 16, e.g. NHD with several heads): a tiled
+    //     tensor-map copy of a [block_size slots] x [272 bytes] box whose inner start is the
+    //     cell address rounded down to 16 bytes;
+    //   raw_mode 2 (cells of a page contiguous: HND, or one KV head): a plain bulk copy of the
+    //     run, again from the 16-byte boundary below it.
+    // TMA writes shared memory directly (no L1 staging) and a handful of 4 KB copies per tile
+    // keeps tens of KB in flight per SM.  The block id of the next tile's page is fetched
+    // before waiting for the raw stage, so the block-table latency is off the refill path.
+    const int pages_per_tile = kKeys >> p.block_shift;
+    if (lane < pages_per_tile) {
+      const int bs = p.block_size;
+      const int32_t* bt = p.block_table + (int64_t)t.req * p.block_table_row_stride;
+      const uint8_t* kb = p.k.data + (int64_t)kvh * p.k.stride_head;
+      const uint32_t delta = (uint32_t)(reinterpret_cast<uintptr_t>(kb) & 15);
+      // inner coordinate (4-byte elements) of this head's box: the tensor map starts at the
+      // 16-byte boundary below head 0's first cell
+      const int tma_x = (int)((reinterpret_cast<uintptr_t>(kb) - delta -
+                               (reinterpret_cast<uintptr_t>(p.k.data) & ~(uintptr_t)15)) >> 2);
+      const uint32_t raw_s = tc::smem_u32(smem + L::raw);
+      // block id of this lane's page of a tile, -1 if no key of the page is in range
+      auto page_block = [&](int tile) -> int {
+        const int pos0 = (tile_begin + tile) * kKeys + lane * bs;
+        if (tile >= n_tiles || pos0 >= range_end || pos0 + bs <= range_begin) return -1;
+        return __ldg(bt + (pos0 >> p.block_shift));
+      };
+      int blk = page_block(0);
+#pragma unroll 1
+      for (int j = 0; j < n_tiles; ++j) {
+        const int blk_next = page_block(j + 1);
+        const int rs = j % kRawStages;
+        if (j >= kRawStages) ok &= wait_or_abort(&bars[B::raw_free + rs], ((j / kRawStages) - 1) & 1, abort_flag);
+        uint64_t* bar = &bars[B::raw_full + rs];
+        if (blk >= 0 && ok) {
+          const uint32_t dst = raw_s + rs * kRawStageBytes + lane * bs * kRawRow;
+          if (p.raw_mode == 1) {
+            mbar_arrive_expect_tx(bar, bs * kRawRow);
+            tma_load_3d(dst, &tmap, tma_x, 0, blk, bar);
+          } else {
+            const uint8_t* src = kb + (int64_t)blk * p.k.stride_block - delta;
+            const uint32_t bytes = (delta + bs * (2 * kHeadDimI8 + 8) + 15u) & ~15u;
+            mbar_arrive_expect_tx(bar, bytes);
+            bulk_copy_g2s(dst, src, bytes, bar);
+          }
+        } else {
+          mbar_arrive(bar);
+        }
+        blk = blk_next;
+      }
+    }
+  } else if (warp == kQkWarp) {
+    // =========================== QK issuer ====================================
+    // Tile i belongs to softmax group g = i & 1; it is that group's k-th tile (k = i >> 1)
+    // and its S^T lands in the group's buffer k % SB.  This thread runs ahead of the softmax
+    // as far as the image stages and the S^T buffers allow.
     if (lane == 0) {
       STAT_DECL
-      const uint32_t qimg_s = tc::smem_u32(qimg), pimg_s = tc::smem_u32(pimg);
-      auto issue_qk = [&](int i) {
-        const int g = i & 1;
+      const uint32_t qimg_s = tc::smem_u32(qimg);
+#pragma unroll 1
+      for (int i = 0; i < n_tiles; ++i) {
+        const int g = i & 1, k = i >> 1, sb = k % SB;
         STAT_WAIT(0, ok &= wait_or_abort(&bars[B::full + i % NS], (i / NS) & 1, abort_flag))
-        if (i >= 2) STAT_WAIT(1, ok &= wait_or_abort(&bars[B::s_free + g], ((i >> 1) - 1) & 1, abort_flag))
+        if (k >= SB) STAT_WAIT(1, ok &= wait_or_abort(&bars[B::s_free + 2 * g + sb], ((k / SB) - 1) & 1, abort_flag))
         tc::fence_after_sync();
-        issue_qk_i8<NPAD>(tmem_base + g * L::s_cols, stage0 + (i % NS) * kStageBytes, qimg_s);
-        tc::mma_commit(&bars[B::s_ready + g]);
-      };
-      issue_qk(0);
-      if (n_tiles > 1) issue_qk(1);
+        issue_qk_i8<NPAD>(tmem_base + (g * SB + sb) * L::s_cols, stage0 + (i % NS) * kStageBytes, qimg_s);
+        tc::mma_commit(&bars[B::s_ready + 2 * g + sb]);
+      }
+      STAT_FLUSH(1)
+    }
+  } else if (warp == kPvWarp) {
+    // =========================== PV issuer ====================================
+    // O^T of tile i goes to its group's TMEM buffer; its completion also frees the image
+    // stage (the QK of the same tile finished before the softmax could produce P).
+    if (lane == 0) {
+      const uint32_t pimg_s = tc::smem_u32(pimg);
 #pragma unroll 1
       for (int i = 0; i < n_tiles; ++i) {
         const int g = i & 1;
-        STAT_WAIT(2, ok &= wait_or_abort(&bars[B::p_ready + g], (i >> 1) & 1, abort_flag))
-        if (i >= 2) STAT_WAIT(3, ok &= wait_or_abort(&bars[B::o_free + g], ((i >> 1) - 1) & 1, abort_flag))
+        ok &= wait_or_abort(&bars[B::p_ready + g], (i >> 1) & 1, abort_flag);
+        if (i >= 2) ok &= wait_or_abort(&bars[B::o_free + g], ((i >> 1) - 1) & 1, abort_flag);
         tc::fence_after_sync();
-        issue_pv_i8<NPAD, PD>(tmem_base + 2 * L::s_cols + g * L::o_cols, stage0 + (i % NS) * kStageBytes + kImgBytes,
+        issue_pv_i8<NPAD, PD>(tmem_base + L::s_total + g * L::o_cols, stage0 + (i % NS) * kStageBytes + kImgBytes,
                               pimg_s + g * (PD * NPAD * kKeys));
         tc::mma_commit(&bars[B::o_ready + g]);
         tc::mma_commit(&bars[B::empty + i % NS]);
-        if (i + 2 < n_tiles) issue_qk(i + 2);
       }
-      STAT_FLUSH(1)
     }
   } else if (warp < 2 * 4) {
     // =========================== softmax ======================================
@@ -462,7 +499,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     auto fold_o = [&](int j) {
       STAT_WAIT(1, ok &= wait_or_abort(&bars[B::o_ready + g], (j >> 1) & 1, abort_flag))
       tc::fence_after_sync();
-      const uint32_t o_tmem = tmem_base + 2 * L::s_cols + g * L::o_cols + lane_addr;
+      const uint32_t o_tmem = tmem_base + L::s_total + g * L::o_cols + lane_addr;
 #pragma unroll
       for (int q4 = 0; q4 < NPAD / 4; ++q4) {
         if (q4 * 4 < rows) {
@@ -490,11 +527,13 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       const int b = it & 1;
       float* wred_i = wred_g + b * 4 * (NPAD + 1);
       const uint8_t* scales = smem + L::stages + (i % NS) * kStageBytes + 2 * kImgBytes;
-      STAT_WAIT(0, ok &= wait_or_abort(&bars[B::s_ready + g], it & 1, abort_flag))
+      const int sb = it % SB;
+      STAT_WAIT(0, ok &= wait_or_abort(&bars[B::s_ready + 2 * g + sb], (it / SB) & 1, abort_flag))
       tc::fence_after_sync();
+      STAT_T(tS0_)
       const float ks_cur = reinterpret_cast<const float*>(scales)[gt];
       const float vs_cur = reinterpret_cast<const float*>(scales)[kKeys + gt];
-      const uint32_t s_tmem = tmem_base + g * L::s_cols + lane_addr;
+      const uint32_t s_tmem = tmem_base + (g * SB + sb) * L::s_cols + lane_addr;
       const int pos = (tile_begin + i) * kKeys + gt;
       const bool interior = (tile_begin + i) * kKeys >= mask_lo && (tile_begin + i) * kKeys + (kKeys - 1) <= mask_hi;
       const float mult = ks_cur * p.scale_log2;
@@ -517,15 +556,21 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
           }
         }
       }
+      STAT_ADD(3, clock64() - tS0_)
+      STAT_T(tS1_)
       tc::fence_before_sync();
-      mbar_arrive(&bars[B::s_free + g]);  // S^T buffer g may be overwritten by the QK of tile i + 2
+      mbar_arrive(&bars[B::s_free + 2 * g + sb]);  // this S^T buffer may be overwritten by a later QK
       {
         const int key = __reduce_max_sync(0xffffffffu, float_key(vs_cur));
         if (lane == 0) wred_i[gw * (NPAD + 1) + NPAD] = key_float(key);
       }
       // O^T of this group's previous tile; afterwards its P image is free.
+      STAT_ADD(4, clock64() - tS1_)
+      STAT_T(tS2_)
       if (it > 0) fold_o(i - 2);
-      STAT_WAIT(2, named_barrier(1 + g, kGroupThreads))  // per-warp maxima visible; alpha / unit consumed
+      STAT_ADD(5, clock64() - tS2_)
+      STAT_WAIT(2, named_barrier(1 + g, kGroupThreads))
+      STAT_T(tS3_)  // per-warp maxima visible; alpha / unit consumed
       const float* mrun_i = mrun_g + b * NPAD;
       const float vs_max = fmaxf(fmaxf(wred_i[NPAD], wred_i[(NPAD + 1) + NPAD]),
                                  fmaxf(wred_i[2 * (NPAD + 1) + NPAD], wred_i[3 * (NPAD + 1) + NPAD]));
@@ -534,28 +579,34 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
         if (q16 * 16 < rows) {
           uint32_t dig[PD][4] = {};
 #pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const int n = q16 * 16 + e;
-            if (n < rows) {
-              const float m_old = mrun_i[n];
-              const float m_tile = fmaxf(fmaxf(wred_i[n], wred_i[(NPAD + 1) + n]),
-                                         fmaxf(wred_i[2 * (NPAD + 1) + n], wred_i[3 * (NPAD + 1) + n]));
-              const float m_new = fmaxf(m_old, m_tile);
-              const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-              const float a = fast_exp2(m_old - m_use);
-              const float pr = fast_exp2(s[n] - m_use);
-              l_part[n] = fmaf(l_part[n], a, pr);
-              // largest p * v_scale of the tile bounds the fixed-point range
-              const float bound = vs_max * fast_exp2(m_tile - m_use);
-              const float inv_u = bound > 0.f ? (float)XMAX * __frcp_rn(bound) : 0.f;
-              int x = __float2int_rn(pr * vs_cur * inv_u);
-              x = min(x, XMAX);
+          for (int q4 = 0; q4 < 4; ++q4) {
+            // Whole groups of four rows, padded rows included (their scores are finite
+            // and their columns of O^T are never read): no branch per row, so the four
+            // dependency chains overlap.
+            if (q16 * 16 + q4 * 4 < rows) {
 #pragma unroll
-              for (int k = 0; k < PD; ++k) dig[k][e >> 2] |= (uint32_t)((x >> (7 * k)) & 127) << (8 * (e & 3));
-              if (gt == n) {
-                alpha_g[n] = a;
-                unit_g[n] = bound * (1.0f / (float)XMAX);
-                mrun_g[(b ^ 1) * NPAD + n] = m_new;
+              for (int e = 0; e < 4; ++e) {
+                const int n = q16 * 16 + q4 * 4 + e;
+                const float m_old = mrun_i[n];
+                const float m_tile = fmaxf(fmaxf(wred_i[n], wred_i[(NPAD + 1) + n]),
+                                           fmaxf(wred_i[2 * (NPAD + 1) + n], wred_i[3 * (NPAD + 1) + n]));
+                const float m_new = fmaxf(m_old, m_tile);
+                const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+                const float a = fast_exp2(m_old - m_use);
+                const float pr = fast_exp2(s[n] - m_use);
+                l_part[n] = fmaf(l_part[n], a, pr);
+                // largest p * v_scale of the tile bounds the fixed-point range
+                const float bound = vs_max * fast_exp2(m_tile - m_use);
+                const float inv_u = bound > 0.f ? __fdividef((float)XMAX, bound) : 0.f;
+                int x = __float2int_rn(pr * vs_cur * inv_u);
+                x = min(x, XMAX);
+#pragma unroll
+                for (int k = 0; k < PD; ++k) dig[k][q4] |= (uint32_t)((x >> (7 * k)) & 127) << (8 * e);
+                if (gt == n) {
+                  alpha_g[n] = a;
+                  unit_g[n] = bound * (1.0f / (float)XMAX);
+                  mrun_g[(b ^ 1) * NPAD + n] = m_new;
+                }
               }
             }
           }
@@ -565,8 +616,11 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
                 make_uint4(dig[k][0], dig[k][1], dig[k][2], dig[k][3]);
         }
       }
+      STAT_ADD(6, clock64() - tS3_)
+      STAT_T(tS4_)
       tc::fence_async_smem();
       mbar_arrive(&bars[B::p_ready + g]);  // P image, alpha, unit of tile i complete
+      STAT_ADD(7, clock64() - tS4_)
     }
     if (it > 0) fold_o(g + 2 * (it - 1));
     if (gt == 0) { STAT_FLUSH(2) }
@@ -683,20 +737,20 @@ int raw_mode_for(const KernelParams& p) {
   return 0;
 }
 
-template <int NPAD, int PD, int NS, int NR>
+template <int NPAD, int PD, int NS, int NR, int SB>
 cudaError_t launch_cfg(const KernelParams& p, const CUtensorMap& map, cudaStream_t stream) {
-  constexpr int smem = Layout<NPAD, PD, NS, NR>::total;
+  constexpr int smem = Layout<NPAD, PD, NS, NR, SB>::total;
   static bool configured[64] = {};
   int dev = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return err;
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    err = cudaFuncSetAttribute(umma_i8_attention_kernel<NPAD, PD, NS, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    err = cudaFuncSetAttribute(umma_i8_attention_kernel<NPAD, PD, NS, NR, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (err != cudaSuccess) return err;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   const dim3 grid(p.num_q_tiles, p.num_kv_heads, p.num_splits);
-  umma_i8_attention_kernel<NPAD, PD, NS, NR><<<grid, kThreads, smem, stream>>>(p, map);
+  umma_i8_attention_kernel<NPAD, PD, NS, NR, SB><<<grid, kThreads, smem, stream>>>(p, map);
   return cudaGetLastError();
 }
 
@@ -736,10 +790,16 @@ cudaError_t launch_umma_i8_attention(const KernelParams& p_in, cudaStream_t stre
   CUtensorMap map{};
   if (p.raw_mode == 1 && !make_page_map(p, p.num_blocks, &map)) return cudaErrorInvalidValue;
   const int rows = p.bq * p.group;
-  if (rows <= 16) return launch_cfg<16, 3, 3, 3>(p, map, stream);
-  if (rows <= 32) return launch_cfg<32, 2, 3, 2>(p, map, stream);
-  return launch_cfg<64, 2, 2, 2>(p, map, stream);
+  if (rows <= 16) return launch_cfg<16, 3, 4, 2, 2>(p, map, stream);
+  if (rows <= 32) return launch_cfg<32, 2, 3, 2, 1>(p, map, stream);
+  return launch_cfg<64, 2, 2, 2, 1>(p, map, stream);
 }
+
+#ifdef PTHB200_WAIT_STATS
+extern "C" int pthb200_debug_wait_stats(long long* out) {
+  return cudaMemcpyFromSymbol(out, g_wait_stats, sizeof(long long) * 36) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 // Reads and clears the integer kernel's status word (device must be idle).
 cudaError_t read_i8_status(unsigned int* v) {
