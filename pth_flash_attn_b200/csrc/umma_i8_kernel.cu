@@ -44,11 +44,14 @@ namespace pthb200 {
 __device__ unsigned int g_i8_status = 0;
 #ifdef PTHB200_WAIT_STATS
 // Debug build only: cycles that one thread of each role of CTA (0,0,0) spent in each wait.
-__device__ long long g_wait_stats[3][12];
+__device__ long long g_wait_stats[4][12];
 #define STAT_DECL long long st_[12] = {0}; const long long st_begin_ = clock64();
 #define STAT_WAIT(slot, expr) { const long long t0_ = clock64(); expr; st_[slot] += clock64() - t0_; }
 #define STAT_ADD(slot, v) st_[slot] += (v);
 #define STAT_T(name) const long long name = clock64();
+#define STAT_ENTRY const long long k_entry_ = clock64(); unsigned long long k_ns_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(k_ns_));
+#define STAT_MARK(slot) if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) g_wait_stats[3][slot] = clock64() - k_entry_;
+#define STAT_EXIT if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { unsigned long long e_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(e_)); g_wait_stats[3][10] = (long long)(e_ - k_ns_); }
 #define STAT_FLUSH(role) if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { st_[11] = clock64() - st_begin_; for (int q_ = 0; q_ < 12; ++q_) g_wait_stats[role][q_] = st_[q_]; }
 #else
 #define STAT_DECL
@@ -56,6 +59,9 @@ __device__ long long g_wait_stats[3][12];
 #define STAT_ADD(slot, v)
 #define STAT_T(name)
 #define STAT_FLUSH(role)
+#define STAT_ENTRY
+#define STAT_MARK(slot)
+#define STAT_EXIT
 #endif
 
 namespace {
@@ -68,25 +74,24 @@ constexpr int kPvWarp = 13;                             // lane 0 issues the O^T
 constexpr int kLoadWarp = 14;                           // issues the page copies
 constexpr int kThreads = kSoftmaxThreads + kProducerThreads + 96;
 constexpr int kStageScales = 2 * kKeys * 4;                 // k_scale[128], v_scale[128]
-constexpr int kStageBytes = 2 * kImgBytes + kStageScales;   // 34,048 B
+constexpr int kVStageBytes = kImgBytes + kStageScales;      // V image and both scale vectors of one tile
 constexpr int kRawRow = 272;                                // aligned bytes that cover a 264-byte cell
 constexpr int kRawStageBytes = kKeys * kRawRow;             // 34,816 B
 
-template <int NPAD, int PD, int NS, int NR, int SB>
+template <int NPAD, int PD, int NS, int NK, int NR, int SB>
 struct Layout {
-  static constexpr int stages = 0;
-  static constexpr int qimg = stages + NS * kStageBytes;            // [8][2 NPAD][16]
+  static constexpr int kstages = 0;                                 // [NK] K images
+  static constexpr int vstages = kstages + NK * kImgBytes;          // [NS] V image + scales
+  static constexpr int qimg = vstages + NS * kVStageBytes;          // [8][2 NPAD][16]
   static constexpr int pimg = qimg + 8 * 2 * NPAD * 16;             // [2 groups][PD NPAD / 16][128][16]
   static constexpr int raw = pimg + 2 * PD * NPAD * kKeys;          // [NR][128][272] raw cells
   static constexpr int wred = raw + NR * kRawStageBytes;                            // float [2 groups][2][4][NPAD + 1]
-  static constexpr int mrun = wred + 2 * 2 * 4 * (NPAD + 1) * 4;    // float [2 groups][2][NPAD]
-  static constexpr int alpha = mrun + 2 * 2 * NPAD * 4;             // float [2 groups][NPAD]
-  static constexpr int unit = alpha + 2 * NPAD * 4;                 // float [2 groups][NPAD]
-  static constexpr int sq = unit + 2 * NPAD * 4;                    // float [NPAD]
+  static constexpr int mrun = wred + 2 * 2 * 4 * (NPAD + 1) * 4;    // float [2 groups][2 NPAD], first NPAD used
+  static constexpr int sq = mrun + 2 * 2 * NPAD * 4;                // float [NPAD]
   static constexpr int rlo = sq + NPAD * 4;                         // int [NPAD]
   static constexpr int rhi = rlo + NPAD * 4;                        // int [NPAD]
   static constexpr int bars = (rhi + NPAD * 4 + 7) / 8 * 8;         // uint64 [2 NS + 10 + NR]
-  static constexpr int misc = bars + (2 * NS + 14 + 2 * NR) * 8;    // abort flag, TMEM slot
+  static constexpr int misc = bars + (2 * NS + NK + 14 + 2 * NR) * 8;    // abort flag, TMEM slot
   static constexpr int total = misc + 16;
   static constexpr int s_cols = 2 * NPAD;
   static constexpr int o_cols = PD * NPAD;
@@ -97,10 +102,10 @@ struct Layout {
 };
 
 // Barrier indices inside the barrier array.
-template <int NS, int NR>
+template <int NS, int NK, int NR>
 struct Bars {
   static constexpr int full = 0;             // [NS] producers -> MMA, 128 arrivals
-  static constexpr int empty = NS;           // [NS] MMA (tcgen05.commit) -> producers
+  static constexpr int empty = NS;           // [NS] PV issuer (tcgen05.commit) -> producers: V stage free
   static constexpr int s_ready = 2 * NS;      // [2 groups][2] MMA -> softmax
   static constexpr int s_free = 2 * NS + 4;   // [2 groups][2] softmax -> MMA, 128 arrivals
   static constexpr int o_ready = 2 * NS + 8;  // [2] MMA -> softmax
@@ -108,6 +113,7 @@ struct Bars {
   static constexpr int p_ready = 2 * NS + 12; // [2] softmax -> MMA, 128 arrivals
   static constexpr int raw_full = 2 * NS + 14;// [NR] page copies -> producers
   static constexpr int raw_free = 2 * NS + 14 + NR;  // [NR] producers -> loader, 128 arrivals
+  static constexpr int kempty = 2 * NS + 14 + 2 * NR; // [NK] QK issuer (tcgen05.commit) -> producers
 };
 
 __device__ __forceinline__ void named_barrier(int id, int count) {
@@ -150,21 +156,20 @@ __device__ __forceinline__ void row_target(const KernelParams& p, const RowTile&
   *head = kvh * p.group + n % p.group;
 }
 
-template <int NPAD, int PD, int NS, int NR, int SB>
+template <int NPAD, int PD, int NS, int NK, int NR, int SB>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_constant__ CUtensorMap tmap) {
-  using L = Layout<NPAD, PD, NS, NR, SB>;
-  using B = Bars<NS, NR>;
+  using L = Layout<NPAD, PD, NS, NK, NR, SB>;
+  using B = Bars<NS, NK, NR>;
   constexpr int kRawStages = NR;
   constexpr int XMAX = (1 << (7 * PD)) - 1;
   static_assert(NS >= 2, "two image stages: one feeding the MMAs, one being filled");
+  STAT_ENTRY
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* qimg = smem + L::qimg;
   uint8_t* pimg = smem + L::pimg;
   float* wred = reinterpret_cast<float*>(smem + L::wred);
   float* mrun = reinterpret_cast<float*>(smem + L::mrun);
-  float* alpha_s = reinterpret_cast<float*>(smem + L::alpha);
-  float* unit_s = reinterpret_cast<float*>(smem + L::unit);
   float* sq = reinterpret_cast<float*>(smem + L::sq);
   int* rlo = reinterpret_cast<int*>(smem + L::rlo);
   int* rhi = reinterpret_cast<int*>(smem + L::rhi);
@@ -210,8 +215,9 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     return;
   }
 
+  STAT_MARK(0)
   const int n_tiles = tile_end - tile_begin;
-  const uint32_t stage0 = tc::smem_u32(smem + L::stages);
+  const uint32_t kstage0 = tc::smem_u32(smem + L::kstages), vstage0 = tc::smem_u32(smem + L::vstages);
 
   // ---- set-up by all threads -------------------------------------------------
   if (tid < NPAD) {
@@ -226,6 +232,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       tc::mbar_init(&bars[B::full + s], kProducerThreads);
       tc::mbar_init(&bars[B::empty + s], 1);
     }
+    for (int s = 0; s < NK; ++s) tc::mbar_init(&bars[B::kempty + s], 1);
     for (int b = 0; b < 2; ++b) {
       for (int k = 0; k < 2; ++k) {
         tc::mbar_init(&bars[B::s_ready + 2 * b + k], 1);
@@ -302,6 +309,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
   tc::fence_after_sync();
   const uint32_t tmem_base = *tslot;
   bool ok = true;
+  STAT_MARK(1)
 
   if (warp >= 8 && warp < kQkWarp) {
     // =========================== producers ====================================
@@ -347,10 +355,11 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       mbar_arrive(&bars[B::raw_free + rs]);
       const int st = j % NS;
       if (j >= NS) STAT_WAIT(0, ok &= wait_or_abort(&bars[B::empty + st], ((j / NS) - 1) & 1, abort_flag))
+      if (j >= NK) STAT_WAIT(1, ok &= wait_or_abort(&bars[B::kempty + j % NK], ((j / NK) - 1) & 1, abort_flag))
       STAT_T(tP4_)
-      uint8_t* stage = smem + L::stages + st * kStageBytes;
-      uint8_t* krow = stage + pt * 16;
-      uint8_t* vrow = stage + kImgBytes + pt * 16;
+      uint8_t* stage = smem + L::vstages + st * kVStageBytes;  // V image, then the scales
+      uint8_t* krow = smem + L::kstages + (j % NK) * kImgBytes + pt * 16;
+      uint8_t* vrow = stage + pt * 16;
       if (!odd) {
 #pragma unroll
         for (int b = 0; b < 8; ++b) {
@@ -358,8 +367,8 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
           *reinterpret_cast<uint4*>(vrow + b * kImgChunk) =
               make_uint4(w[33 + 4 * b], w[34 + 4 * b], w[35 + 4 * b], w[36 + 4 * b]);
         }
-        *reinterpret_cast<uint32_t*>(stage + 2 * kImgBytes + pt * 4) = w[32];
-        *reinterpret_cast<uint32_t*>(stage + 2 * kImgBytes + kKeys * 4 + pt * 4) = w[65];
+        *reinterpret_cast<uint32_t*>(stage + kImgBytes + pt * 4) = w[32];
+        *reinterpret_cast<uint32_t*>(stage + kImgBytes + kKeys * 4 + pt * 4) = w[65];
       } else {
 #pragma unroll
         for (int b = 0; b < 8; ++b) {
@@ -368,8 +377,8 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
           *reinterpret_cast<uint4*>(vrow + b * kImgChunk) =
               make_uint4(w[35 + 4 * b], w[36 + 4 * b], w[37 + 4 * b], w[38 + 4 * b]);
         }
-        *reinterpret_cast<uint32_t*>(stage + 2 * kImgBytes + pt * 4) = w[34];
-        *reinterpret_cast<uint32_t*>(stage + 2 * kImgBytes + kKeys * 4 + pt * 4) = w[67];
+        *reinterpret_cast<uint32_t*>(stage + kImgBytes + pt * 4) = w[34];
+        *reinterpret_cast<uint32_t*>(stage + kImgBytes + kKeys * 4 + pt * 4) = w[67];
       }
       STAT_ADD(7, clock64() - tP4_)
       STAT_T(tP5_)
@@ -445,8 +454,9 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
         STAT_WAIT(0, ok &= wait_or_abort(&bars[B::full + i % NS], (i / NS) & 1, abort_flag))
         if (k >= SB) STAT_WAIT(1, ok &= wait_or_abort(&bars[B::s_free + 2 * g + sb], ((k / SB) - 1) & 1, abort_flag))
         tc::fence_after_sync();
-        issue_qk_i8<NPAD>(tmem_base + (g * SB + sb) * L::s_cols, stage0 + (i % NS) * kStageBytes, qimg_s);
+        issue_qk_i8<NPAD>(tmem_base + (g * SB + sb) * L::s_cols, kstage0 + (i % NK) * kImgBytes, qimg_s);
         tc::mma_commit(&bars[B::s_ready + 2 * g + sb]);
+        tc::mma_commit(&bars[B::kempty + i % NK]);  // the K image is dead once S^T exists
       }
       STAT_FLUSH(1)
     }
@@ -462,7 +472,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
         ok &= wait_or_abort(&bars[B::p_ready + g], (i >> 1) & 1, abort_flag);
         if (i >= 2) ok &= wait_or_abort(&bars[B::o_free + g], ((i >> 1) - 1) & 1, abort_flag);
         tc::fence_after_sync();
-        issue_pv_i8<NPAD, PD>(tmem_base + L::s_total + g * L::o_cols, stage0 + (i % NS) * kStageBytes + kImgBytes,
+        issue_pv_i8<NPAD, PD>(tmem_base + L::s_total + g * L::o_cols, vstage0 + (i % NS) * kVStageBytes,
                               pimg_s + g * (PD * NPAD * kKeys));
         tc::mma_commit(&bars[B::o_ready + g]);
         tc::mma_commit(&bars[B::empty + i % NS]);
@@ -481,8 +491,6 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     uint8_t* pimg_g = pimg + g * (PD * NPAD * kKeys);
     float* wred_g = wred + g * (2 * 4 * (NPAD + 1));   // [2][4][NPAD + 1]
     float* mrun_g = mrun + g * (2 * NPAD);             // [2][NPAD]
-    float* alpha_g = alpha_s + g * NPAD;
-    float* unit_g = unit_s + g * NPAD;
     int mask_lo, mask_hi, tmp;  // key positions every live row sees: such tiles need no mask
     visible_range(p, t, t.first_idx + t.ntok - 1, &mask_lo, &tmp);
     visible_range(p, t, t.first_idx, &tmp, &mask_hi);
@@ -494,8 +502,22 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       acc[n] = 0.f;
       l_part[n] = 0.f;
     }
+    // Per-row softmax state lives in LANES, not in shared memory: lane l of every warp holds,
+    // for row l + 32 j, the running maximum and the factors of the latest tile (every warp
+    // computes the same values), and the row loops fetch them with warp shuffles.
+    constexpr int RL = (NPAD + 31) / 32;
+    float m_run[RL], a_l[RL], unit_l[RL], muse_l[RL], invu_l[RL];
+#pragma unroll
+    for (int j = 0; j < RL; ++j) {
+      m_run[j] = -INFINITY;
+      a_l[j] = 0.f;
+      unit_l[j] = 0.f;
+      muse_l[j] = 0.f;
+      invu_l[j] = 0.f;
+    }
 
-    // Folds O^T of tile j (this group's TMEM buffer) into the register accumulator.
+    // Folds O^T of tile j (this group's TMEM buffer) into the register accumulator, with the
+    // rescale factor and digit unit of that tile (still in a_l / unit_l).
     auto fold_o = [&](int j) {
       STAT_WAIT(1, ok &= wait_or_abort(&bars[B::o_ready + g], (j >> 1) & 1, abort_flag))
       tc::fence_after_sync();
@@ -510,10 +532,12 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int n = q4 * 4 + e;
+            const float alpha_n = __shfl_sync(0xffffffffu, a_l[n >> 5], n & 31);
+            const float unit_n = __shfl_sync(0xffffffffu, unit_l[n >> 5], n & 31);
             float o = int_to_float(d[PD - 1][e]);
 #pragma unroll
             for (int k = PD - 2; k >= 0; --k) o = fmaf(o, 128.f, int_to_float(d[k][e]));
-            acc[n] = fmaf(acc[n], alpha_g[n], o * unit_g[n]);
+            acc[n] = fmaf(acc[n], alpha_n, o * unit_n);
           }
         }
       }
@@ -526,7 +550,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     for (int i = g; i < n_tiles; i += 2, ++it) {
       const int b = it & 1;
       float* wred_i = wred_g + b * 4 * (NPAD + 1);
-      const uint8_t* scales = smem + L::stages + (i % NS) * kStageBytes + 2 * kImgBytes;
+      const uint8_t* scales = smem + L::vstages + (i % NS) * kVStageBytes + kImgBytes;
       const int sb = it % SB;
       STAT_WAIT(0, ok &= wait_or_abort(&bars[B::s_ready + 2 * g + sb], (it / SB) & 1, abort_flag))
       tc::fence_after_sync();
@@ -538,6 +562,9 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       const bool interior = (tile_begin + i) * kKeys >= mask_lo && (tile_begin + i) * kKeys + (kKeys - 1) <= mask_hi;
       const float mult = ks_cur * p.scale_log2;
       float s[NPAD];
+      int mykey[RL];  // warp maximum of row lane + 32 j, as an ordered integer key
+#pragma unroll
+      for (int j = 0; j < RL; ++j) mykey[j] = float_key(-INFINITY);
 #pragma unroll
       for (int q4 = 0; q4 < NPAD / 4; ++q4) {
         if (q4 * 4 < rows) {
@@ -552,10 +579,13 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
             const bool vis = interior || (pos >= rlo[n] && pos <= rhi[n]);
             s[n] = vis ? sv : -INFINITY;
             const int key = __reduce_max_sync(0xffffffffu, float_key(s[n]));
-            if (lane == (n & 31)) wred_i[gw * (NPAD + 1) + n] = key_float(key);
+            if (lane == (n & 31)) mykey[n >> 5] = key;
           }
         }
       }
+#pragma unroll
+      for (int j = 0; j < RL; ++j)
+        if (lane + 32 * j < NPAD) wred_i[gw * (NPAD + 1) + lane + 32 * j] = key_float(mykey[j]);
       STAT_ADD(3, clock64() - tS0_)
       STAT_T(tS1_)
       tc::fence_before_sync();
@@ -570,10 +600,25 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       if (it > 0) fold_o(i - 2);
       STAT_ADD(5, clock64() - tS2_)
       STAT_WAIT(2, named_barrier(1 + g, kGroupThreads))
-      STAT_T(tS3_)  // per-warp maxima visible; alpha / unit consumed
-      const float* mrun_i = mrun_g + b * NPAD;
+      STAT_T(tS3_)  // per-warp maxima of the tile visible to the whole group
       const float vs_max = fmaxf(fmaxf(wred_i[NPAD], wred_i[(NPAD + 1) + NPAD]),
                                  fmaxf(wred_i[2 * (NPAD + 1) + NPAD], wred_i[3 * (NPAD + 1) + NPAD]));
+#pragma unroll
+      for (int j = 0; j < RL; ++j) {
+        const int r = (lane + 32 * j) & (NPAD - 1);
+        const float m_tile = fmaxf(fmaxf(wred_i[r], wred_i[(NPAD + 1) + r]),
+                                   fmaxf(wred_i[2 * (NPAD + 1) + r], wred_i[3 * (NPAD + 1) + r]));
+        const float m_old = m_run[j];
+        const float m_new = fmaxf(m_old, m_tile);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        a_l[j] = fast_exp2(m_old - m_use);
+        // largest p * v_scale of the tile bounds the fixed-point range of its digits
+        const float bound = vs_max * fast_exp2(m_tile - m_use);
+        invu_l[j] = bound > 0.f ? __fdividef((float)XMAX, bound) : 0.f;
+        unit_l[j] = bound * (1.0f / (float)XMAX);
+        muse_l[j] = m_use;
+        m_run[j] = m_new;
+      }
 #pragma unroll
       for (int q16 = 0; q16 < NPAD / 16; ++q16) {
         if (q16 * 16 < rows) {
@@ -587,26 +632,15 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const int n = q16 * 16 + q4 * 4 + e;
-                const float m_old = mrun_i[n];
-                const float m_tile = fmaxf(fmaxf(wred_i[n], wred_i[(NPAD + 1) + n]),
-                                           fmaxf(wred_i[2 * (NPAD + 1) + n], wred_i[3 * (NPAD + 1) + n]));
-                const float m_new = fmaxf(m_old, m_tile);
-                const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-                const float a = fast_exp2(m_old - m_use);
+                const float m_use = __shfl_sync(0xffffffffu, muse_l[n >> 5], n & 31);
+                const float a = __shfl_sync(0xffffffffu, a_l[n >> 5], n & 31);
+                const float inv_u = __shfl_sync(0xffffffffu, invu_l[n >> 5], n & 31);
                 const float pr = fast_exp2(s[n] - m_use);
                 l_part[n] = fmaf(l_part[n], a, pr);
-                // largest p * v_scale of the tile bounds the fixed-point range
-                const float bound = vs_max * fast_exp2(m_tile - m_use);
-                const float inv_u = bound > 0.f ? __fdividef((float)XMAX, bound) : 0.f;
                 int x = __float2int_rn(pr * vs_cur * inv_u);
                 x = min(x, XMAX);
 #pragma unroll
                 for (int k = 0; k < PD; ++k) dig[k][q4] |= (uint32_t)((x >> (7 * k)) & 127) << (8 * e);
-                if (gt == n) {
-                  alpha_g[n] = a;
-                  unit_g[n] = bound * (1.0f / (float)XMAX);
-                  mrun_g[(b ^ 1) * NPAD + n] = m_new;
-                }
               }
             }
           }
@@ -619,15 +653,21 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       STAT_ADD(6, clock64() - tS3_)
       STAT_T(tS4_)
       tc::fence_async_smem();
-      mbar_arrive(&bars[B::p_ready + g]);  // P image, alpha, unit of tile i complete
+      mbar_arrive(&bars[B::p_ready + g]);  // P image of tile i complete
       STAT_ADD(7, clock64() - tS4_)
     }
     if (it > 0) fold_o(g + 2 * (it - 1));
     if (gt == 0) { STAT_FLUSH(2) }
+    STAT_MARK(2)
 
     // ---- epilogue: reduce the row sums inside the group, merge the two groups ----
     named_barrier(1 + g, kGroupThreads);
     float* wsum = wred_g;  // [4][NPAD + 1]
+    if (gw == 0) {
+#pragma unroll
+      for (int j = 0; j < RL; ++j)
+        if (lane + 32 * j < NPAD) mrun_g[lane + 32 * j] = m_run[j];
+    }
 #pragma unroll
     for (int n = 0; n < NPAD; ++n) {
       if (n < rows) {
@@ -650,8 +690,8 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     if (g == 0) {
       const float* w0 = wred;
       const float* w1 = wred + 2 * 4 * (NPAD + 1);
-      const float* m0p = mrun + (it & 1) * NPAD;                                   // group 0 ran `it` tiles
-      const float* m1p = mrun + 2 * NPAD + ((n_tiles >> 1) & 1) * NPAD;            // group 1 ran n_tiles / 2
+      const float* m0p = mrun;             // running maxima published by the two groups
+      const float* m1p = mrun + 2 * NPAD;
 #pragma unroll
       for (int n = 0; n < NPAD; ++n) {
         if (n < rows) {
@@ -688,8 +728,11 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     }
   }
 
+  STAT_MARK(3)
   tc::fence_before_sync();
   __syncthreads();
+  STAT_MARK(4)
+  STAT_EXIT
   if (warp == 0) tc::tmem_dealloc(tmem_base, L::tmem_alloc);
   if (tid == 0 && *abort_flag) atomicOr(&g_i8_status, 4u);
   (void)ok;
@@ -737,20 +780,22 @@ int raw_mode_for(const KernelParams& p) {
   return 0;
 }
 
-template <int NPAD, int PD, int NS, int NR, int SB>
+template <int NPAD, int PD, int NS, int NK, int NR, int SB>
 cudaError_t launch_cfg(const KernelParams& p, const CUtensorMap& map, cudaStream_t stream) {
-  constexpr int smem = Layout<NPAD, PD, NS, NR, SB>::total;
+  constexpr int smem = Layout<NPAD, PD, NS, NK, NR, SB>::total;
+  static_assert(smem <= 227 * 1024, "shared memory of one CTA");
+  static_assert(Layout<NPAD, PD, NS, NK, NR, SB>::tmem_need <= 512, "TMEM columns");
   static bool configured[64] = {};
   int dev = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return err;
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    err = cudaFuncSetAttribute(umma_i8_attention_kernel<NPAD, PD, NS, NR, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    err = cudaFuncSetAttribute(umma_i8_attention_kernel<NPAD, PD, NS, NK, NR, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (err != cudaSuccess) return err;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   const dim3 grid(p.num_q_tiles, p.num_kv_heads, p.num_splits);
-  umma_i8_attention_kernel<NPAD, PD, NS, NR, SB><<<grid, kThreads, smem, stream>>>(p, map);
+  umma_i8_attention_kernel<NPAD, PD, NS, NK, NR, SB><<<grid, kThreads, smem, stream>>>(p, map);
   return cudaGetLastError();
 }
 
@@ -790,14 +835,14 @@ cudaError_t launch_umma_i8_attention(const KernelParams& p_in, cudaStream_t stre
   CUtensorMap map{};
   if (p.raw_mode == 1 && !make_page_map(p, p.num_blocks, &map)) return cudaErrorInvalidValue;
   const int rows = p.bq * p.group;
-  if (rows <= 16) return launch_cfg<16, 3, 4, 2, 2>(p, map, stream);
-  if (rows <= 32) return launch_cfg<32, 2, 3, 2, 1>(p, map, stream);
-  return launch_cfg<64, 2, 2, 2, 1>(p, map, stream);
+  if (rows <= 16) return launch_cfg<16, 3, 4, 2, 3, 2>(p, map, stream);
+  if (rows <= 32) return launch_cfg<32, 2, 3, 2, 3, 1>(p, map, stream);
+  return launch_cfg<64, 2, 3, 2, 2, 1>(p, map, stream);
 }
 
 #ifdef PTHB200_WAIT_STATS
 extern "C" int pthb200_debug_wait_stats(long long* out) {
-  return cudaMemcpyFromSymbol(out, g_wait_stats, sizeof(long long) * 36) == cudaSuccess ? 0 : -1;
+  return cudaMemcpyFromSymbol(out, g_wait_stats, sizeof(long long) * 48) == cudaSuccess ? 0 : -1;
 }
 #endif
 
