@@ -208,7 +208,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -219,7 +219,7 @@ class ClockSampler:
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) >= 6:
-                self.rows.append(parts)
+                self.rows.append((time.monotonic(), parts))
 
     def __exit__(self, *exc):
         if self.proc is not None:
@@ -229,10 +229,19 @@ class ClockSampler:
             except subprocess.TimeoutExpired:
                 self.proc.kill()
 
-    def summary(self):
+    def summary(self, t0=None, t1=None):
+        """Median SM clock and the throttle reasons seen.  With (t0, t1) only the samples
+        taken inside that host-time window count, if there are at least three of them; a
+        shorter timed region falls back to every sample taken while the GPU was under the
+        benchmark's load (warm-up, timed steps, end-to-end and per-kernel passes)."""
+        rows, window = [r for _, r in self.rows], "whole load phase"
+        if t0 is not None:
+            inside = [r for t, r in self.rows if t0 <= t <= t1]
+            if len(inside) >= 3:
+                rows, window = inside, "timed region"
         sm, mx, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for r in self.rows:
+        for r in rows:
             try:
                 sm.append(float(r[0]))
                 mx.append(float(r[1]))
@@ -242,7 +251,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "window": window}
 
 
 # --------------------------------------------------------------------------
@@ -442,11 +451,13 @@ def main():
             ms = float(t.item())
         return ms
 
+    clk = ClockSampler(local_rank)
+    clk.__enter__()
     for i in range(max(args.warmup, 3)):
         run_step(i)
-    with ClockSampler(local_rank) as clk:
-        ms_total = timed(run_step, args.steps)
-    clocks = clk.summary()
+    t_begin = time.monotonic()
+    ms_total = timed(run_step, args.steps)
+    t_end = time.monotonic()
     ms_per_step = ms_total / args.steps
     value = step_bytes_total / (ms_per_step * 1e-3) / 1e9
 
@@ -474,6 +485,8 @@ def main():
             evs.append((a, b))
     torch.cuda.synchronize()
     attn_ms = sum(a.elapsed_time(b) for a, b in evs) / reps  # all attention launches of one step
+    clk.__exit__()
+    clocks = clk.summary(t_begin, t_end)
     peaks_path = REPO / "MEASURED_PEAKS.json"
     if peaks_path.is_file():
         peaks, peak_src = json.loads(peaks_path.read_text()), "measured"
@@ -490,7 +503,7 @@ def main():
         roof = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                 "traffic": None}
     roof["peak_source"] = peak_src
-    roof["kernel"] = "umma_attention_kernel"
+    roof["kernel"] = "umma_i8_attention_kernel"
     roof["kernel_ms_per_step"] = attn_ms
     roof["algorithmic_bytes_per_step"] = step_bytes_local
     traffic_file = REPO / "profiles" / "traffic.json"
@@ -506,14 +519,17 @@ def main():
         line = {
             "metric": "kv_read_bandwidth", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "us_per_layer": ms_per_step * 1e3,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 cache, bf16 MMA, fp32 softmax",
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8",
             "data": "synthetic",
             "config": {"workload": args.config, "launches": [
                 {"batch": len(l["seq_lens"]), "context_max": max(l["seq_lens"]), "q_len": max(l["q_lens"]),
                  "window": l.get("window", 0), "num_splits": d.S, "bq": d.bq} for l, d in zip(launches, dls)],
                 "Hq": launches[0]["Hq"], "Hkv": hkv_total, "D": D, "block_size": BS, "sharding": f"kv_heads/{world}",
                 "l2_policy": ("inputs larger than L2" if sets == 1 else f"rotation over {sets} cache sets (>= 4x L2)"),
-                "cuda_graph": bool(graphs), "kv_bytes_per_step": step_bytes_total, "flops_per_step": step_flops_total},
+                "cuda_graph": bool(graphs),
+                "arithmetic": "int8 cache bytes and int8 digits of Q / P on tcgen05 kind::i8, int32 accumulators, "
+                              "fp32 softmax and output accumulation",
+                "kv_bytes_per_step": step_bytes_total, "flops_per_step": step_flops_total},
             "tflops": step_flops_total / (ms_per_step * 1e-3) / 1e12,
             "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": sum(d.h2d for d in dls), "d2h_bytes_per_step": sum(d.d2h for d in dls)},

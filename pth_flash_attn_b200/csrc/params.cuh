@@ -68,17 +68,20 @@ struct RowTile {
 // Row tile x of the grid: request r owns tiles [qsl[r]/bq + r, ... + ceil(q_len/bq)).
 // The start index is strictly increasing in r, so the owner is found by
 // bisection; tiles that fall between two requests are surplus (req = -1).
-__device__ __forceinline__ RowTile resolve_row_tile(const KernelParams& p, int x) {
+// `qsl(i)` reads query_start_loc[i] and `len(r)` seq_lens[r] (from global memory, or from
+// copies of them).
+template <class LoadQsl, class LoadLen>
+__device__ __forceinline__ RowTile resolve_row_tile_with(const KernelParams& p, int x, LoadQsl qsl, LoadLen len) {
   RowTile t;
   t.req = -1;
   int lo = 0, hi = p.num_reqs - 1;
   while (lo < hi) {
     const int mid = (lo + hi + 1) >> 1;
-    const int first = __ldg(p.query_start_loc + mid) / p.bq + mid;
+    const int first = qsl(mid) / p.bq + mid;
     if (first <= x) lo = mid; else hi = mid - 1;
   }
-  const int q0 = __ldg(p.query_start_loc + lo);
-  const int q1 = __ldg(p.query_start_loc + lo + 1);
+  const int q0 = qsl(lo);
+  const int q1 = qsl(lo + 1);
   const int j = x - (q0 / p.bq + lo);
   const int q_len = q1 - q0;
   if (j < 0 || j * p.bq >= q_len) return t;
@@ -87,8 +90,13 @@ __device__ __forceinline__ RowTile resolve_row_tile(const KernelParams& p, int x
   t.tok0 = q0 + t.first_idx;
   t.ntok = min(p.bq, q_len - t.first_idx);
   t.q_len = q_len;
-  t.seq_len = __ldg(p.seq_lens + lo);
+  t.seq_len = len(lo);
   return t;
+}
+
+__device__ __forceinline__ RowTile resolve_row_tile(const KernelParams& p, int x) {
+  return resolve_row_tile_with(
+      p, x, [&](int i) { return __ldg(p.query_start_loc + i); }, [&](int r) { return __ldg(p.seq_lens + r); });
 }
 
 // Inclusive visible key range of the query token with index i inside its

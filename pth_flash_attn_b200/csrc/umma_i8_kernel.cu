@@ -177,10 +177,27 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::misc);
   uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + L::misc + 8);
 
-  const RowTile t = resolve_row_tile(p, blockIdx.x);
-  if (t.req < 0) return;
   const int kvh = blockIdx.y, split = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // Row tile of this CTA.  The bisection over query_start_loc is a chain of dependent
+  // loads: when the arrays fit, the CTA first copies them (and seq_lens) into still unused
+  // shared memory with one round of coalesced loads and bisects there.
+  constexpr int kQslCache = 4096;
+  RowTile t;
+  if (p.num_reqs + 1 <= kQslCache) {
+    int* qsl_s = reinterpret_cast<int*>(smem + L::raw);
+    int* len_s = qsl_s + kQslCache;
+    for (int i = tid; i <= p.num_reqs; i += kThreads) {
+      qsl_s[i] = __ldg(p.query_start_loc + i);
+      if (i < p.num_reqs) len_s[i] = __ldg(p.seq_lens + i);
+    }
+    __syncthreads();
+    t = resolve_row_tile_with(p, blockIdx.x, [&](int i) { return qsl_s[i]; }, [&](int r) { return len_s[r]; });
+    __syncthreads();  // the copy is dead: the raw ring may be filled
+  } else {
+    t = resolve_row_tile(p, blockIdx.x);
+  }
+  if (t.req < 0) return;
   const int rows = t.ntok * p.group;  // <= NPAD by construction of bq
   int tile_begin, tile_end, range_begin, range_end;
   split_tiles(p, t, split, &tile_begin, &tile_end, &range_begin, &range_end);
@@ -220,13 +237,6 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
   const uint32_t kstage0 = tc::smem_u32(smem + L::kstages), vstage0 = tc::smem_u32(smem + L::vstages);
 
   // ---- set-up by all threads -------------------------------------------------
-  if (tid < NPAD) {
-    int lo = 0, hi = -1;
-    if (tid < rows) visible_range(p, t, t.first_idx + tid / p.group, &lo, &hi);
-    rlo[tid] = lo;
-    rhi[tid] = hi;
-    for (int k = 0; k < 4; ++k) mrun[k * NPAD + tid] = -INFINITY;
-  }
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
       tc::mbar_init(&bars[B::full + s], kProducerThreads);
@@ -253,56 +263,6 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     tc::tmem_alloc(tslot, L::tmem_alloc);
     tc::tmem_relinquish();
   }
-  // Q digits: 8 threads per row, 16 elements each (threads 0..127, 16 rows per pass).
-  if (tid < 128) {
-    for (int base = 0; base < NPAD; base += 16) {
-      const int n = base + (tid >> 3), part = tid & 7;
-      float v[16];
-      if (n < rows) {
-        int token, head;
-        row_target(p, t, kvh, n, &token, &head);
-        const uint4* src = reinterpret_cast<const uint4*>(p.q + (int64_t)token * p.q_stride_token +
-                                                          (int64_t)head * p.q_stride_head + part * 32);
-        const uint4 a = src[0], b = src[1];
-        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          v[2 * e] = __uint_as_float(w[e] << 16);
-          v[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
-        }
-      } else {
-#pragma unroll
-        for (int e = 0; e < 16; ++e) v[e] = 0.f;
-      }
-      float amax = 0.f;
-#pragma unroll
-      for (int e = 0; e < 16; ++e) amax = fmaxf(amax, fabsf(v[e]));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-      const bool finite_row = amax > 0.f && amax < INFINITY;
-      const float inv = finite_row ? 32512.f / amax : 0.f;
-      uint32_t hi_w[4] = {0, 0, 0, 0}, lo_w[4] = {0, 0, 0, 0};
-#pragma unroll
-      for (int e = 0; e < 16; ++e) {
-        int qi = __float2int_rn(v[e] * inv);
-        qi = max(-32512, min(32512, qi));
-        const int qh = (qi + 128) >> 8;
-        const int ql = qi - (qh << 8);
-        hi_w[e >> 2] |= (uint32_t)(qh & 0xff) << (8 * (e & 3));
-        lo_w[e >> 2] |= (uint32_t)(ql & 0xff) << (8 * (e & 3));
-      }
-      // image row of (digit, n) is digit * NPAD + n; 16-byte column block `part`
-      *reinterpret_cast<uint4*>(qimg + part * (2 * NPAD * 16) + n * 16) = make_uint4(hi_w[0], hi_w[1], hi_w[2], hi_w[3]);
-      *reinterpret_cast<uint4*>(qimg + part * (2 * NPAD * 16) + (NPAD + n) * 16) =
-          make_uint4(lo_w[0], lo_w[1], lo_w[2], lo_w[3]);
-      if (part == 0) sq[n] = finite_row ? amax / 32512.f : 0.f;
-    }
-  }
-  // P image: zero once (rows that are not live keep zero digits).
-  for (int i = tid * 16; i < 2 * PD * NPAD * kKeys; i += kThreads * 16)
-    *reinterpret_cast<uint4*>(pimg + i) = make_uint4(0u, 0u, 0u, 0u);
-
   tc::fence_before_sync();
   tc::fence_async_smem();
   __syncthreads();
@@ -445,6 +405,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     // Tile i belongs to softmax group g = i & 1; it is that group's k-th tile (k = i >> 1)
     // and its S^T lands in the group's buffer k % SB.  This thread runs ahead of the softmax
     // as far as the image stages and the S^T buffers allow.
+    named_barrier(5, kSoftmaxThreads + 32);  // wait for the Q image
     if (lane == 0) {
       STAT_DECL
       const uint32_t qimg_s = tc::smem_u32(qimg);
@@ -484,6 +445,63 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     // maximum, sum and accumulator (as if the KV range were split in two inside the CTA);
     // the two states are merged in the epilogue.  Thread t of a group owns key t of S^T and
     // output column d = t of O^T.
+    if (tid < NPAD) {
+      int lo = 0, hi = -1;
+      if (tid < rows) visible_range(p, t, t.first_idx + tid / p.group, &lo, &hi);
+      rlo[tid] = lo;
+      rhi[tid] = hi;
+    }
+    // Q digits: 8 threads per row, 16 elements each (32 rows per pass).  The page copies
+    // and the realignment of the first tiles run meanwhile.
+    {
+      for (int base = 0; base < NPAD; base += 32) {
+        const int n = base + (tid >> 3), part = tid & 7;
+        float v[16];
+        if (n < rows) {
+          int token, head;
+          row_target(p, t, kvh, n, &token, &head);
+          const uint4* src = reinterpret_cast<const uint4*>(p.q + (int64_t)token * p.q_stride_token +
+                                                            (int64_t)head * p.q_stride_head + part * 32);
+          const uint4 a = src[0], b = src[1];
+          const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+  #pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            v[2 * e] = __uint_as_float(w[e] << 16);
+            v[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+          }
+        } else {
+  #pragma unroll
+          for (int e = 0; e < 16; ++e) v[e] = 0.f;
+        }
+        float amax = 0.f;
+  #pragma unroll
+        for (int e = 0; e < 16; ++e) amax = fmaxf(amax, fabsf(v[e]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+        const bool finite_row = amax > 0.f && amax < INFINITY;
+        const float inv = finite_row ? 32512.f / amax : 0.f;
+        uint32_t hi_w[4] = {0, 0, 0, 0}, lo_w[4] = {0, 0, 0, 0};
+  #pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          int qi = __float2int_rn(v[e] * inv);
+          qi = max(-32512, min(32512, qi));
+          const int qh = (qi + 128) >> 8;
+          const int ql = qi - (qh << 8);
+          hi_w[e >> 2] |= (uint32_t)(qh & 0xff) << (8 * (e & 3));
+          lo_w[e >> 2] |= (uint32_t)(ql & 0xff) << (8 * (e & 3));
+        }
+        // image row of (digit, n) is digit * NPAD + n; 16-byte column block `part`
+        if (n < NPAD) {
+        *reinterpret_cast<uint4*>(qimg + part * (2 * NPAD * 16) + n * 16) = make_uint4(hi_w[0], hi_w[1], hi_w[2], hi_w[3]);
+        *reinterpret_cast<uint4*>(qimg + part * (2 * NPAD * 16) + (NPAD + n) * 16) =
+            make_uint4(lo_w[0], lo_w[1], lo_w[2], lo_w[3]);
+        if (part == 0) sq[n] = finite_row ? amax / 32512.f : 0.f;
+        }
+      }
+    }
+    tc::fence_async_smem();
+    named_barrier(5, kSoftmaxThreads + 32);  // Q image, row scales and masks complete; the QK issuer may start
     const int g = warp >> 2;
     const int gt = tid & 127;          // thread index inside the group
     const int gw = warp & 3;           // warp inside the group = TMEM lane quadrant

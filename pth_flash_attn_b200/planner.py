@@ -12,18 +12,23 @@ Same public surface as the reference planner (python/pth_flash_attn/planner.py:
   a CUDA graph captured for its descriptor.
 
 What differs is the machine model.  A row tile of this library holds up to 64
-rows (query heads of one KV head x query tokens), as in the reference, but the
-kernels run three 128-thread CTAs per SM on a 148-SM part and read the cache in
-128-key tiles.  The split count is chosen per launch from the descriptor:
+rows (query heads of one KV head x query tokens), as in the reference, but at
+head size 128 the kernel is one warp-specialised CTA per SM (it keeps about
+220 KB of cache bytes in flight in shared memory) on a 148-SM part and reads
+the cache in 128-key tiles.  The split count is chosen per launch from the
+descriptor:
 
     work items per split = Hkv * row tiles            (row tiles: see below)
-    S = the count in [S_min, 2 S_min] that leaves the fullest last wave,
-        S_min = ceil(WAVES * C_target / items)        (WAVES = 4)
+    S = max(1, C_target // items)
 
-Several waves of work items let the hardware's block scheduler even out
-requests of different length, which the planner cannot see.  ``wm`` keeps its
-meaning of "16 * wm rows per tile" because it is part of the op's frozen
-schema; the kernels pad rows to 16/32/64 accordingly.
+that is: no split once the unsplit work items fill the GPU, otherwise the
+largest count that still fits ONE wave.  Every CTA pays a fixed cost (finding
+its row tile, quantising Q, filling the copy pipeline, merging its two softmax
+groups) worth some tens of KV tiles, and every split adds a partial for the
+combine kernel to read, so more, shorter CTAs than one wave lose more than a
+fuller last wave wins (measured on B200 at 8 K and 128 K keys per request).
+``wm`` keeps its meaning of "16 * wm rows per tile" because it is part of the
+op's frozen schema; the kernels pad rows to 16/32/64 accordingly.
 """
 
 from __future__ import annotations
@@ -34,13 +39,11 @@ ROWS_PER_WM = 16
 WM_CHOICES = (1, 2, 4)
 MAX_ROWS_PER_CTA = ROWS_PER_WM * WM_CHOICES[-1]
 # Resident CTAs per SM of the attention kernels, by head size.
-CTAS_PER_SM = {64: 4, 128: 3, 256: 2}
+CTAS_PER_SM = {64: 4, 128: 1, 256: 2}
 SUPPORTED_HEAD_SIZES = tuple(sorted(CTAS_PER_SM))
 WINDOWED_HEAD_SIZES = (128,)
 KV_TILE_TOKENS = 128
 PARTIAL_BYTES_PER_ELEMENT = 4
-# Waves of work items a launch aims for (see the module docstring).
-TARGET_WAVES = 4
 B200_NUM_SMS = 148
 
 DESCRIPTOR_FIELDS = (
@@ -159,15 +162,8 @@ class LaunchPlan:
 
 
 def _pick_splits(items: int, target: int) -> int:
-    """Split count in [S_min, 2 S_min] whose last wave is fullest (ties: fewer splits)."""
-    s_min = max(1, _ceil_div(TARGET_WAVES * target, items))
-    best, best_fill = s_min, -1.0
-    for s in range(s_min, 2 * s_min + 1):
-        waves = s * items / target
-        fill = waves / _ceil_div(s * items, target)
-        if fill > best_fill + 1e-9:
-            best, best_fill = s, fill
-    return best
+    """Largest split count whose CTAs still fit one wave (1 if the items alone fill it)."""
+    return max(1, target // items)
 
 
 def plan_launch(
@@ -232,17 +228,16 @@ def plan_launch(
 
 
 def s_alone(*, Hkv: int, D: int, num_sms: int) -> int:
-    """Splits that let ONE row tile per KV head occupy TARGET_WAVES waves of the GPU."""
+    """Splits that let ONE row tile per KV head fill one wave of the GPU."""
     hkv = _require_int("Hkv", Hkv, 1)
-    return 2 * _ceil_div(TARGET_WAVES * c_target(D=D, num_sms=num_sms), hkv)
+    return _pick_splits(hkv, c_target(D=D, num_sms=num_sms))
 
 
 def workspace_token_splits(*, max_num_seqs: int, q_dec_max: int, Hkv: int, D: int, num_sms: int) -> int:
     """Token-splits to reserve so that every plan this module makes fits.
 
     A launch of R requests of up to ``q_dec_max`` tokens needs ``S * T`` with
-    ``T <= R * q_dec_max`` and ``S <= 2 ceil(WAVES * C_target / (Hkv * R))``; the
-    product is largest at R = 1 or R = max_num_seqs.
+    ``T <= R * q_dec_max`` and ``S <= max(1, C_target // (Hkv * R))``.
     """
     seqs = _require_int("max_num_seqs", max_num_seqs, 1)
     q_dec = _require_int("q_dec_max", q_dec_max, 1)
@@ -251,8 +246,7 @@ def workspace_token_splits(*, max_num_seqs: int, q_dec_max: int, Hkv: int, D: in
     hkv = _require_int("Hkv", Hkv, 1)
     worst = 0
     for r in range(1, seqs + 1):
-        s = 2 * max(1, _ceil_div(TARGET_WAVES * target, hkv * r))
-        worst = max(worst, min(s, alone) * r * q_dec)
+        worst = max(worst, min(_pick_splits(hkv * r, target), alone) * r * q_dec)
     return worst
 
 

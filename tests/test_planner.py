@@ -62,7 +62,7 @@ def test_plan_is_a_pure_function_of_the_descriptor():
 def test_baseline_shapes():
     # one request at any length must still spread over the machine
     one = _plan(num_tokens=1, num_reqs=1)
-    assert one.wm == 1 and one.bq == 4 and one.num_splits * 8 >= 2 * planner.c_target(D=128, num_sms=148)
+    assert one.wm == 1 and one.bq == 4 and one.num_splits == planner.c_target(D=128, num_sms=148) // 8 == 18
     # a full batch needs few splits
     full = _plan()
     assert 1 <= full.num_splits <= 16
