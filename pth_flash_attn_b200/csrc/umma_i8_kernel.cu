@@ -68,11 +68,10 @@ namespace {
 
 constexpr int kGroupThreads = 128;                      // one softmax warpgroup
 constexpr int kSoftmaxThreads = 2 * kGroupThreads;      // warps 0-3 and 4-7
-constexpr int kProducerThreads = 128;                   // warps 8-11
-constexpr int kQkWarp = 12;                             // lane 0 issues the S^T = K Q^T MMAs
-constexpr int kPvWarp = 13;                             // lane 0 issues the O^T = V^T P MMAs
-constexpr int kLoadWarp = 14;                           // issues the page copies
-constexpr int kThreads = kSoftmaxThreads + kProducerThreads + 96;
+constexpr int kProducerThreads = 128;                   // one producer group: one thread per key of a tile
+// Warps after the softmax groups: NP producer groups of four warps (group k realigns the
+// tiles j with j % NP == k), then the QK issuer, the PV issuer and the loader warp.
+__host__ __device__ constexpr int threads_for(int np) { return kSoftmaxThreads + np * kProducerThreads + 96; }
 constexpr int kStageScales = 2 * kKeys * 4;                 // k_scale[128], v_scale[128]
 constexpr int kVStageBytes = kImgBytes + kStageScales;      // V image and both scale vectors of one tile
 constexpr int kRawRow = 272;                                // aligned bytes that cover a 264-byte cell
@@ -156,13 +155,18 @@ __device__ __forceinline__ void row_target(const KernelParams& p, const RowTile&
   *head = kvh * p.group + n % p.group;
 }
 
-template <int NPAD, int PD, int NS, int NK, int NR, int SB>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int NPAD, int PD, int NS, int NK, int NR, int SB, int RQ, int NP>
+__global__ void __launch_bounds__(threads_for(NP), 1)
 umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_constant__ CUtensorMap tmap) {
   using L = Layout<NPAD, PD, NS, NK, NR, SB>;
   using B = Bars<NS, NK, NR>;
   constexpr int kRawStages = NR;
   constexpr int XMAX = (1 << (7 * PD)) - 1;
+  constexpr int kThreads = threads_for(NP);
+  constexpr int kQkWarp = 8 + 4 * NP;   // lane 0 issues the S^T = K Q^T MMAs
+  constexpr int kPvWarp = kQkWarp + 1;  // lane 0 issues the O^T = V^T P MMAs
+  constexpr int kLoadWarp = kQkWarp + 2;  // issues the page copies
+  static_assert(RQ >= 1 && 4 * RQ <= NPAD, "RQ = groups of four rows the softmax handles (rows <= 4 RQ)");
   static_assert(NS >= 2, "two image stages: one feeding the MMAs, one being filled");
   STAT_ENTRY
   extern __shared__ __align__(128) uint8_t smem[];
@@ -273,7 +277,8 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
 
   if (warp >= 8 && warp < kQkWarp) {
     // =========================== producers ====================================
-    const int pt = tid - kSoftmaxThreads;  // key of the tile this thread resolves
+    const int pgrp = (warp - 8) >> 2;                              // producer group
+    const int pt = (tid - kSoftmaxThreads) & (kProducerThreads - 1);  // key of the tile this thread resolves
     // The raw bytes of a tile are brought in by the loader warp (below), page by page; when a
     // raw tile has landed, producer thread t moves the words of key t into the operand
     // images: with delta = (cell address mod 16) in {0, 8}, word w of K block j is raw word
@@ -288,10 +293,17 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     const uint32_t cell_off = my_page * bs * kRawRow + my_slot * row_pitch + delta;  // inside a raw stage
     const bool odd = (cell_off & 8u) != 0;
 #pragma unroll 1
-    for (int j = 0; j < n_tiles; ++j) {
+    for (int j = pgrp; j < n_tiles; j += NP) {
       const int rs = j % kRawStages;
       const int pos = (tile_begin + j) * kKeys + pt;
       const bool valid = pos >= range_begin && pos < range_end;
+      if constexpr (NP > 1) {
+        // A raw stage is shared by the producer groups in turn (NR is not a multiple of NP).
+        // A parity wait only tells apart two consecutive phases, so this group must not look
+        // at raw_full[rs] while the stage's PREVIOUS tile (another group's) is still pending:
+        // first wait until that tile has been taken out of the stage.
+        if (j >= kRawStages) ok &= wait_or_abort(&bars[B::raw_free + rs], ((j / kRawStages) - 1) & 1, abort_flag);
+      }
       STAT_WAIT(2, ok &= wait_or_abort(&bars[B::raw_full + rs], (j / kRawStages) & 1, abort_flag))
       STAT_T(tP0_)
       uint32_t w[kRawRow / 4];
@@ -346,7 +358,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       mbar_arrive(&bars[B::full + st]);
       STAT_ADD(8, clock64() - tP5_)
     }
-    if (pt == 0) { STAT_FLUSH(0) }
+    if (pt == 0 && pgrp == 0) { STAT_FLUSH(0) }
   } else if (warp == kLoadWarp) {
     // =========================== loader =======================================
     // The raw bytes of a tile arrive PAGE BY PAGE through TMA: one copy per KV page and head,
@@ -514,9 +526,10 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     visible_range(p, t, t.first_idx, &tmp, &mask_hi);
 
     STAT_DECL
-    float acc[NPAD], l_part[NPAD];
+    constexpr int NROW = 4 * RQ;  // rows this instance computes (live rows rounded up to four)
+    float acc[NROW], l_part[NROW];
 #pragma unroll
-    for (int n = 0; n < NPAD; ++n) {
+    for (int n = 0; n < NROW; ++n) {
       acc[n] = 0.f;
       l_part[n] = 0.f;
     }
@@ -541,8 +554,8 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       tc::fence_after_sync();
       const uint32_t o_tmem = tmem_base + L::s_total + g * L::o_cols + lane_addr;
 #pragma unroll
-      for (int q4 = 0; q4 < NPAD / 4; ++q4) {
-        if (q4 * 4 < rows) {
+      for (int q4 = 0; q4 < RQ; ++q4) {
+        {
           uint32_t d[PD][4];
 #pragma unroll
           for (int k = 0; k < PD; ++k) tmem_ld4(o_tmem + k * NPAD + q4 * 4, d[k]);
@@ -579,13 +592,13 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       const int pos = (tile_begin + i) * kKeys + gt;
       const bool interior = (tile_begin + i) * kKeys >= mask_lo && (tile_begin + i) * kKeys + (kKeys - 1) <= mask_hi;
       const float mult = ks_cur * p.scale_log2;
-      float s[NPAD];
+      float s[NROW];
       int mykey[RL];  // warp maximum of row lane + 32 j, as an ordered integer key
 #pragma unroll
       for (int j = 0; j < RL; ++j) mykey[j] = float_key(-INFINITY);
 #pragma unroll
-      for (int q4 = 0; q4 < NPAD / 4; ++q4) {
-        if (q4 * 4 < rows) {
+      for (int q4 = 0; q4 < RQ; ++q4) {
+        {
           uint32_t hi[4], lo[4];
           tmem_ld4(s_tmem + q4 * 4, hi);
           tmem_ld4(s_tmem + NPAD + q4 * 4, lo);
@@ -639,14 +652,14 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       }
 #pragma unroll
       for (int q16 = 0; q16 < NPAD / 16; ++q16) {
-        if (q16 * 16 < rows) {
+        if (q16 * 4 < RQ) {
           uint32_t dig[PD][4] = {};
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
             // Whole groups of four rows, padded rows included (their scores are finite
             // and their columns of O^T are never read): no branch per row, so the four
             // dependency chains overlap.
-            if (q16 * 16 + q4 * 4 < rows) {
+            if (q16 * 4 + q4 < RQ) {
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const int n = q16 * 16 + q4 * 4 + e;
@@ -687,7 +700,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
         if (lane + 32 * j < NPAD) mrun_g[lane + 32 * j] = m_run[j];
     }
 #pragma unroll
-    for (int n = 0; n < NPAD; ++n) {
+    for (int n = 0; n < NROW; ++n) {
       if (n < rows) {
         float v = l_part[n];
 #pragma unroll
@@ -701,7 +714,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     if (g == 1) {
       ok &= wait_or_abort(&bars[B::full + (n_tiles - 1) % NS], ((n_tiles - 1) / NS) & 1, abort_flag);
 #pragma unroll
-      for (int n = 0; n < NPAD; ++n)
+      for (int n = 0; n < NROW; ++n)
         if (n < rows) park[n * kKeys + gt] = acc[n];
     }
     named_barrier(4, 2 * kGroupThreads);  // both groups: sums, maxima and the parked accumulator visible
@@ -711,7 +724,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       const float* m0p = mrun;             // running maxima published by the two groups
       const float* m1p = mrun + 2 * NPAD;
 #pragma unroll
-      for (int n = 0; n < NPAD; ++n) {
+      for (int n = 0; n < NROW; ++n) {
         if (n < rows) {
           const float l0 = w0[n] + w0[(NPAD + 1) + n] + w0[2 * (NPAD + 1) + n] + w0[3 * (NPAD + 1) + n];
           const float l1 = w1[n] + w1[(NPAD + 1) + n] + w1[2 * (NPAD + 1) + n] + w1[3 * (NPAD + 1) + n];
@@ -798,7 +811,7 @@ int raw_mode_for(const KernelParams& p) {
   return 0;
 }
 
-template <int NPAD, int PD, int NS, int NK, int NR, int SB>
+template <int NPAD, int PD, int NS, int NK, int NR, int SB, int RQ, int NP>
 cudaError_t launch_cfg(const KernelParams& p, const CUtensorMap& map, cudaStream_t stream) {
   constexpr int smem = Layout<NPAD, PD, NS, NK, NR, SB>::total;
   static_assert(smem <= 227 * 1024, "shared memory of one CTA");
@@ -808,12 +821,12 @@ cudaError_t launch_cfg(const KernelParams& p, const CUtensorMap& map, cudaStream
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return err;
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    err = cudaFuncSetAttribute(umma_i8_attention_kernel<NPAD, PD, NS, NK, NR, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    err = cudaFuncSetAttribute(umma_i8_attention_kernel<NPAD, PD, NS, NK, NR, SB, RQ, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (err != cudaSuccess) return err;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   const dim3 grid(p.num_q_tiles, p.num_kv_heads, p.num_splits);
-  umma_i8_attention_kernel<NPAD, PD, NS, NK, NR, SB><<<grid, kThreads, smem, stream>>>(p, map);
+  umma_i8_attention_kernel<NPAD, PD, NS, NK, NR, SB, RQ, NP><<<grid, threads_for(NP), smem, stream>>>(p, map);
   return cudaGetLastError();
 }
 
@@ -853,9 +866,14 @@ cudaError_t launch_umma_i8_attention(const KernelParams& p_in, cudaStream_t stre
   CUtensorMap map{};
   if (p.raw_mode == 1 && !make_page_map(p, p.num_blocks, &map)) return cudaErrorInvalidValue;
   const int rows = p.bq * p.group;
-  if (rows <= 16) return launch_cfg<16, 3, 4, 2, 3, 2>(p, map, stream);
-  if (rows <= 32) return launch_cfg<32, 2, 3, 2, 3, 1>(p, map, stream);
-  return launch_cfg<64, 2, 3, 2, 2, 1>(p, map, stream);
+  // Instances by live rows: the softmax code of each handles exactly ceil(rows / 4) row
+  // groups, which keeps the decode loop small enough for the instruction cache.
+  // The decode instance (rows <= 4) needs few registers and runs two producer groups.
+  if (rows <= 4) return launch_cfg<16, 3, 4, 2, 3, 2, 1, 2>(p, map, stream);
+  if (rows <= 8) return launch_cfg<16, 3, 4, 2, 3, 2, 2, 1>(p, map, stream);
+  if (rows <= 16) return launch_cfg<16, 3, 4, 2, 3, 2, 4, 1>(p, map, stream);
+  if (rows <= 32) return launch_cfg<32, 2, 3, 2, 3, 1, 8, 1>(p, map, stream);
+  return launch_cfg<64, 2, 3, 2, 2, 1, 16, 1>(p, map, stream);
 }
 
 #ifdef PTHB200_WAIT_STATS
