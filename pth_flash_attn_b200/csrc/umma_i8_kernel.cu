@@ -2,9 +2,7 @@
 //
 // The cache holds int8 K and V, so both contractions run on the int8 tensor path
 // (tcgen05.mma.kind::i8, int32 accumulators in TMEM) with the cache bytes used AS
-// STORED: the raw bytes of a 128-key tile are copied global -> shared (cp.async,
-// through the block table) straight into the MMA operand images.  Nothing is
-// widened, dequantised or converted on the way.
+// STORED: nothing is widened, dequantised or converted between HBM and the MMA.
 //
 // The two floating-point operands become exact sums of int8 "digits":
 //   Q row n:  q = sq[n] * (256 qh + ql),   qh, ql int8     (sq = absmax / 32512)
@@ -18,19 +16,31 @@
 // (relative 2^-16 of the row maximum) and the 7 PD-bit quantisation of
 // p * v_scale (relative 2^-(7 PD + 1) of the tile maximum).
 //
-// One CTA = one work item (row tile x KV head x split), 288 threads in three roles
-// that meet only through mbarriers:
-//   warps 4-7  producers: thread t resolves key t through the block table, then the
-//              128 threads copy the tile's K rows (8-byte pieces), V rows (4-byte
-//              pieces; V is only 4-byte aligned inside a cache cell) and both
-//              scales into a ring of NS stages, NS - 1 tiles ahead of the consumers;
-//   warp 8     one thread issues the MMAs: QK of tile i + 1 before PV of tile i, so
-//              the tensor pipe never waits for the softmax of the tile it feeds;
-//   warps 0-3  softmax: thread t owns key t of S^T (scores -> running maximum ->
-//              probabilities -> digits of P) and output column d = t of O^T, which
-//              it folds tile by tile into an fp32 register accumulator
-//              (acc = acc * alpha + O^T * u), so TMEM never holds a value that needs
-//              rescaling.
+// One CTA per SM = one work item (row tile x KV head x split).  Its warps have six
+// roles that meet only through mbarriers (tile = 128 consecutive keys):
+//   loader     (1 warp)  lane `page` issues one TMA copy per KV page of a tile - a
+//              [block_size slots] x [272 bytes] box of a tiled tensor map, or a bulk
+//              copy when a page's cells are contiguous - into a ring of NR raw stages;
+//              block ids are fetched one tile ahead;
+//   producers  (NP groups of 4 warps; group k takes the tiles j with j % NP == k)
+//              thread t reads the 272 raw bytes around key t's cell into registers,
+//              releases the raw stage, and writes them 16 bytes at a time into the
+//              canonical (no-swizzle) operand images: K into a ring of NK K images,
+//              V and the two scale vectors into a ring of NS V stages.  A cell is only
+//              8-byte aligned and V starts 132 bytes into it, which is why the bytes
+//              pass through registers once;
+//   QK issuer  (1 thread) S^T of tile i into one of SB buffers per softmax group, as far
+//              ahead of the softmax as the images and buffers allow; its commit also
+//              frees the K image;
+//   PV issuer  (1 thread) O^T of tile i once its P image is complete; its commit also
+//              frees the V stage;
+//   softmax    (2 groups of 4 warps; group g owns the tiles with i % 2 == g and its own
+//              running maximum, sum and accumulator) thread t owns key t of S^T
+//              (scores -> tile maximum -> probabilities -> digits of P) and output
+//              column d = t of O^T, which it folds tile by tile into an fp32 register
+//              accumulator (acc = acc * alpha + O^T * u), so TMEM never holds a value
+//              that needs rescaling.  Per-row factors live in lanes and travel by
+//              shuffle.  The two groups' states are merged in the epilogue.
 // Every mbarrier wait is bounded: a wait that gives up raises a CTA-wide abort
 // flag (all later waits return at once), sets bit 2 of the status word, and the
 // CTA still finishes and frees its TMEM.
