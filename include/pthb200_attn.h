@@ -195,6 +195,28 @@ int32_t pthb200_combine(const PthAttnCombineArgs* args, void* stream);
 int32_t pthb200_combine_ex(const PthAttnCombineArgs* args, const PthB200Options* options,
                            void* stream);
 
+/* Attention + combine in one call that performs NO allocation: the split partials
+ * live in a fixed 8 MiB array inside this library (a __device__ array of the loaded
+ * module, one instance per GPU) instead of a caller workspace; args->ws_o / ws_lse
+ * and their strides are ignored.  It has no counterpart in the reference, whose op
+ * always takes the workspace from its caller.  It is for callers that have no way
+ * to obtain device memory at the point of the call: an engine that has handed all
+ * free memory to its KV-cache pool after profiling and forbids allocation inside
+ * forward (the reference's backend must reserve its workspace up front for this
+ * reason), or a binding in a language with no route to the framework's allocator.
+ * Limits and rules:
+ *   - num_splits * num_tokens * num_q_heads * (head_size + 1) * 4 bytes (o rounded up
+ *     to 256 bytes) must fit 8 MiB, else PTH_ATTN_EINVAL with both numbers in the
+ *     message; with num_splits == 1 the array is not used;
+ *   - the first call on a device looks the array up (cudaGetSymbolAddress, which may
+ *     load the module there): make that call before any stream capture; later calls
+ *     only launch kernels;
+ *   - every call on a device uses the same array, so calls whose kernels can overlap
+ *     (two streams, or unordered host threads) race on it: keep them on one stream or
+ *     order them yourself.  Nothing in the array needs clearing between calls.
+ * Results are those of pthb200_attention + pthb200_combine with a dense workspace. */
+int32_t pthb200_attention_noalloc(const PthAttnArgs* args, void* stream);
+
 /* Host-only helpers of the op layer (no device access).
  * pthb200_tile_tokens: query tokens per row tile for a launch planned with `wm`
  * (1, 2 or 4), group size G and host bound max_query_len; returns -1 if wm is

@@ -124,6 +124,7 @@ EXPORTED_SYMBOLS = (
     "pthb200_attention_ex",
     "pthb200_combine",
     "pthb200_combine_ex",
+    "pthb200_attention_noalloc",
     "pthb200_tile_tokens",
     "pthb200_check_call",
     "pthb200_launch_count",
@@ -162,6 +163,8 @@ class B200Lib:
         lib.pthb200_attention.argtypes = [ap, ctypes.c_void_p]
         lib.pthb200_attention_ex.restype = ctypes.c_int32
         lib.pthb200_attention_ex.argtypes = [ap, op, ctypes.c_void_p]
+        lib.pthb200_attention_noalloc.restype = ctypes.c_int32
+        lib.pthb200_attention_noalloc.argtypes = [ap, ctypes.c_void_p]
         lib.pthb200_combine.restype = ctypes.c_int32
         lib.pthb200_combine.argtypes = [cp, ctypes.c_void_p]
         lib.pthb200_combine_ex.restype = ctypes.c_int32
@@ -200,6 +203,10 @@ class B200Lib:
             return int(self.lib.pthb200_attention(ctypes.byref(args), stream or None))
         return int(self.lib.pthb200_attention_ex(ctypes.byref(args), ctypes.byref(options),
                                                  stream or None))
+
+    def attention_noalloc(self, args: PthAttnArgs, *, stream: int = 0) -> int:
+        """Attention + combine with the split partials in the library's built-in array."""
+        return int(self.lib.pthb200_attention_noalloc(ctypes.byref(args), stream or None))
 
     def combine(self, args: PthAttnCombineArgs, *, options: PthB200Options | None = None,
                 stream: int = 0) -> int:

@@ -314,3 +314,111 @@ int32_t pthb200_launch_count(const PthAttnArgs* args, int32_t* attention_kernels
 }
 
 }  // extern "C"
+
+// ---- split attention without a caller workspace ---------------------------------
+//
+// pthb200_attention_noalloc runs attention + combine like the two calls above, but keeps
+// the split partials in a fixed array inside this library instead of a workspace the
+// caller allocated.  The array belongs to the loaded module (one instance per device),
+// so the call performs no allocation of any kind.
+//
+// Nothing in the array has to start at zero: every partial (o and log-sum-exp) that the
+// combine of a call reads is written by the attention launch of the same call, including
+// the "-inf, no keys" marker of an empty split, so stale bytes of an earlier call are
+// never read.  All calls on a device share the one array: two calls whose kernels may
+// overlap (different streams, or different host threads without ordering between them)
+// race on it.
+
+#include <mutex>
+
+// Capacity of the built-in array: split partials of one call, o and lse, fp32.
+#define PTHB200_BUILTIN_WS_BYTES (8u * 1024u * 1024u)
+static __device__ __align__(256) unsigned char g_pthb200_builtin_ws[PTHB200_BUILTIN_WS_BYTES];
+
+namespace pthb200 {
+namespace {
+
+constexpr int kMaxDevices = 64;
+std::mutex g_builtin_ws_mutex;
+unsigned char* g_builtin_ws_ptr[kMaxDevices] = {};
+
+// Device address of the array on the CURRENT device.  Looked up once per device (the
+// lookup may load the module on that device, which is why a first call belongs before
+// any stream capture); later calls only read the cached pointer.
+int32_t builtin_ws(unsigned char** out) {
+  int dev = -1;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return fail(PTH_ATTN_ECUDA, std::string("cudaGetDevice failed: ") + cudaGetErrorString(err));
+  PTHB_REQUIRE(dev >= 0 && dev < kMaxDevices, "pthb200_attention_noalloc: device ordinal out of range");
+  std::lock_guard<std::mutex> lock(g_builtin_ws_mutex);
+  if (g_builtin_ws_ptr[dev] == nullptr) {
+    unsigned char* ptr = nullptr;
+    err = cudaGetSymbolAddress((void**)&ptr, g_pthb200_builtin_ws);
+    if (err != cudaSuccess || ptr == nullptr) {
+      return fail(PTH_ATTN_ECUDA, std::string("pthb200_attention_noalloc: cudaGetSymbolAddress failed: ") +
+                                      cudaGetErrorString(err));
+    }
+    g_builtin_ws_ptr[dev] = ptr;
+  }
+  *out = g_builtin_ws_ptr[dev];
+  return PTH_ATTN_OK;
+}
+
+}  // namespace
+}  // namespace pthb200
+
+extern "C" int32_t pthb200_attention_noalloc(const PthAttnArgs* args, void* stream) {
+  using namespace pthb200;
+  g_last_error.clear();
+  PTHB_REQUIRE(args != nullptr, "args is NULL");
+  PTHB_REQUIRE(args->abi_version == PTH_ATTN_ABI_VERSION, "args.abi_version does not match the library");
+  PTHB_REQUIRE(args->struct_bytes == (int32_t)sizeof(PthAttnArgs), "args.struct_bytes != sizeof(PthAttnArgs)");
+  if (args->num_splits <= 1) return attention_impl(args, nullptr, stream, true);  // no partials at all
+  PTHB_REQUIRE(args->num_tokens >= 1 && args->num_q_heads >= 1 && is_head_size(args->head_size),
+               "num_tokens and num_q_heads must be >= 1 and head_size 64, 128 or 256");
+  // dense partials: o [S][T][Hq][D] fp32, then lse [S][T][Hq] fp32 at the next 256-byte boundary
+  const int64_t rows = (int64_t)args->num_splits * args->num_tokens * args->num_q_heads;
+  const int64_t o_bytes = (rows * args->head_size * 4 + 255) / 256 * 256;
+  const int64_t need = o_bytes + rows * 4;
+  if (need > (int64_t)PTHB200_BUILTIN_WS_BYTES) {
+    return fail(PTH_ATTN_EINVAL,
+                "pthb200_attention_noalloc: the split partials of this call need " + std::to_string(need) +
+                    " bytes (num_splits * num_tokens * num_q_heads * (head_size + 1) * 4), the built-in array holds " +
+                    std::to_string((int64_t)PTHB200_BUILTIN_WS_BYTES) +
+                    "; use fewer splits, or pthb200_attention with a workspace of your own");
+  }
+  unsigned char* ws = nullptr;
+  if (int32_t rc = builtin_ws(&ws)) return rc;
+  PthAttnArgs a = *args;
+  a.ws_o = reinterpret_cast<float*>(ws);
+  a.ws_o_stride_head = (int64_t)a.head_size * 4;
+  a.ws_o_stride_token = a.ws_o_stride_head * a.num_q_heads;
+  a.ws_o_stride_split = a.ws_o_stride_token * a.num_tokens;
+  a.ws_lse = reinterpret_cast<float*>(ws + o_bytes);
+  a.ws_lse_stride_head = 4;
+  a.ws_lse_stride_token = (int64_t)4 * a.num_q_heads;
+  a.ws_lse_stride_split = a.ws_lse_stride_token * a.num_tokens;
+  if (int32_t rc = attention_impl(&a, nullptr, stream, true)) return rc;
+  PthAttnCombineArgs c{};
+  c.abi_version = PTH_ATTN_ABI_VERSION;
+  c.struct_bytes = (int32_t)sizeof(PthAttnCombineArgs);
+  c.ws_o = a.ws_o;
+  c.ws_o_stride_split = a.ws_o_stride_split;
+  c.ws_o_stride_token = a.ws_o_stride_token;
+  c.ws_o_stride_head = a.ws_o_stride_head;
+  c.ws_lse = a.ws_lse;
+  c.ws_lse_stride_split = a.ws_lse_stride_split;
+  c.ws_lse_stride_token = a.ws_lse_stride_token;
+  c.ws_lse_stride_head = a.ws_lse_stride_head;
+  c.out = a.out;
+  c.out_dtype = a.out_dtype;
+  c.out_stride_token = a.out_stride_token;
+  c.out_stride_head = a.out_stride_head;
+  c.query_start_loc = a.query_start_loc;
+  c.num_reqs = a.num_reqs;
+  c.num_tokens = a.num_tokens;
+  c.num_q_heads = a.num_q_heads;
+  c.head_size = a.head_size;
+  c.num_splits = a.num_splits;
+  return combine_impl(&c, nullptr, stream);
+}
