@@ -198,7 +198,7 @@ class DeviceLaunch:
 # clocks
 # --------------------------------------------------------------------------
 # Measured with ncu on the batch-64 decode launch (see profiles/).
-DRAM_BYTES_PER_ALGORITHMIC_BYTE = 1.22
+DRAM_BYTES_PER_ALGORITHMIC_BYTE = 1.23
 
 
 class ClockSampler:
@@ -356,7 +356,7 @@ def reference_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--config", default="long_decode")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
