@@ -249,6 +249,11 @@ int32_t pthb200_test_tile(const void* k, const void* q, const void* v, const voi
  * o_out int32 [128][48]. */
 int32_t pthb200_test_tile_i8(const void* k, const void* q, const void* v, const void* pm,
                              int32_t* s_out, int32_t* o_out, void* stream);
+/* The row-major counterpart (query rows on the MMA M dimension): k, v int8 [128][128];
+ * q bf16 [128 rows][128]; pm bf16 [128 rows][128 keys], handed to the MMA through
+ * TMEM; s_out fp32 [128 rows][128 keys] = q k^T, o_out fp32 [128 rows][128] = pm v. */
+int32_t pthb200_test_tile_rows(const void* k, const void* q, const void* v, const void* pm,
+                               float* s_out, float* o_out, void* stream);
 /* Synchronises the device, returns and clears the status word in which a
  * kernel records a bounded wait that gave up (0 = none). */
 int32_t pthb200_device_status(int32_t* status);

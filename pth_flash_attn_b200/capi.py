@@ -130,6 +130,7 @@ EXPORTED_SYMBOLS = (
     "pthb200_launch_count",
     "pthb200_test_tile",
     "pthb200_test_tile_i8",
+    "pthb200_test_tile_rows",
     "pthb200_device_status",
 )
 
@@ -180,6 +181,8 @@ class B200Lib:
         lib.pthb200_test_tile.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int32, ctypes.c_void_p]
         lib.pthb200_test_tile_i8.restype = ctypes.c_int32
         lib.pthb200_test_tile_i8.argtypes = [ctypes.c_void_p] * 7
+        lib.pthb200_test_tile_rows.restype = ctypes.c_int32
+        lib.pthb200_test_tile_rows.argtypes = [ctypes.c_void_p] * 7
         lib.pthb200_device_status.restype = ctypes.c_int32
         lib.pthb200_device_status.argtypes = [ctypes.POINTER(ctypes.c_int32)]
         if lib.pthb200_abi_version() != ABI_VERSION:

@@ -174,6 +174,7 @@ cudaError_t launch_scalar_attention(const KernelParams& p, cudaStream_t stream);
 cudaError_t launch_umma_attention(const KernelParams& p, cudaStream_t stream);
 cudaError_t launch_umma_i8_attention(const KernelParams& p, cudaStream_t stream);
 cudaError_t read_i8_status(unsigned int* v);
+cudaError_t read_rows_status(unsigned int* v);
 cudaError_t launch_combine_kernel(const CombineParams& p, cudaStream_t stream);
 // True if the tcgen05 kernel handles these parameters.
 bool umma_supports(const KernelParams& p, const char** why);

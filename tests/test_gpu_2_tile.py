@@ -56,3 +56,27 @@ def test_umma_tile_int8():
     o_want = v.astype(np.int64).T @ pm.astype(np.int64)
     assert np.array_equal(s_out.cpu().numpy(), s_want)
     assert np.array_equal(o_out.cpu().numpy(), o_want)
+
+
+def test_umma_tile_rows():
+    """Row-major building blocks: S = Q K^T (rows on M) and O = P V with P read from TMEM."""
+    lib = capi.load_library()
+    rng = np.random.default_rng(21)
+    k = rng.integers(-128, 128, size=(128, 128), dtype=np.int8)
+    v = rng.integers(-128, 128, size=(128, 128), dtype=np.int8)
+    q = orc.round_to_bf16(rng.standard_normal((128, 128), dtype=np.float32))
+    pm = orc.round_to_bf16(rng.random((128, 128), dtype=np.float32))
+    dev = "cuda"
+    kt, vt = torch.from_numpy(k).to(dev), torch.from_numpy(v).to(dev)
+    qt = torch.from_numpy(q).to(dev).to(torch.bfloat16)
+    pt = torch.from_numpy(pm).to(dev).to(torch.bfloat16)
+    s_out = torch.full((128, 128), float("nan"), dtype=torch.float32, device=dev)
+    o_out = torch.full((128, 128), float("nan"), dtype=torch.float32, device=dev)
+    rc = lib.lib.pthb200_test_tile_rows(kt.data_ptr(), qt.data_ptr(), vt.data_ptr(), pt.data_ptr(),
+                                        s_out.data_ptr(), o_out.data_ptr(), None)
+    assert rc == capi.OK
+    assert lib.device_status() == 0, "a bounded wait gave up"
+    s_want = q.astype(np.float64) @ k.astype(np.float64).T          # [row][key]
+    o_want = pm.astype(np.float64) @ v.astype(np.float64)           # [row][d]
+    np.testing.assert_allclose(s_out.cpu().numpy(), s_want, rtol=1e-5, atol=1e-2)
+    np.testing.assert_allclose(o_out.cpu().numpy(), o_want, rtol=1e-5, atol=1e-2)
