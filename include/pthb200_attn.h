@@ -160,7 +160,9 @@ enum {
   PTHB200_KERNEL_SCALAR = 1, /* CUDA-core kernel: every head size, layout, dtype */
   PTHB200_KERNEL_UMMA = 2,   /* tcgen05 int8 kernel (kind::i8, cache bytes used as stored);
                                 EINVAL where it does not apply */
-  PTHB200_KERNEL_UMMA_BF16 = 3 /* tcgen05 kernel that widens the cache to bf16 (kind::f16) */
+  PTHB200_KERNEL_UMMA_BF16 = 3, /* tcgen05 kernel that widens the cache to bf16 (kind::f16) */
+  PTHB200_KERNEL_UMMA_ROWS = 4  /* tcgen05 kernel with query rows on the MMA M dimension
+                                   (prefill, wide verification); bf16 operands */
 };
 
 /* Options of the _ex entry points.  Zero-initialise, then set abi_version and

@@ -17,7 +17,7 @@ from pathlib import Path
 ABI_VERSION = 2
 F32, F16, BF16 = 0, 1, 2
 OK, EINVAL, ECUDA, ENOCUDA = 0, -1, -2, -3
-KERNEL_AUTO, KERNEL_SCALAR, KERNEL_UMMA, KERNEL_UMMA_BF16 = 0, 1, 2, 3
+KERNEL_AUTO, KERNEL_SCALAR, KERNEL_UMMA, KERNEL_UMMA_BF16, KERNEL_UMMA_ROWS = 0, 1, 2, 3, 4
 
 LIBRARY_PATH = Path(__file__).with_name("libpthb200_attn.so")
 

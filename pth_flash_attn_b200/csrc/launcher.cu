@@ -47,7 +47,7 @@ int32_t check_options(const PthB200Options* o) {
   if (o == nullptr) return PTH_ATTN_OK;
   PTHB_REQUIRE(o->abi_version == PTH_ATTN_ABI_VERSION, "options.abi_version does not match the library");
   PTHB_REQUIRE(o->struct_bytes == (int32_t)sizeof(PthB200Options), "options.struct_bytes != sizeof(PthB200Options)");
-  PTHB_REQUIRE(o->kernel >= PTHB200_KERNEL_AUTO && o->kernel <= PTHB200_KERNEL_UMMA_BF16, "options.kernel is not a kernel family");
+  PTHB_REQUIRE(o->kernel >= PTHB200_KERNEL_AUTO && o->kernel <= PTHB200_KERNEL_UMMA_ROWS, "options.kernel is not a kernel family");
   if (o->lse_out != nullptr) {
     PTHB_REQUIRE(aligned(o->lse_out, 4), "options.lse_out must be 4-byte aligned");
     PTHB_REQUIRE(o->lse_stride_token % 4 == 0 && o->lse_stride_head % 4 == 0 && o->lse_stride_token >= 0 &&
@@ -179,10 +179,22 @@ int32_t choose_family(const KernelParams& p, const PthB200Options* opt, int32_t*
   } else if (want == PTHB200_KERNEL_UMMA_BF16) {
     PTHB_REQUIRE(umma_ok, std::string("options.kernel = UMMA_BF16 does not apply: ") + why);
     *family = want;
+  } else if (want == PTHB200_KERNEL_UMMA_ROWS) {
+    const char* why_rows = "";
+    PTHB_REQUIRE(umma_rows_supports(p, &why_rows), std::string("options.kernel = UMMA_ROWS does not apply: ") + why_rows);
+    *family = want;
   } else if (want == PTHB200_KERNEL_SCALAR) {
     *family = PTHB200_KERNEL_SCALAR;
   } else {
-    *family = i8_ok ? PTHB200_KERNEL_UMMA : umma_ok ? PTHB200_KERNEL_UMMA_BF16 : PTHB200_KERNEL_SCALAR;
+    // Tall row tiles (prefill chunks, wide verification: more than 16 rows per KV head and
+    // tile) go to the row-major kernel, short ones (decode, narrow verification) to the
+    // token-major integer kernel.
+    const char* why_rows = "";
+    const bool tall = (int64_t)p.bq * p.group > 16;
+    *family = (tall && umma_rows_supports(p, &why_rows)) ? PTHB200_KERNEL_UMMA_ROWS
+              : i8_ok                                   ? PTHB200_KERNEL_UMMA
+              : umma_ok                                 ? PTHB200_KERNEL_UMMA_BF16
+                                                        : PTHB200_KERNEL_SCALAR;
   }
   return PTH_ATTN_OK;
 }
@@ -197,6 +209,8 @@ int32_t attention_impl(const PthAttnArgs* a, const PthB200Options* opt, void* st
   cudaError_t err;
   if (family == PTHB200_KERNEL_UMMA) {
     err = launch_umma_i8_attention(p, static_cast<cudaStream_t>(stream));
+  } else if (family == PTHB200_KERNEL_UMMA_ROWS) {
+    err = launch_umma_rows_attention(p, static_cast<cudaStream_t>(stream));
   } else if (family == PTHB200_KERNEL_UMMA_BF16) {
     err = launch_umma_attention(p, static_cast<cudaStream_t>(stream));
   } else {

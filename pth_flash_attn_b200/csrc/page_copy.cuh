@@ -1,0 +1,106 @@
+// Shared by the tcgen05 attention kernels that fetch whole cache cells with TMA: the raw
+// tile geometry, the mbarrier / bulk-copy wrappers of the loader and producer roles, the
+// bounded wait, and the host side of the page tensor map.
+//
+// A raw tile holds, for each of the 128 keys of a KV tile, the 272 bytes from the 16-byte
+// boundary below the key's 264-byte cell (K[128] | k_scale | V[128] | v_scale, 8-byte
+// aligned): with delta = cell address mod 16 in {0, 8}, K is at raw bytes delta .. delta + 127,
+// k_scale at delta + 128, V at delta + 132, v_scale at delta + 260.
+#pragma once
+
+#include <cuda.h>
+
+#include "params.cuh"
+#include "tcgen05.cuh"
+
+namespace pthb200 {
+namespace {
+
+constexpr int kRawKeys = 128;                               // keys of one KV tile
+constexpr int kRawRow = 272;                                // aligned bytes that cover a 264-byte cell
+constexpr int kRawStageBytes = kRawKeys * kRawRow;          // 34,816 B
+
+__device__ __forceinline__ void named_barrier(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc::smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tc::smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bulk copy global -> shared (both 16-byte aligned, size a multiple of 16); completion is
+// signalled on the mbarrier as `bytes` of transaction count.
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const uint8_t* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(tc::smem_u32(bar))
+               : "memory");
+}
+
+// Tiled TMA load of one box of a rank-3 tensor map into shared memory.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(tc::smem_u32(bar))
+      : "memory");
+}
+
+// Bounded wait with a CTA-wide abort flag: once any wait has given up, every wait returns.
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < (1u << 22); ++i) {
+    if (tc::mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 63u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ void row_target(const KernelParams& p, const RowTile& t, int kvh, int n, int* token, int* head) {
+  *token = t.tok0 + n / p.group;
+  *head = kvh * p.group + n % p.group;
+}
+
+// cuTensorMapEncodeTiled, looked up once through the runtime (no link against libcuda).
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult st;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &st) != cudaSuccess ||
+        st != cudaDriverEntryPointSuccess) {
+      ptr = nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+// Tensor map over the cache as 4-byte elements: [slot bytes / 4][block_size slots][num_blocks],
+// starting at the 16-byte boundary below head 0's first cell; one box = all slots of one page x
+// 272 bytes.  Returns false if the driver refuses the geometry.
+bool make_page_map(const KernelParams& p, int num_blocks, CUtensorMap* map) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return false;
+  const uintptr_t base = reinterpret_cast<uintptr_t>(p.k.data) & ~(uintptr_t)15;
+  const cuuint64_t dims[3] = {(cuuint64_t)(p.k.stride_slot / 4), (cuuint64_t)p.block_size, (cuuint64_t)num_blocks};
+  const cuuint64_t strides[2] = {(cuuint64_t)p.k.stride_slot, (cuuint64_t)p.k.stride_block};
+  const cuuint32_t box[3] = {(cuuint32_t)(kRawRow / 4), (cuuint32_t)p.block_size, 1u};
+  const cuuint32_t elem[3] = {1u, 1u, 1u};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, reinterpret_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// 1 = tiled TMA per page, 2 = bulk copy per contiguous page run, 0 = neither applies.
+int raw_mode_for(const KernelParams& p) {
+  if (p.block_shift < 4 || p.block_shift > 7) return 0;  // 16 .. 128 keys per page, a power of two
+  if (p.k.stride_block % 16 != 0) return 0;
+  if (p.k.stride_slot == 2 * p.head_size + 8) return 2;
+  if (p.k.stride_slot % 16 == 0 && p.k.stride_slot >= kRawRow) return 1;
+  return 0;
+}
+
+}  // namespace
+}  // namespace pthb200

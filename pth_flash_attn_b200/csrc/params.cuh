@@ -173,6 +173,7 @@ constexpr float kLn2 = 0.69314718055994530942f;
 cudaError_t launch_scalar_attention(const KernelParams& p, cudaStream_t stream);
 cudaError_t launch_umma_attention(const KernelParams& p, cudaStream_t stream);
 cudaError_t launch_umma_i8_attention(const KernelParams& p, cudaStream_t stream);
+cudaError_t launch_umma_rows_attention(const KernelParams& p, cudaStream_t stream);
 cudaError_t read_i8_status(unsigned int* v);
 cudaError_t read_rows_status(unsigned int* v);
 cudaError_t launch_combine_kernel(const CombineParams& p, cudaStream_t stream);
@@ -180,5 +181,7 @@ cudaError_t launch_combine_kernel(const CombineParams& p, cudaStream_t stream);
 bool umma_supports(const KernelParams& p, const char** why);
 // True if the integer tcgen05 kernel handles these parameters.
 bool umma_i8_supports(const KernelParams& p, const char** why);
+// True if the row-major tcgen05 kernel handles these parameters.
+bool umma_rows_supports(const KernelParams& p, const char** why);
 
 }  // namespace pthb200

@@ -48,6 +48,7 @@
 
 #include "params.cuh"
 #include "umma_i8.cuh"
+#include "page_copy.cuh"
 
 namespace pthb200 {
 
@@ -84,8 +85,6 @@ constexpr int kProducerThreads = 128;                   // one producer group: o
 __host__ __device__ constexpr int threads_for(int np) { return kSoftmaxThreads + np * kProducerThreads + 96; }
 constexpr int kStageScales = 2 * kKeys * 4;                 // k_scale[128], v_scale[128]
 constexpr int kVStageBytes = kImgBytes + kStageScales;      // V image and both scale vectors of one tile
-constexpr int kRawRow = 272;                                // aligned bytes that cover a 264-byte cell
-constexpr int kRawStageBytes = kKeys * kRawRow;             // 34,816 B
 
 template <int NPAD, int PD, int NS, int NK, int NR, int SB>
 struct Layout {
@@ -124,46 +123,6 @@ struct Bars {
   static constexpr int raw_free = 2 * NS + 14 + NR;  // [NR] producers -> loader, 128 arrivals
   static constexpr int kempty = 2 * NS + 14 + 2 * NR; // [NK] QK issuer (tcgen05.commit) -> producers
 };
-
-__device__ __forceinline__ void named_barrier(int id, int count) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc::smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tc::smem_u32(bar)), "r"(bytes) : "memory");
-}
-// Bulk copy global -> shared (both 16-byte aligned, size a multiple of 16); completion is
-// signalled on the mbarrier as `bytes` of transaction count.
-__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const uint8_t* src, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(tc::smem_u32(bar))
-               : "memory");
-}
-
-// Tiled TMA load of one box of a rank-3 tensor map into shared memory.
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(tc::smem_u32(bar))
-      : "memory");
-}
-
-// Bounded wait with a CTA-wide abort flag: once any wait has given up, every wait returns.
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < (1u << 22); ++i) {
-    if (tc::mbar_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 63u && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
-}
-
-__device__ __forceinline__ void row_target(const KernelParams& p, const RowTile& t, int kvh, int n, int* token, int* head) {
-  *token = t.tok0 + n / p.group;
-  *head = kvh * p.group + n % p.group;
-}
 
 template <int NPAD, int PD, int NS, int NK, int NR, int SB, int RQ, int NP>
 __global__ void __launch_bounds__(threads_for(NP), 1)
@@ -777,48 +736,6 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
   if (warp == 0) tc::tmem_dealloc(tmem_base, L::tmem_alloc);
   if (tid == 0 && *abort_flag) atomicOr(&g_i8_status, 4u);
   (void)ok;
-}
-
-// cuTensorMapEncodeTiled, looked up once through the runtime (no link against libcuda).
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult st;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &st) != cudaSuccess ||
-        st != cudaDriverEntryPointSuccess) {
-      ptr = nullptr;
-    }
-    return reinterpret_cast<EncodeTiledFn>(ptr);
-  }();
-  return fn;
-}
-
-// Tensor map over the cache as 4-byte elements: [slot bytes / 4][block_size slots][num_blocks],
-// starting at the 16-byte boundary below head 0's first cell; one box = all slots of one page x
-// 272 bytes.  Returns false if the driver refuses the geometry.
-bool make_page_map(const KernelParams& p, int num_blocks, CUtensorMap* map) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (fn == nullptr) return false;
-  const uintptr_t base = reinterpret_cast<uintptr_t>(p.k.data) & ~(uintptr_t)15;
-  const cuuint64_t dims[3] = {(cuuint64_t)(p.k.stride_slot / 4), (cuuint64_t)p.block_size, (cuuint64_t)num_blocks};
-  const cuuint64_t strides[2] = {(cuuint64_t)p.k.stride_slot, (cuuint64_t)p.k.stride_block};
-  const cuuint32_t box[3] = {(cuuint32_t)(kRawRow / 4), (cuuint32_t)p.block_size, 1u};
-  const cuuint32_t elem[3] = {1u, 1u, 1u};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, reinterpret_cast<void*>(base), dims, strides, box, elem,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-// 1 = tiled TMA per page, 2 = bulk copy per contiguous page run, 0 = neither applies.
-int raw_mode_for(const KernelParams& p) {
-  if (p.block_shift < 4 || p.block_shift > 7) return 0;  // 16 .. 128 keys per page, a power of two
-  if (p.k.stride_block % 16 != 0) return 0;
-  if (p.k.stride_slot == 2 * p.head_size + 8) return 2;
-  if (p.k.stride_slot % 16 == 0 && p.k.stride_slot >= kRawRow) return 1;
-  return 0;
 }
 
 template <int NPAD, int PD, int NS, int NK, int NR, int SB, int RQ, int NP>

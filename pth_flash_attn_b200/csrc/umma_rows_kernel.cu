@@ -1,12 +1,558 @@
-// Row-major tcgen05 attention kernel, head size 128 (query rows on the MMA M dimension).
+// Row-major tcgen05 attention kernel, head size 128: query rows on the MMA M dimension.
+//
+// For launches with many rows per KV head (prefill chunks, wide verification steps) the
+// work per KV tile is dominated by the two contractions and by one exponential per
+// (row, key).  This kernel gives every query row of a 128-row tile one softmax thread
+// (TMEM lane = row), so the row maximum and sum never leave that thread's registers:
+//
+//   loader     (1 warp)   TMA page copies of the raw cache cells into a ring of raw stages
+//                         (same scheme as the integer kernel);
+//   producers  (4 warps)  thread t widens key t's int8 K and V bytes exactly to bf16 and
+//                         writes them into the K image and the V stage (canonical
+//                         no-swizzle layout), with the two scale vectors;
+//   QK issuer  (1 thread) S = Q K^T, M = 128 rows, N = 128 keys, fp32 in TMEM, one buffer
+//                         per softmax group;
+//   softmax    (2 groups of 4 warps; group g owns the tiles i with i % 2 == g) thread r:
+//                         pass 1 finds the tile maximum of row r (score = S * k_scale *
+//                         softmax_scale * log2 e), pass 2 writes p * v_scale as packed bf16
+//                         into TMEM over the columns of S it has already read.  The
+//                         reference maximum of a row moves only when the running maximum
+//                         outgrows it by 2^8; then the thread rescales its row of O in
+//                         TMEM.  In steady state O is never touched by the softmax;
+//   PV issuer  (1 thread) O += P V with P read from TMEM (the A operand), V from the
+//                         V stage as an MN-major B operand, N = 128 (d), fp32 in TMEM.
+// The two groups' (m, l, O) are merged in the epilogue.  TMEM: S0 S1 O0 O1, 128 columns
+// each.  Every mbarrier wait is bounded (see page_copy.cuh).
 #include <cuda.h>
 
 #include "params.cuh"
 #include "umma_rows.cuh"
+#include "page_copy.cuh"
 
 namespace pthb200 {
 
 __device__ unsigned int g_rows_status = 0;
+
+namespace {
+
+constexpr int kRGroup = 128;             // threads of one softmax group = rows of a tile
+constexpr int kRSoftmax = 2 * kRGroup;   // warps 0-3, 4-7
+constexpr int kRProducers = 128;         // warps 8-11
+constexpr int kRQkWarp = 12, kRPvWarp = 13, kRLoadWarp = 14;
+constexpr int kRThreads = 480;
+constexpr int kRNK = 1;                  // K images
+constexpr int kRNS = 2;                  // V stages (V image + both scale vectors)
+constexpr int kRNR = 2;                  // raw stages
+constexpr int kRVStage = kWideBytes + 2 * kTileKeys * 4;
+constexpr float kRescaleGap = 8.0f;      // log2 units a row maximum may outgrow its reference
+
+struct RLayout {
+  static constexpr int kimg = 0;
+  static constexpr int vst = kimg + kRNK * kWideBytes;
+  static constexpr int qimg = vst + kRNS * kRVStage;
+  static constexpr int raw = qimg + kQImageBytes;
+  static constexpr int park_m = raw + kRNR * kRawStageBytes;   // float [128]
+  static constexpr int park_l = park_m + kRGroup * 4;          // float [128]
+  static constexpr int bars = park_l + kRGroup * 4;            // uint64 [...]
+  static constexpr int n_bars = kRNS * 2 + kRNK + 6 + 2 * kRNR;
+  static constexpr int misc = bars + n_bars * 8;
+  static constexpr int total = misc + 16;
+};
+static_assert(RLayout::raw % 128 == 0 && RLayout::vst % 128 == 0 && RLayout::qimg % 128 == 0, "TMA / image alignment");
+static_assert(RLayout::total <= 227 * 1024, "shared memory of one CTA");
+
+struct RBars {
+  static constexpr int full = 0;                       // [NS] producers -> QK, 128 arrivals
+  static constexpr int vempty = kRNS;                  // [NS] PV commit -> producers
+  static constexpr int kempty = 2 * kRNS;              // [NK] QK commit -> producers
+  static constexpr int s_ready = 2 * kRNS + kRNK;      // [2] QK commit -> softmax
+  static constexpr int p_ready = s_ready + 2;          // [2] softmax -> PV, 128 arrivals
+  static constexpr int pv_done = p_ready + 2;          // [2] PV commit -> QK, softmax
+  static constexpr int raw_full = pv_done + 2;         // [NR]
+  static constexpr int raw_free = raw_full + kRNR;     // [NR] producers -> loader, 128 arrivals
+};
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(kRThreads, 1)
+umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_constant__ CUtensorMap tmap) {
+  using L = RLayout;
+  using B = RBars;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* qimg = smem + L::qimg;
+  float* park_m = reinterpret_cast<float*>(smem + L::park_m);
+  float* park_l = reinterpret_cast<float*>(smem + L::park_l);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::bars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::misc);
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + L::misc + 8);
+
+  const int kvh = blockIdx.y, split = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // Row tile of this CTA: bisect a shared-memory copy of query_start_loc when it fits.
+  constexpr int kQslCache = 4096;
+  RowTile t;
+  if (p.num_reqs + 1 <= kQslCache) {
+    int* qsl_s = reinterpret_cast<int*>(smem + L::raw);
+    int* len_s = qsl_s + kQslCache;
+    for (int i = tid; i <= p.num_reqs; i += kRThreads) {
+      qsl_s[i] = __ldg(p.query_start_loc + i);
+      if (i < p.num_reqs) len_s[i] = __ldg(p.seq_lens + i);
+    }
+    __syncthreads();
+    t = resolve_row_tile_with(p, blockIdx.x, [&](int i) { return qsl_s[i]; }, [&](int r) { return len_s[r]; });
+    __syncthreads();
+  } else {
+    t = resolve_row_tile(p, blockIdx.x);
+  }
+  if (t.req < 0) return;
+  const int rows = t.ntok * p.group;  // <= 128 by construction of bq
+  int tile_begin, tile_end, range_begin, range_end;
+  split_tiles(p, t, split, &tile_begin, &tile_end, &range_begin, &range_end);
+
+  if (tile_begin >= tile_end) {
+    // No keys for this work item: zero output, log-sum-exp -inf.
+    for (int idx = tid; idx < rows * kHeadDim; idx += kRThreads) {
+      const int n = idx >> 7, d = idx & 127;
+      int token, head;
+      row_target(p, t, kvh, n, &token, &head);
+      if (p.num_splits == 1) {
+        store_out_elem(p.out + (int64_t)token * p.out_stride_token + (int64_t)head * p.out_stride_head, d, p.out_dtype, 0.f);
+      } else {
+        reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.ws_o) + (int64_t)split * p.ws_o_stride_split +
+                                 (int64_t)token * p.ws_o_stride_token + (int64_t)head * p.ws_o_stride_head)[d] = 0.f;
+      }
+    }
+    if (tid < rows) {
+      int token, head;
+      row_target(p, t, kvh, tid, &token, &head);
+      if (p.num_splits > 1) {
+        *reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.ws_lse) + (int64_t)split * p.ws_lse_stride_split +
+                                  (int64_t)token * p.ws_lse_stride_token + (int64_t)head * p.ws_lse_stride_head) = -INFINITY;
+      } else if (p.lse_out != nullptr) {
+        *reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.lse_out) + (int64_t)token * p.lse_stride_token +
+                                  (int64_t)head * p.lse_stride_head) = -INFINITY;
+      }
+    }
+    return;
+  }
+
+  const int n_tiles = tile_end - tile_begin;
+  if (tid == 0) {
+    for (int s = 0; s < kRNS; ++s) {
+      tc::mbar_init(&bars[B::full + s], kRProducers);
+      tc::mbar_init(&bars[B::vempty + s], 1);
+    }
+    for (int s = 0; s < kRNK; ++s) tc::mbar_init(&bars[B::kempty + s], 1);
+    for (int g = 0; g < 2; ++g) {
+      tc::mbar_init(&bars[B::s_ready + g], 1);
+      tc::mbar_init(&bars[B::p_ready + g], kRGroup);
+      tc::mbar_init(&bars[B::pv_done + g], 1);
+    }
+    for (int s = 0; s < kRNR; ++s) {
+      tc::mbar_init(&bars[B::raw_full + s], kRawKeys >> p.block_shift);
+      tc::mbar_init(&bars[B::raw_free + s], kRProducers);
+    }
+    *abort_flag = 0;
+    tc::mbar_init_fence();
+  }
+  if (warp == 0) {
+    tc::tmem_alloc(tslot, 512);
+    tc::tmem_relinquish();
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = *tslot;
+  const uint32_t kimg_s = tc::smem_u32(smem + L::kimg), vst_s = tc::smem_u32(smem + L::vst);
+  bool ok = true;
+
+  if (warp >= 8 && warp < kRQkWarp) {
+    // =========================== producers ====================================
+    const int pt = tid - kRSoftmax;  // key of the tile this thread widens
+    const int bs = p.block_size;
+    const uint8_t* kb = p.k.data + (int64_t)kvh * p.k.stride_head;
+    const uint32_t delta = (uint32_t)(reinterpret_cast<uintptr_t>(kb) & 15);
+    const int row_pitch = p.raw_mode == 1 ? kRawRow : 2 * kHeadDim + 8;
+    const int my_page = pt >> p.block_shift, my_slot = pt & (bs - 1);
+    const uint32_t cell_off = my_page * bs * kRawRow + my_slot * row_pitch + delta;  // inside a raw stage
+    const bool odd = (cell_off & 8u) != 0;
+#pragma unroll 1
+    for (int j = 0; j < n_tiles; ++j) {
+      const int rs = j % kRNR;
+      const int pos = (tile_begin + j) * kTileKeys + pt;
+      const bool valid = pos >= range_begin && pos < range_end;
+      ok &= wait_or_abort(&bars[B::raw_full + rs], (j / kRNR) & 1, abort_flag);
+      uint32_t w[kRawRow / 4];
+      if (valid) {
+        const uint4* row = reinterpret_cast<const uint4*>(smem + L::raw + rs * kRawStageBytes + (cell_off & ~15u));
+#pragma unroll
+        for (int c = 0; c < kRawRow / 16; ++c) {
+          const uint4 v = row[c];
+          w[4 * c] = v.x;
+          w[4 * c + 1] = v.y;
+          w[4 * c + 2] = v.z;
+          w[4 * c + 3] = v.w;
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < kRawRow / 4; ++c) w[c] = 0u;
+      }
+      mbar_arrive(&bars[B::raw_free + rs]);  // the row is in registers: the stage may be refilled
+      const int st = j % kRNS;
+      uint8_t* kdst = smem + L::kimg + (j % kRNK) * kWideBytes + pt * 16;
+      uint8_t* vstage = smem + L::vst + st * kRVStage;
+      uint8_t* vdst = vstage + pt * 16;
+      if (j >= kRNK) ok &= wait_or_abort(&bars[B::kempty + j % kRNK], ((j / kRNK) - 1) & 1, abort_flag);
+      if (!odd) {
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c)
+          *reinterpret_cast<uint4*>(kdst + c * kChunkStride) = widen8_bf16(make_uint2(w[2 * c], w[2 * c + 1]));
+      } else {
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c)
+          *reinterpret_cast<uint4*>(kdst + c * kChunkStride) = widen8_bf16(make_uint2(w[2 + 2 * c], w[3 + 2 * c]));
+      }
+      if (j >= kRNS) ok &= wait_or_abort(&bars[B::vempty + st], ((j / kRNS) - 1) & 1, abort_flag);
+      if (!odd) {
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c)
+          *reinterpret_cast<uint4*>(vdst + c * kChunkStride) = widen8_bf16(make_uint2(w[33 + 2 * c], w[34 + 2 * c]));
+        *reinterpret_cast<uint32_t*>(vstage + kWideBytes + pt * 4) = w[32];
+        *reinterpret_cast<uint32_t*>(vstage + kWideBytes + kTileKeys * 4 + pt * 4) = w[65];
+      } else {
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c)
+          *reinterpret_cast<uint4*>(vdst + c * kChunkStride) = widen8_bf16(make_uint2(w[35 + 2 * c], w[36 + 2 * c]));
+        *reinterpret_cast<uint32_t*>(vstage + kWideBytes + pt * 4) = w[34];
+        *reinterpret_cast<uint32_t*>(vstage + kWideBytes + kTileKeys * 4 + pt * 4) = w[67];
+      }
+      tc::fence_async_smem();
+      mbar_arrive(&bars[B::full + st]);
+    }
+  } else if (warp == kRLoadWarp) {
+    // =========================== loader =======================================
+    // One TMA copy per KV page of a tile, issued by lane `page`: a tiled tensor-map box of
+    // [block_size slots] x [272 bytes] (raw_mode 1) or one bulk copy of a contiguous page
+    // run (raw_mode 2); the next tile's block ids are fetched before waiting for the stage.
+    const int pages_per_tile = kRawKeys >> p.block_shift;
+    if (lane < pages_per_tile) {
+      const int bs = p.block_size;
+      const int32_t* bt = p.block_table + (int64_t)t.req * p.block_table_row_stride;
+      const uint8_t* kb = p.k.data + (int64_t)kvh * p.k.stride_head;
+      const uint32_t delta = (uint32_t)(reinterpret_cast<uintptr_t>(kb) & 15);
+      const int tma_x = (int)((reinterpret_cast<uintptr_t>(kb) - delta -
+                               (reinterpret_cast<uintptr_t>(p.k.data) & ~(uintptr_t)15)) >> 2);
+      const uint32_t raw_s = tc::smem_u32(smem + L::raw);
+      auto page_block = [&](int tile) -> int {
+        const int pos0 = (tile_begin + tile) * kTileKeys + lane * bs;
+        if (tile >= n_tiles || pos0 >= range_end || pos0 + bs <= range_begin) return -1;
+        return __ldg(bt + (pos0 >> p.block_shift));
+      };
+      int blk = page_block(0);
+#pragma unroll 1
+      for (int j = 0; j < n_tiles; ++j) {
+        const int blk_next = page_block(j + 1);
+        const int rs = j % kRNR;
+        if (j >= kRNR) ok &= wait_or_abort(&bars[B::raw_free + rs], ((j / kRNR) - 1) & 1, abort_flag);
+        uint64_t* bar = &bars[B::raw_full + rs];
+        if (blk >= 0 && ok) {
+          const uint32_t dst = raw_s + rs * kRawStageBytes + lane * bs * kRawRow;
+          if (p.raw_mode == 1) {
+            mbar_arrive_expect_tx(bar, bs * kRawRow);
+            tma_load_3d(dst, &tmap, tma_x, 0, blk, bar);
+          } else {
+            const uint8_t* src = kb + (int64_t)blk * p.k.stride_block - delta;
+            const uint32_t bytes = (delta + bs * (2 * kHeadDim + 8) + 15u) & ~15u;
+            mbar_arrive_expect_tx(bar, bytes);
+            bulk_copy_g2s(dst, src, bytes, bar);
+          }
+        } else {
+          mbar_arrive(bar);
+        }
+        blk = blk_next;
+      }
+    }
+  } else if (warp == kRQkWarp) {
+    // =========================== QK issuer ====================================
+    named_barrier(5, kRSoftmax + 32);  // wait for the Q image
+    if (lane == 0) {
+      const uint32_t qimg_s = tc::smem_u32(qimg);
+#pragma unroll 1
+      for (int i = 0; i < n_tiles; ++i) {
+        const int g = i & 1, k = i >> 1;
+        ok &= wait_or_abort(&bars[B::full + i % kRNS], (i / kRNS) & 1, abort_flag);
+        // S(g) doubles as P(g): free once the PV of this group's previous tile has read it
+        if (k >= 1) ok &= wait_or_abort(&bars[B::pv_done + g], (k - 1) & 1, abort_flag);
+        tc::fence_after_sync();
+        issue_qk_rows(tmem_base + g * 128, qimg_s, kimg_s + (i % kRNK) * kWideBytes);
+        tc::mma_commit(&bars[B::s_ready + g]);
+        tc::mma_commit(&bars[B::kempty + i % kRNK]);
+      }
+    }
+  } else if (warp == kRPvWarp) {
+    // =========================== PV issuer ====================================
+    if (lane == 0) {
+#pragma unroll 1
+      for (int i = 0; i < n_tiles; ++i) {
+        const int g = i & 1, k = i >> 1;
+        ok &= wait_or_abort(&bars[B::p_ready + g], k & 1, abort_flag);
+        tc::fence_after_sync();
+        issue_pv_rows(tmem_base + 256 + g * 128, tmem_base + g * 128, vst_s + (i % kRNS) * kRVStage, k > 0);
+        tc::mma_commit(&bars[B::pv_done + g]);
+        tc::mma_commit(&bars[B::vempty + i % kRNS]);
+      }
+    }
+  } else if (warp < 8) {
+    // =========================== softmax ======================================
+    const int g = warp >> 2;
+    const int row = tid & 127;   // row of the tile = TMEM lane
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t s_tmem = tmem_base + g * 128 + lane_addr;        // S(g), later P(g)
+    const uint32_t o_tmem = tmem_base + 256 + g * 128 + lane_addr;  // O(g)
+
+    // ---- Q image: thread (row, half) copies 8 of the 16 d-chunks of its row ----
+    {
+      const int half = tid >> 7;
+      int token, head;
+      row_target(p, t, kvh, row, &token, &head);
+      const uint4* src = reinterpret_cast<const uint4*>(p.q + (int64_t)token * p.q_stride_token +
+                                                        (int64_t)head * p.q_stride_head);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const int cc = half * 8 + c;
+        const uint4 v = row < rows ? __ldg(src + cc) : make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(qimg + cc * kChunkStride + row * 16) = v;
+      }
+    }
+    tc::fence_async_smem();
+    named_barrier(5, kRSoftmax + 32);  // Q image complete; the QK issuer may start
+
+    int rlo = 0, rhi = -1;  // visible keys of this row (none for a padding row)
+    if (row < rows) visible_range(p, t, t.first_idx + row / p.group, &rlo, &rhi);
+    int mask_lo, mask_hi, tmp;  // key positions every live row sees: such tiles need no mask
+    visible_range(p, t, t.first_idx + t.ntok - 1, &mask_lo, &tmp);
+    visible_range(p, t, t.first_idx, &tmp, &mask_hi);
+
+    float m_ref = -INFINITY;  // reference maximum of the row's exponentials (log2 units)
+    float l = 0.f;            // sum of exp2(score - m_ref)
+    int it = 0;
+#pragma unroll 1
+    for (int i = g; i < n_tiles; i += 2, ++it) {
+      const float* ksp = reinterpret_cast<const float*>(smem + L::vst + (i % kRNS) * kRVStage + kWideBytes);
+      const float* vsp = ksp + kTileKeys;
+      const int pos0 = (tile_begin + i) * kTileKeys;
+      const bool interior = pos0 >= mask_lo && pos0 + (kTileKeys - 1) <= mask_hi;
+      ok &= wait_or_abort(&bars[B::s_ready + g], it & 1, abort_flag);
+      tc::fence_after_sync();
+
+      // ---- pass 1: maximum of the row's scores in this tile ----
+      float m_t = -INFINITY;
+#pragma unroll 1
+      for (int j = 0; j < 4; ++j) {
+        uint32_t r[32];
+        tc::tmem_ld32(s_tmem + j * 32, r);
+        tc::tmem_ld_wait();
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int n4 = 0; n4 < 8; ++n4) {
+          const float4 ks4 = reinterpret_cast<const float4*>(ksp)[j * 8 + n4];
+          const float kk[4] = {ks4.x, ks4.y, ks4.z, ks4.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int n = n4 * 4 + e;
+            float s = __uint_as_float(r[n]) * (kk[e] * p.scale_log2);
+            if (!interior) {
+              const int pos = pos0 + j * 32 + n;
+              s = (pos >= rlo && pos <= rhi) ? s : -INFINITY;
+            }
+            mx[e] = fmaxf(mx[e], s);
+          }
+        }
+        m_t = fmaxf(m_t, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])));
+      }
+
+      // ---- move the reference maximum if the row has outgrown it ----
+      const float m_new = fmaxf(m_ref, m_t);
+      const bool need = m_t > m_ref + kRescaleGap;  // also true when m_ref is still -inf
+      if (it == 0) {
+        m_ref = m_new;  // nothing accumulated yet
+      } else if (__any_sync(0xffffffffu, need)) {
+        // O(g) must be at rest: the PV of this group's previous tile has completed
+        ok &= wait_or_abort(&bars[B::pv_done + g], (it - 1) & 1, abort_flag);
+        tc::fence_after_sync();
+        const float alpha = need ? ex2f(m_ref - m_new) : 1.0f;  // 0 when m_ref was -inf
+#pragma unroll 1
+        for (int j = 0; j < 4; ++j) {
+          uint32_t r[32];
+          tc::tmem_ld32(o_tmem + j * 32, r);
+          tc::tmem_ld_wait();
+#pragma unroll
+          for (int n = 0; n < 32; ++n) r[n] = __float_as_uint(__uint_as_float(r[n]) * alpha);
+          tc::tmem_st32(o_tmem + j * 32, r);
+        }
+        tc::tmem_st_wait();
+        l *= alpha;
+        if (need) m_ref = m_new;
+      }
+      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+
+      // ---- pass 2: p * v_scale as packed bf16 over the columns of S already read ----
+#pragma unroll 1
+      for (int j = 0; j < 4; ++j) {
+        uint32_t r[32];
+        tc::tmem_ld32(s_tmem + j * 32, r);
+        tc::tmem_ld_wait();
+        uint32_t pk[16];
+        float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int n4 = 0; n4 < 8; ++n4) {
+          const float4 ks4 = reinterpret_cast<const float4*>(ksp)[j * 8 + n4];
+          const float4 vs4 = reinterpret_cast<const float4*>(vsp)[j * 8 + n4];
+          const float kk[4] = {ks4.x, ks4.y, ks4.z, ks4.w};
+          const float vv[4] = {vs4.x, vs4.y, vs4.z, vs4.w};
+          float pv[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int n = n4 * 4 + e;
+            float pr = ex2f(fmaf(__uint_as_float(r[n]), kk[e] * p.scale_log2, -m_use));
+            if (!interior) {
+              const int pos = pos0 + j * 32 + n;
+              pr = (pos >= rlo && pos <= rhi) ? pr : 0.f;
+            }
+            ls[e] += pr;
+            pv[e] = pr * vv[e];
+          }
+          pk[n4 * 2] = pack_bf16(pv[0], pv[1]);
+          pk[n4 * 2 + 1] = pack_bf16(pv[2], pv[3]);
+        }
+        l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+        tc::tmem_st16(s_tmem + j * 16, pk);
+      }
+      tc::tmem_st_wait();
+      tc::fence_before_sync();
+      mbar_arrive(&bars[B::p_ready + g]);  // P of tile i complete
+    }
+
+    // ---- epilogue: merge the two groups' (m, l, O) and write the rows ----
+    const int my_tiles = it;
+    if (my_tiles > 0) {
+      ok &= wait_or_abort(&bars[B::pv_done + g], (my_tiles - 1) & 1, abort_flag);
+      tc::fence_after_sync();
+    }
+    float* park = reinterpret_cast<float*>(smem + L::raw);  // [d][row] fp32, the raw ring is idle by now
+    if (g == 1) {
+      // every producer has finished reading the raw ring once the last tile's images are full
+      ok &= wait_or_abort(&bars[B::full + (n_tiles - 1) % kRNS], ((n_tiles - 1) / kRNS) & 1, abort_flag);
+      park_m[row] = m_ref;
+      park_l[row] = l;
+      if (my_tiles > 0) {
+#pragma unroll 1
+        for (int j = 0; j < 4; ++j) {
+          uint32_t r[32];
+          tc::tmem_ld32(o_tmem + j * 32, r);
+          tc::tmem_ld_wait();
+#pragma unroll
+          for (int n = 0; n < 32; ++n) park[(j * 32 + n) * kRGroup + row] = __uint_as_float(r[n]);
+        }
+      }
+    }
+    named_barrier(4, kRSoftmax);
+    if (g == 0) {
+      const float m1 = park_m[row], l1 = park_l[row];
+      const float m = fmaxf(m_ref, m1);
+      const float c0 = m_ref == -INFINITY ? 0.f : ex2f(m_ref - m);
+      const float c1 = m1 == -INFINITY ? 0.f : ex2f(m1 - m);
+      const float lsum = l * c0 + l1 * c1;
+      const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
+      int token, head;
+      row_target(p, t, kvh, row, &token, &head);
+      uint8_t* out_row = p.out + (int64_t)token * p.out_stride_token + (int64_t)head * p.out_stride_head;
+      float* ws_row = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.ws_o) + (int64_t)split * p.ws_o_stride_split +
+                                               (int64_t)token * p.ws_o_stride_token + (int64_t)head * p.ws_o_stride_head);
+#pragma unroll 1
+      for (int j = 0; j < 4; ++j) {
+        uint32_t r[32];
+        tc::tmem_ld32(o_tmem + j * 32, r);  // group 0 always has a tile
+        tc::tmem_ld_wait();
+        float o[32];
+#pragma unroll
+        for (int n = 0; n < 32; ++n) {
+          const float o1 = c1 > 0.f ? park[(j * 32 + n) * kRGroup + row] * c1 : 0.f;
+          o[n] = (__uint_as_float(r[n]) * c0 + o1) * inv;
+        }
+        if (row < rows) {
+          if (p.num_splits > 1) {
+#pragma unroll
+            for (int n = 0; n < 32; n += 4)
+              *reinterpret_cast<float4*>(ws_row + j * 32 + n) = make_float4(o[n], o[n + 1], o[n + 2], o[n + 3]);
+          } else if (p.out_dtype == PTH_ATTN_BF16) {
+#pragma unroll
+            for (int n = 0; n < 32; n += 8)
+              *reinterpret_cast<uint4*>(out_row + (j * 32 + n) * 2) =
+                  make_uint4(pack_bf16(o[n], o[n + 1]), pack_bf16(o[n + 2], o[n + 3]), pack_bf16(o[n + 4], o[n + 5]),
+                             pack_bf16(o[n + 6], o[n + 7]));
+          } else {
+#pragma unroll
+            for (int n = 0; n < 32; ++n) store_out_elem(out_row, j * 32 + n, p.out_dtype, o[n]);
+          }
+        }
+      }
+      if (row < rows) {
+        const float lse2 = lsum > 0.f ? m + log2f(lsum) : -INFINITY;
+        if (p.num_splits > 1) {
+          *reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.ws_lse) + (int64_t)split * p.ws_lse_stride_split +
+                                    (int64_t)token * p.ws_lse_stride_token + (int64_t)head * p.ws_lse_stride_head) = lse2;
+        } else if (p.lse_out != nullptr) {
+          *reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.lse_out) + (int64_t)token * p.lse_stride_token +
+                                    (int64_t)head * p.lse_stride_head) = lse2 * kLn2;
+        }
+      }
+    }
+  }
+
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(tmem_base, 512);
+  if (tid == 0 && *abort_flag) atomicOr(&g_rows_status, 4u);
+  (void)ok;
+}
+
+}  // namespace
+
+// The row-major kernel reads the cache like the integer kernel (packed cells through TMA
+// page copies) and takes bf16 queries.
+bool umma_rows_supports(const KernelParams& p, const char** why) { return umma_i8_supports(p, why); }
+
+cudaError_t launch_umma_rows_attention(const KernelParams& p_in, cudaStream_t stream) {
+  KernelParams p = p_in;
+  // Row tiles of 128 rows, whatever tile height the caller planned with: the partition of
+  // the query tokens into row tiles is internal to a launch.
+  p.bq = 128 / p.group > 0 ? 128 / p.group : 1;
+  p.num_q_tiles = p.num_tokens / p.bq + p.num_reqs;
+  p.raw_mode = raw_mode_for(p);
+  CUtensorMap map{};
+  if (p.raw_mode == 1 && !make_page_map(p, p.num_blocks, &map)) return cudaErrorInvalidValue;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    err = cudaFuncSetAttribute(umma_rows_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RLayout::total);
+    if (err != cudaSuccess) return err;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  const dim3 grid(p.num_q_tiles, p.num_kv_heads, p.num_splits);
+  umma_rows_attention_kernel<<<grid, kRThreads, RLayout::total, stream>>>(p, map);
+  return cudaGetLastError();
+}
 
 // Reads and clears this file's status word (device must be idle).
 cudaError_t read_rows_status(unsigned int* v) {

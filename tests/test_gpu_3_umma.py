@@ -13,7 +13,7 @@ GOLDEN_D128 = ["attn_decode", "attn_verify4", "attn_window_causal", "attn_window
                "attn_noncausal", "attn_mixed"]
 
 
-KERNELS = [capi.KERNEL_UMMA, capi.KERNEL_UMMA_BF16]
+KERNELS = [capi.KERNEL_UMMA, capi.KERNEL_UMMA_BF16, capi.KERNEL_UMMA_ROWS]
 
 
 @pytest.mark.parametrize("kernel", KERNELS)
@@ -90,3 +90,34 @@ def test_window_drafter_long():
     res = run_case(c, q, qsl, scale, bq=16, num_splits=4, window=4096, kernel=capi.KERNEL_UMMA)
     check_out(res["out"], ref.out, what="window 4096")
     check_lse(res["lse"], ref.lse, what="window 4096")
+
+
+@pytest.mark.parametrize("S", [1, 3])
+def test_rows_kernel_prefill_chunk(S):
+    """A prefill chunk longer than one 128-row tile, ragged ends, plus a decode request."""
+    from tests.gpu_util import run_case
+
+    lens = [700, 1500, 90]
+    qlens = [300, 37, 1]
+    c, q, qsl = _seeded(lens, qlens, 16, 2, seed=123)
+    scale = 128 ** -0.5
+    ref = orc.ref_attention_paged(q, c, qsl, scale)
+    res = run_case(c, q, qsl, scale, bq=8, num_splits=S, kernel=capi.KERNEL_UMMA_ROWS)
+    assert capi.load_library().device_status() == 0
+    check_out(res["out"], ref.out, what=f"rows prefill S{S}")
+    check_lse(res["lse"], ref.lse, what=f"rows prefill S{S}")
+    assert res["tail_intact"]
+
+
+def test_rows_kernel_window_and_auto_choice():
+    """Drafter-shaped launch (16 tokens, window) on the row-major kernel, and through AUTO."""
+    from tests.gpu_util import run_case
+
+    lens = [9000, 5000]
+    c, q, qsl = _seeded(lens, [16, 16], 8, 2, seed=91)
+    scale = 128 ** -0.5
+    ref = orc.ref_attention_paged(q, c, qsl, scale, window=4096)
+    for kernel in (capi.KERNEL_UMMA_ROWS, capi.KERNEL_AUTO):
+        res = run_case(c, q, qsl, scale, bq=16, num_splits=2, window=4096, kernel=kernel)
+        check_out(res["out"], ref.out, what="rows window 4096")
+        check_lse(res["lse"], ref.lse, what="rows window 4096")
