@@ -167,7 +167,7 @@ class DeviceLaunch:
         s = self.sets[which % len(self.sets)]
         host.attention_forward(self.q, self.out, s["views"], s["bt"], self.lens, self.qsl, bq=self.bq,
                                num_splits=self.S, softmax_scale=D ** -0.5, ws_o=self.ws_o, ws_lse=self.ws_lse,
-                               window=self.window, causal=self.causal, flags=self.flags)
+                               window=self.window, causal=self.causal, flags=self.flags, kernel=KERNEL_CHOICE)
 
     def launch_attention_only(self, which=0):
         """Only the attention kernel (for the per-kernel roofline timing)."""
@@ -178,7 +178,7 @@ class DeviceLaunch:
                                 num_splits=self.S, softmax_scale=D ** -0.5, ws_o=self.ws_o, ws_lse=self.ws_lse,
                                 window=self.window, causal=self.causal)
         lib = capi.load_library()
-        rc = lib.attention(a, options=capi.make_options(capi.KERNEL_AUTO, self.flags),
+        rc = lib.attention(a, options=capi.make_options(KERNEL_CHOICE, self.flags),
                            stream=self.torch.cuda.current_stream().cuda_stream)
         if rc != 0:
             raise RuntimeError(lib.last_error())
@@ -197,6 +197,9 @@ class DeviceLaunch:
 # --------------------------------------------------------------------------
 # clocks
 # --------------------------------------------------------------------------
+# Kernel family of the C ABI options (0 = the library's own choice); --kernel overrides it for exploration.
+KERNEL_CHOICE = 0
+
 # Measured with ncu on the batch-64 decode launch (see profiles/).
 DRAM_BYTES_PER_ALGORITHMIC_BYTE = 1.23
 
@@ -361,12 +364,15 @@ def main():
     ap.add_argument("--config", default="long_decode")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--splits", type=int, default=0, help="override the planner's split count (exploration)")
+    ap.add_argument("--kernel", type=int, default=0, help="kernel family of the C ABI (exploration; 0 = automatic)")
     ap.add_argument("--layout", default="NHD", choices=["NHD", "HND"], help="physical order inside a page")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--profile", action="store_true",
                     help="three eager passes over the workload and exit (the command to run under ncu)")
     args = ap.parse_args()
+    global KERNEL_CHOICE
+    KERNEL_CHOICE = args.kernel
     if args.impl == "reference":
         reference_arm(args)
         return

@@ -46,10 +46,15 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 }
 
 // Bounded wait with a CTA-wide abort flag: once any wait has given up, every wait returns.
+// The thread sleeps inside try_wait (suspend hint) rather than spinning; the bound is a
+// deadline of 2^32 SM cycles (about two seconds), checked between sleeps.
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < (1u << 22); ++i) {
-    if (tc::mbar_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 63u && *abort_flag) return false;
+  if (tc::mbar_try_wait(bar, parity)) return true;
+  const long long deadline = clock64() + (1ll << 32);
+  for (;;) {
+    if (tc::mbar_try_wait_hint(bar, parity, 100000u)) return true;
+    if (*abort_flag) return false;
+    if (clock64() > deadline) break;
   }
   *abort_flag = 1;
   return false;

@@ -7,9 +7,10 @@
 //
 //   loader     (1 warp)   TMA page copies of the raw cache cells into a ring of raw stages
 //                         (same scheme as the integer kernel);
-//   producers  (4 warps)  thread t widens key t's int8 K and V bytes exactly to bf16 and
-//                         writes them into the K image and the V stage (canonical
-//                         no-swizzle layout), with the two scale vectors;
+//   producers  (8 warps)  thread t of the K set / V set widens key t's int8 K / V bytes
+//                         exactly to bf16 into the K image / the V stage (canonical
+//                         no-swizzle layout), with k_scale * softmax_scale * log2 e and
+//                         v_scale of the key;
 //   QK issuer  (1 thread) S = Q K^T, M = 128 rows, N = 128 keys, fp32 in TMEM, one buffer
 //                         per softmax group;
 //   softmax    (2 groups of 4 warps; group g owns the tiles i with i % 2 == g) thread r:
@@ -25,6 +26,8 @@
 // each.  Every mbarrier wait is bounded (see page_copy.cuh).
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "params.cuh"
 #include "umma_rows.cuh"
 #include "page_copy.cuh"
@@ -32,18 +35,30 @@
 namespace pthb200 {
 
 __device__ unsigned int g_rows_status = 0;
+#ifdef PTHB200_ROWS_STATS
+// Debug build only: cycles one thread of each role of CTA (0,0,0) spent in each phase.
+__device__ long long g_rows_stats[4][12];
+#define RSTAT_DECL long long st_[12] = {0}; const long long st_begin_ = clock64();
+#define RSTAT(slot, expr) { const long long t0_ = clock64(); expr; st_[slot] += clock64() - t0_; }
+#define RSTAT_FLUSH(role) if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { st_[11] = clock64() - st_begin_; for (int q_ = 0; q_ < 12; ++q_) g_rows_stats[role][q_] = st_[q_]; }
+#else
+#define RSTAT_DECL
+#define RSTAT(slot, expr) { expr; }
+#define RSTAT_FLUSH(role)
+#endif
 
 namespace {
 
 constexpr int kRGroup = 128;             // threads of one softmax group = rows of a tile
 constexpr int kRSoftmax = 2 * kRGroup;   // warps 0-3, 4-7
-constexpr int kRProducers = 128;         // warps 8-11
-constexpr int kRQkWarp = 12, kRPvWarp = 13, kRLoadWarp = 14;
-constexpr int kRThreads = 480;
+constexpr int kRProducers = 256;         // warps 8-11 (K half) and 12-15 (V half)
+constexpr int kRQkWarp = 16, kRPvWarp = 17, kRLoadWarp = 18;
+constexpr int kRThreads = 608;
 constexpr int kRNK = 1;                  // K images
 constexpr int kRNS = 2;                  // V stages (V image + both scale vectors)
 constexpr int kRNR = 2;                  // raw stages
-constexpr int kRVStage = kWideBytes + 2 * kTileKeys * 4;
+constexpr int kRVStage = kWideBytes + kTileKeys * 4;  // V image + v_scale[128]
+constexpr int kRKsRing = 4;                          // tiles of scaled k_scale vectors kept
 constexpr float kRescaleGap = 8.0f;      // log2 units a row maximum may outgrow its reference
 
 struct RLayout {
@@ -51,10 +66,11 @@ struct RLayout {
   static constexpr int vst = kimg + kRNK * kWideBytes;
   static constexpr int qimg = vst + kRNS * kRVStage;
   static constexpr int raw = qimg + kQImageBytes;
-  static constexpr int park_m = raw + kRNR * kRawStageBytes;   // float [128]
+  static constexpr int ksc = raw + kRNR * kRawStageBytes;      // float [kRKsRing][128]: k_scale * scale * log2 e
+  static constexpr int park_m = ksc + kRKsRing * kTileKeys * 4; // float [128]
   static constexpr int park_l = park_m + kRGroup * 4;          // float [128]
   static constexpr int bars = park_l + kRGroup * 4;            // uint64 [...]
-  static constexpr int n_bars = kRNS * 2 + kRNK + 6 + 2 * kRNR;
+  static constexpr int n_bars = kRNS * 2 + 2 * kRNK + 6 + 2 * kRNR;
   static constexpr int misc = bars + n_bars * 8;
   static constexpr int total = misc + 16;
 };
@@ -62,10 +78,11 @@ static_assert(RLayout::raw % 128 == 0 && RLayout::vst % 128 == 0 && RLayout::qim
 static_assert(RLayout::total <= 227 * 1024, "shared memory of one CTA");
 
 struct RBars {
-  static constexpr int full = 0;                       // [NS] producers -> QK, 128 arrivals
-  static constexpr int vempty = kRNS;                  // [NS] PV commit -> producers
-  static constexpr int kempty = 2 * kRNS;              // [NK] QK commit -> producers
-  static constexpr int s_ready = 2 * kRNS + kRNK;      // [2] QK commit -> softmax
+  static constexpr int vfull = 0;                      // [NS] V producers -> softmax (pass 2), 128 arrivals
+  static constexpr int vempty = kRNS;                  // [NS] PV commit -> V producers
+  static constexpr int kempty = 2 * kRNS;              // [NK] QK commit -> K producers
+  static constexpr int kfull = 2 * kRNS + kRNK;        // [NK] K producers -> QK, 128 arrivals
+  static constexpr int s_ready = 2 * kRNS + 2 * kRNK;  // [2] QK commit -> softmax
   static constexpr int p_ready = s_ready + 2;          // [2] softmax -> PV, 128 arrivals
   static constexpr int pv_done = p_ready + 2;          // [2] PV commit -> QK, softmax
   static constexpr int raw_full = pv_done + 2;         // [NR]
@@ -147,10 +164,13 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
   const int n_tiles = tile_end - tile_begin;
   if (tid == 0) {
     for (int s = 0; s < kRNS; ++s) {
-      tc::mbar_init(&bars[B::full + s], kRProducers);
+      tc::mbar_init(&bars[B::vfull + s], kRProducers / 2);
       tc::mbar_init(&bars[B::vempty + s], 1);
     }
-    for (int s = 0; s < kRNK; ++s) tc::mbar_init(&bars[B::kempty + s], 1);
+    for (int s = 0; s < kRNK; ++s) {
+      tc::mbar_init(&bars[B::kempty + s], 1);
+      tc::mbar_init(&bars[B::kfull + s], kRProducers / 2);
+    }
     for (int g = 0; g < 2; ++g) {
       tc::mbar_init(&bars[B::s_ready + g], 1);
       tc::mbar_init(&bars[B::p_ready + g], kRGroup);
@@ -176,7 +196,10 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
 
   if (warp >= 8 && warp < kRQkWarp) {
     // =========================== producers ====================================
-    const int pt = tid - kRSoftmax;  // key of the tile this thread widens
+    // Warps 8-11 widen the K half of the raw cells into the K image, warps 12-15 the V half
+    // (and both scales) into the V stage; thread pt of either set owns key pt of the tile.
+    const int pt = tid & 127;
+    const bool v_part = warp >= 12;
     const int bs = p.block_size;
     const uint8_t* kb = p.k.data + (int64_t)kvh * p.k.stride_head;
     const uint32_t delta = (uint32_t)(reinterpret_cast<uintptr_t>(kb) & 15);
@@ -184,17 +207,20 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
     const int my_page = pt >> p.block_shift, my_slot = pt & (bs - 1);
     const uint32_t cell_off = my_page * bs * kRawRow + my_slot * row_pitch + delta;  // inside a raw stage
     const bool odd = (cell_off & 8u) != 0;
+    RSTAT_DECL
 #pragma unroll 1
     for (int j = 0; j < n_tiles; ++j) {
       const int rs = j % kRNR;
       const int pos = (tile_begin + j) * kTileKeys + pt;
       const bool valid = pos >= range_begin && pos < range_end;
-      ok &= wait_or_abort(&bars[B::raw_full + rs], (j / kRNR) & 1, abort_flag);
-      uint32_t w[kRawRow / 4];
+      RSTAT(0, ok &= wait_or_abort(&bars[B::raw_full + rs], (j / kRNR) & 1, abort_flag))
+      // nine 16-byte chunks: raw words 0..35 (K half, k_scale) or 32..67 (k_scale, V half, v_scale)
+      uint32_t w[36];
       if (valid) {
-        const uint4* row = reinterpret_cast<const uint4*>(smem + L::raw + rs * kRawStageBytes + (cell_off & ~15u));
+        const uint4* row = reinterpret_cast<const uint4*>(smem + L::raw + rs * kRawStageBytes + (cell_off & ~15u)) +
+                           (v_part ? 8 : 0);
 #pragma unroll
-        for (int c = 0; c < kRawRow / 16; ++c) {
+        for (int c = 0; c < 9; ++c) {
           const uint4 v = row[c];
           w[4 * c] = v.x;
           w[4 * c + 1] = v.y;
@@ -203,40 +229,47 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
         }
       } else {
 #pragma unroll
-        for (int c = 0; c < kRawRow / 4; ++c) w[c] = 0u;
+        for (int c = 0; c < 36; ++c) w[c] = 0u;
       }
-      mbar_arrive(&bars[B::raw_free + rs]);  // the row is in registers: the stage may be refilled
+      mbar_arrive(&bars[B::raw_free + rs]);  // the half row is in registers: the stage may be refilled
       const int st = j % kRNS;
-      uint8_t* kdst = smem + L::kimg + (j % kRNK) * kWideBytes + pt * 16;
-      uint8_t* vstage = smem + L::vst + st * kRVStage;
-      uint8_t* vdst = vstage + pt * 16;
-      if (j >= kRNK) ok &= wait_or_abort(&bars[B::kempty + j % kRNK], ((j / kRNK) - 1) & 1, abort_flag);
-      if (!odd) {
+      if (!v_part) {
+        uint8_t* kdst = smem + L::kimg + (j % kRNK) * kWideBytes + pt * 16;
+        if (j >= kRNK) RSTAT(1, ok &= wait_or_abort(&bars[B::kempty + j % kRNK], ((j / kRNK) - 1) & 1, abort_flag))
+        float* ksc = reinterpret_cast<float*>(smem + L::ksc) + (j % kRKsRing) * kTileKeys;
+        if (!odd) {
 #pragma unroll
-        for (int c = 0; c < kChunks; ++c)
-          *reinterpret_cast<uint4*>(kdst + c * kChunkStride) = widen8_bf16(make_uint2(w[2 * c], w[2 * c + 1]));
+          for (int c = 0; c < kChunks; ++c)
+            *reinterpret_cast<uint4*>(kdst + c * kChunkStride) = widen8_bf16(make_uint2(w[2 * c], w[2 * c + 1]));
+          ksc[pt] = __uint_as_float(w[32]) * p.scale_log2;
+        } else {
+#pragma unroll
+          for (int c = 0; c < kChunks; ++c)
+            *reinterpret_cast<uint4*>(kdst + c * kChunkStride) = widen8_bf16(make_uint2(w[2 + 2 * c], w[3 + 2 * c]));
+          ksc[pt] = __uint_as_float(w[34]) * p.scale_log2;
+        }
+        tc::fence_async_smem();
+        mbar_arrive(&bars[B::kfull + j % kRNK]);
       } else {
+        uint8_t* vstage = smem + L::vst + st * kRVStage;
+        uint8_t* vdst = vstage + pt * 16;
+        if (j >= kRNS) RSTAT(2, ok &= wait_or_abort(&bars[B::vempty + st], ((j / kRNS) - 1) & 1, abort_flag))
+        if (!odd) {
 #pragma unroll
-        for (int c = 0; c < kChunks; ++c)
-          *reinterpret_cast<uint4*>(kdst + c * kChunkStride) = widen8_bf16(make_uint2(w[2 + 2 * c], w[3 + 2 * c]));
+          for (int c = 0; c < kChunks; ++c)
+            *reinterpret_cast<uint4*>(vdst + c * kChunkStride) = widen8_bf16(make_uint2(w[1 + 2 * c], w[2 + 2 * c]));
+          *reinterpret_cast<uint32_t*>(vstage + kWideBytes + pt * 4) = w[33];
+        } else {
+#pragma unroll
+          for (int c = 0; c < kChunks; ++c)
+            *reinterpret_cast<uint4*>(vdst + c * kChunkStride) = widen8_bf16(make_uint2(w[3 + 2 * c], w[4 + 2 * c]));
+          *reinterpret_cast<uint32_t*>(vstage + kWideBytes + pt * 4) = w[35];
+        }
+        tc::fence_async_smem();
+        mbar_arrive(&bars[B::vfull + st]);
       }
-      if (j >= kRNS) ok &= wait_or_abort(&bars[B::vempty + st], ((j / kRNS) - 1) & 1, abort_flag);
-      if (!odd) {
-#pragma unroll
-        for (int c = 0; c < kChunks; ++c)
-          *reinterpret_cast<uint4*>(vdst + c * kChunkStride) = widen8_bf16(make_uint2(w[33 + 2 * c], w[34 + 2 * c]));
-        *reinterpret_cast<uint32_t*>(vstage + kWideBytes + pt * 4) = w[32];
-        *reinterpret_cast<uint32_t*>(vstage + kWideBytes + kTileKeys * 4 + pt * 4) = w[65];
-      } else {
-#pragma unroll
-        for (int c = 0; c < kChunks; ++c)
-          *reinterpret_cast<uint4*>(vdst + c * kChunkStride) = widen8_bf16(make_uint2(w[35 + 2 * c], w[36 + 2 * c]));
-        *reinterpret_cast<uint32_t*>(vstage + kWideBytes + pt * 4) = w[34];
-        *reinterpret_cast<uint32_t*>(vstage + kWideBytes + kTileKeys * 4 + pt * 4) = w[67];
-      }
-      tc::fence_async_smem();
-      mbar_arrive(&bars[B::full + st]);
     }
+    if (pt == 0 && !v_part) { RSTAT_FLUSH(0) }
   } else if (warp == kRLoadWarp) {
     // =========================== loader =======================================
     // One TMA copy per KV page of a tile, issued by lane `page`: a tiled tensor-map box of
@@ -284,31 +317,35 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
     // =========================== QK issuer ====================================
     named_barrier(5, kRSoftmax + 32);  // wait for the Q image
     if (lane == 0) {
+      RSTAT_DECL
       const uint32_t qimg_s = tc::smem_u32(qimg);
 #pragma unroll 1
       for (int i = 0; i < n_tiles; ++i) {
         const int g = i & 1, k = i >> 1;
-        ok &= wait_or_abort(&bars[B::full + i % kRNS], (i / kRNS) & 1, abort_flag);
+        RSTAT(0, ok &= wait_or_abort(&bars[B::kfull + i % kRNK], (i / kRNK) & 1, abort_flag))
         // S(g) doubles as P(g): free once the PV of this group's previous tile has read it
-        if (k >= 1) ok &= wait_or_abort(&bars[B::pv_done + g], (k - 1) & 1, abort_flag);
+        if (k >= 1) RSTAT(1, ok &= wait_or_abort(&bars[B::pv_done + g], (k - 1) & 1, abort_flag))
         tc::fence_after_sync();
         issue_qk_rows(tmem_base + g * 128, qimg_s, kimg_s + (i % kRNK) * kWideBytes);
         tc::mma_commit(&bars[B::s_ready + g]);
         tc::mma_commit(&bars[B::kempty + i % kRNK]);
       }
+      RSTAT_FLUSH(1)
     }
   } else if (warp == kRPvWarp) {
     // =========================== PV issuer ====================================
     if (lane == 0) {
+      RSTAT_DECL
 #pragma unroll 1
       for (int i = 0; i < n_tiles; ++i) {
         const int g = i & 1, k = i >> 1;
-        ok &= wait_or_abort(&bars[B::p_ready + g], k & 1, abort_flag);
+        RSTAT(0, ok &= wait_or_abort(&bars[B::p_ready + g], k & 1, abort_flag))
         tc::fence_after_sync();
         issue_pv_rows(tmem_base + 256 + g * 128, tmem_base + g * 128, vst_s + (i % kRNS) * kRVStage, k > 0);
         tc::mma_commit(&bars[B::pv_done + g]);
         tc::mma_commit(&bars[B::vempty + i % kRNS]);
       }
+      RSTAT_FLUSH(2)
     }
   } else if (warp < 8) {
     // =========================== softmax ======================================
@@ -341,44 +378,56 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
     visible_range(p, t, t.first_idx + t.ntok - 1, &mask_lo, &tmp);
     visible_range(p, t, t.first_idx, &tmp, &mask_hi);
 
+    RSTAT_DECL
     float m_ref = -INFINITY;  // reference maximum of the row's exponentials (log2 units)
     float l = 0.f;            // sum of exp2(score - m_ref)
     int it = 0;
 #pragma unroll 1
     for (int i = g; i < n_tiles; i += 2, ++it) {
-      const float* ksp = reinterpret_cast<const float*>(smem + L::vst + (i % kRNS) * kRVStage + kWideBytes);
-      const float* vsp = ksp + kTileKeys;
+      const float* ksp = reinterpret_cast<const float*>(smem + L::ksc) + (i % kRKsRing) * kTileKeys;
+      const float* vsp = reinterpret_cast<const float*>(smem + L::vst + (i % kRNS) * kRVStage + kWideBytes);
       const int pos0 = (tile_begin + i) * kTileKeys;
       const bool interior = pos0 >= mask_lo && pos0 + (kTileKeys - 1) <= mask_hi;
-      ok &= wait_or_abort(&bars[B::s_ready + g], it & 1, abort_flag);
+      RSTAT(0, ok &= wait_or_abort(&bars[B::s_ready + g], it & 1, abort_flag))
       tc::fence_after_sync();
+#ifdef PTHB200_ROWS_STATS
+      const long long tp1_ = clock64();
+#endif
 
       // ---- pass 1: maximum of the row's scores in this tile ----
+      // (two instances: interior tiles, which every live row sees whole, skip the mask)
       float m_t = -INFINITY;
+      auto pass1 = [&](auto masked) {
+        constexpr bool kMask = decltype(masked)::value;
 #pragma unroll 1
-      for (int j = 0; j < 4; ++j) {
-        uint32_t r[32];
-        tc::tmem_ld32(s_tmem + j * 32, r);
-        tc::tmem_ld_wait();
-        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        for (int j = 0; j < 4; ++j) {
+          uint32_t r[32];
+          tc::tmem_ld32(s_tmem + j * 32, r);
+          tc::tmem_ld_wait();
+          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int n4 = 0; n4 < 8; ++n4) {
-          const float4 ks4 = reinterpret_cast<const float4*>(ksp)[j * 8 + n4];
-          const float kk[4] = {ks4.x, ks4.y, ks4.z, ks4.w};
+          for (int n4 = 0; n4 < 8; ++n4) {
+            const float4 ks4 = reinterpret_cast<const float4*>(ksp)[j * 8 + n4];  // k_scale * scale * log2 e
+            const float kk[4] = {ks4.x, ks4.y, ks4.z, ks4.w};
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int n = n4 * 4 + e;
-            float s = __uint_as_float(r[n]) * (kk[e] * p.scale_log2);
-            if (!interior) {
-              const int pos = pos0 + j * 32 + n;
-              s = (pos >= rlo && pos <= rhi) ? s : -INFINITY;
+            for (int e = 0; e < 4; ++e) {
+              const int n = n4 * 4 + e;
+              float s = __uint_as_float(r[n]) * kk[e];
+              if constexpr (kMask) {
+                const int pos = pos0 + j * 32 + n;
+                s = (pos >= rlo && pos <= rhi) ? s : -INFINITY;
+              }
+              mx[e] = fmaxf(mx[e], s);
             }
-            mx[e] = fmaxf(mx[e], s);
           }
+          m_t = fmaxf(m_t, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])));
         }
-        m_t = fmaxf(m_t, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])));
-      }
-
+      };
+      if (interior) pass1(std::false_type{}); else pass1(std::true_type{});
+#ifdef PTHB200_ROWS_STATS
+      st_[1] += clock64() - tp1_;
+      const long long tp2_ = clock64();
+#endif
       // ---- move the reference maximum if the row has outgrown it ----
       const float m_new = fmaxf(m_ref, m_t);
       const bool need = m_t > m_ref + kRescaleGap;  // also true when m_ref is still -inf
@@ -403,43 +452,54 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
         if (need) m_ref = m_new;
       }
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+#ifdef PTHB200_ROWS_STATS
+      st_[2] += clock64() - tp2_;
+      const long long tp3_ = clock64();
+#endif
 
       // ---- pass 2: p * v_scale as packed bf16 over the columns of S already read ----
+      RSTAT(5, ok &= wait_or_abort(&bars[B::vfull + i % kRNS], (i / kRNS) & 1, abort_flag))  // v_scale (and V) of tile i
+      auto pass2 = [&](auto masked) {
+        constexpr bool kMask = decltype(masked)::value;
 #pragma unroll 1
-      for (int j = 0; j < 4; ++j) {
-        uint32_t r[32];
-        tc::tmem_ld32(s_tmem + j * 32, r);
-        tc::tmem_ld_wait();
-        uint32_t pk[16];
-        float ls[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int j = 0; j < 4; ++j) {
+          uint32_t r[32];
+          tc::tmem_ld32(s_tmem + j * 32, r);
+          tc::tmem_ld_wait();
+          uint32_t pk[16];
+          float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int n4 = 0; n4 < 8; ++n4) {
-          const float4 ks4 = reinterpret_cast<const float4*>(ksp)[j * 8 + n4];
-          const float4 vs4 = reinterpret_cast<const float4*>(vsp)[j * 8 + n4];
-          const float kk[4] = {ks4.x, ks4.y, ks4.z, ks4.w};
-          const float vv[4] = {vs4.x, vs4.y, vs4.z, vs4.w};
-          float pv[4];
+          for (int n4 = 0; n4 < 8; ++n4) {
+            const float4 ks4 = reinterpret_cast<const float4*>(ksp)[j * 8 + n4];
+            const float4 vs4 = reinterpret_cast<const float4*>(vsp)[j * 8 + n4];
+            const float kk[4] = {ks4.x, ks4.y, ks4.z, ks4.w};
+            const float vv[4] = {vs4.x, vs4.y, vs4.z, vs4.w};
+            float pv[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int n = n4 * 4 + e;
-            float pr = ex2f(fmaf(__uint_as_float(r[n]), kk[e] * p.scale_log2, -m_use));
-            if (!interior) {
-              const int pos = pos0 + j * 32 + n;
-              pr = (pos >= rlo && pos <= rhi) ? pr : 0.f;
+            for (int e = 0; e < 4; ++e) {
+              const int n = n4 * 4 + e;
+              float pr = ex2f(fmaf(__uint_as_float(r[n]), kk[e], -m_use));
+              if constexpr (kMask) {
+                const int pos = pos0 + j * 32 + n;
+                pr = (pos >= rlo && pos <= rhi) ? pr : 0.f;
+              }
+              ls[e] += pr;
+              pv[e] = pr * vv[e];
             }
-            ls[e] += pr;
-            pv[e] = pr * vv[e];
+            pk[n4 * 2] = pack_bf16(pv[0], pv[1]);
+            pk[n4 * 2 + 1] = pack_bf16(pv[2], pv[3]);
           }
-          pk[n4 * 2] = pack_bf16(pv[0], pv[1]);
-          pk[n4 * 2 + 1] = pack_bf16(pv[2], pv[3]);
+          l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+          tc::tmem_st16(s_tmem + j * 16, pk);
         }
-        l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-        tc::tmem_st16(s_tmem + j * 16, pk);
-      }
-      tc::tmem_st_wait();
-      tc::fence_before_sync();
-      mbar_arrive(&bars[B::p_ready + g]);  // P of tile i complete
+      };
+      if (interior) pass2(std::false_type{}); else pass2(std::true_type{});
+#ifdef PTHB200_ROWS_STATS
+      st_[3] += clock64() - tp3_;
+#endif
+      RSTAT(4, tc::tmem_st_wait(); tc::fence_before_sync(); mbar_arrive(&bars[B::p_ready + g]))  // P of tile i complete
     }
+    if (tid == 0) { RSTAT_FLUSH(3) }
 
     // ---- epilogue: merge the two groups' (m, l, O) and write the rows ----
     const int my_tiles = it;
@@ -450,7 +510,8 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
     float* park = reinterpret_cast<float*>(smem + L::raw);  // [d][row] fp32, the raw ring is idle by now
     if (g == 1) {
       // every producer has finished reading the raw ring once the last tile's images are full
-      ok &= wait_or_abort(&bars[B::full + (n_tiles - 1) % kRNS], ((n_tiles - 1) / kRNS) & 1, abort_flag);
+      ok &= wait_or_abort(&bars[B::vfull + (n_tiles - 1) % kRNS], ((n_tiles - 1) / kRNS) & 1, abort_flag);
+      ok &= wait_or_abort(&bars[B::kfull + (n_tiles - 1) % kRNK], ((n_tiles - 1) / kRNK) & 1, abort_flag);
       park_m[row] = m_ref;
       park_l[row] = l;
       if (my_tiles > 0) {
@@ -563,5 +624,11 @@ cudaError_t read_rows_status(unsigned int* v) {
 }
 
 }  // namespace pthb200
+
+#ifdef PTHB200_ROWS_STATS
+extern "C" int pthb200_debug_rows_stats(long long* out) {
+  return cudaMemcpyFromSymbol(out, pthb200::g_rows_stats, sizeof(long long) * 48) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 #include "umma_rows_tile_test.cuh"
