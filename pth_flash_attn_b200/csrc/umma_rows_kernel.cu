@@ -11,8 +11,9 @@
 //                         exactly to bf16 into the K image / the V stage (canonical
 //                         no-swizzle layout), with k_scale * softmax_scale * log2 e and
 //                         v_scale of the key;
-//   QK issuer  (1 thread) S = Q K^T, M = 128 rows, N = 128 keys, fp32 in TMEM, one buffer
-//                         per softmax group;
+//   MMA issuer (1 thread) S = Q K^T (M = 128 rows, N = 128 keys, fp32 in TMEM, one buffer
+//                         per softmax group) and O += P V with P read from TMEM (the A
+//                         operand), V from the V stage as an MN-major B operand;
 //   softmax    (2 groups of 4 warps; group g owns the tiles i with i % 2 == g) thread r:
 //                         pass 1 finds the tile maximum of row r (score = S * k_scale *
 //                         softmax_scale * log2 e), pass 2 writes p * v_scale as packed bf16
@@ -20,8 +21,6 @@
 //                         reference maximum of a row moves only when the running maximum
 //                         outgrows it by 2^8; then the thread rescales its row of O in
 //                         TMEM.  In steady state O is never touched by the softmax;
-//   PV issuer  (1 thread) O += P V with P read from TMEM (the A operand), V from the
-//                         V stage as an MN-major B operand, N = 128 (d), fp32 in TMEM.
 // The two groups' (m, l, O) are merged in the epilogue.  TMEM: S0 S1 O0 O1, 128 columns
 // each.  Every mbarrier wait is bounded (see page_copy.cuh).
 #include <cuda.h>
@@ -52,15 +51,14 @@ namespace {
 constexpr int kRGroup = 128;             // threads of one softmax group = rows of a tile
 constexpr int kRSoftmax = 2 * kRGroup;   // warps 0-3, 4-7
 constexpr int kRProducers = 256;         // warps 8-11 (K half) and 12-15 (V half)
-constexpr int kRQkWarp = 16, kRPvWarp = 17, kRLoadWarp = 18;
-constexpr int kRThreads = 608;
-constexpr int kRNK = 1;                  // K images
-constexpr int kRNS = 2;                  // V stages (V image + both scale vectors)
-constexpr int kRNR = 2;                  // raw stages
+constexpr int kRMmaWarp = 16, kRLoadWarp = 17;
+constexpr int kRThreads = 576;
+constexpr int kRNS = 2;                  // V stages (V image + v_scale)
 constexpr int kRVStage = kWideBytes + kTileKeys * 4;  // V image + v_scale[128]
 constexpr int kRKsRing = 4;                          // tiles of scaled k_scale vectors kept
 constexpr float kRescaleGap = 8.0f;      // log2 units a row maximum may outgrow its reference
 
+template <int kRNK, int kRNR>  // K images, raw stages
 struct RLayout {
   static constexpr int kimg = 0;
   static constexpr int vst = kimg + kRNK * kWideBytes;
@@ -74,9 +72,8 @@ struct RLayout {
   static constexpr int misc = bars + n_bars * 8;
   static constexpr int total = misc + 16;
 };
-static_assert(RLayout::raw % 128 == 0 && RLayout::vst % 128 == 0 && RLayout::qimg % 128 == 0, "TMA / image alignment");
-static_assert(RLayout::total <= 227 * 1024, "shared memory of one CTA");
 
+template <int kRNK, int kRNR>
 struct RBars {
   static constexpr int vfull = 0;                      // [NS] V producers -> softmax (pass 2), 128 arrivals
   static constexpr int vempty = kRNS;                  // [NS] PV commit -> V producers
@@ -99,10 +96,13 @@ __device__ __forceinline__ float ex2f(float x) {
   return y;
 }
 
+template <int kRNK, int kRNR>
 __global__ void __launch_bounds__(kRThreads, 1)
 umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_constant__ CUtensorMap tmap) {
-  using L = RLayout;
-  using B = RBars;
+  using L = RLayout<kRNK, kRNR>;
+  using B = RBars<kRNK, kRNR>;
+  static_assert(L::raw % 128 == 0 && L::vst % 128 == 0 && L::qimg % 128 == 0, "TMA / image alignment");
+  static_assert(L::total <= 227 * 1024, "shared memory of one CTA");
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* qimg = smem + L::qimg;
   float* park_m = reinterpret_cast<float*>(smem + L::park_m);
@@ -194,7 +194,7 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
   const uint32_t kimg_s = tc::smem_u32(smem + L::kimg), vst_s = tc::smem_u32(smem + L::vst);
   bool ok = true;
 
-  if (warp >= 8 && warp < kRQkWarp) {
+  if (warp >= 8 && warp < kRMmaWarp) {
     // =========================== producers ====================================
     // Warps 8-11 widen the K half of the raw cells into the K image, warps 12-15 the V half
     // (and both scales) into the V stage; thread pt of either set owns key pt of the tile.
@@ -313,39 +313,42 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
         blk = blk_next;
       }
     }
-  } else if (warp == kRQkWarp) {
-    // =========================== QK issuer ====================================
+  } else if (warp == kRMmaWarp) {
+    // =========================== MMA issuer ===================================
+    // ONE thread issues every tcgen05.mma of the CTA.  (A version with one issuing thread
+    // for QK and another for PV produced results that varied from run to run; with a single
+    // issuing thread they do not.)  Order: QK(0), QK(1), then for each tile i: PV(i) as soon
+    // as its P is complete, and QK(i + 2) once PV(i) has finished reading P(g), whose
+    // columns S(g) shares.
     named_barrier(5, kRSoftmax + 32);  // wait for the Q image
     if (lane == 0) {
       RSTAT_DECL
       const uint32_t qimg_s = tc::smem_u32(qimg);
-#pragma unroll 1
-      for (int i = 0; i < n_tiles; ++i) {
-        const int g = i & 1, k = i >> 1;
+      auto issue_qk = [&](int i) {
+        const int g = i & 1;
         RSTAT(0, ok &= wait_or_abort(&bars[B::kfull + i % kRNK], (i / kRNK) & 1, abort_flag))
-        // S(g) doubles as P(g): free once the PV of this group's previous tile has read it
-        if (k >= 1) RSTAT(1, ok &= wait_or_abort(&bars[B::pv_done + g], (k - 1) & 1, abort_flag))
         tc::fence_after_sync();
         issue_qk_rows(tmem_base + g * 128, qimg_s, kimg_s + (i % kRNK) * kWideBytes);
         tc::mma_commit(&bars[B::s_ready + g]);
         tc::mma_commit(&bars[B::kempty + i % kRNK]);
-      }
-      RSTAT_FLUSH(1)
-    }
-  } else if (warp == kRPvWarp) {
-    // =========================== PV issuer ====================================
-    if (lane == 0) {
-      RSTAT_DECL
+      };
+      issue_qk(0);
+      if (n_tiles > 1) issue_qk(1);
 #pragma unroll 1
       for (int i = 0; i < n_tiles; ++i) {
         const int g = i & 1, k = i >> 1;
-        RSTAT(0, ok &= wait_or_abort(&bars[B::p_ready + g], k & 1, abort_flag))
+        RSTAT(2, ok &= wait_or_abort(&bars[B::p_ready + g], k & 1, abort_flag))
         tc::fence_after_sync();
         issue_pv_rows(tmem_base + 256 + g * 128, tmem_base + g * 128, vst_s + (i % kRNS) * kRVStage, k > 0);
         tc::mma_commit(&bars[B::pv_done + g]);
         tc::mma_commit(&bars[B::vempty + i % kRNS]);
+        if (i + 2 < n_tiles) {
+          // S(g) doubles as P(g): it is free once this PV has completed
+          RSTAT(1, ok &= wait_or_abort(&bars[B::pv_done + g], k & 1, abort_flag))
+          issue_qk(i + 2);
+        }
       }
-      RSTAT_FLUSH(2)
+      RSTAT_FLUSH(1)
     }
   } else if (warp < 8) {
     // =========================== softmax ======================================
@@ -507,11 +510,21 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
       ok &= wait_or_abort(&bars[B::pv_done + g], (my_tiles - 1) & 1, abort_flag);
       tc::fence_after_sync();
     }
-    float* park = reinterpret_cast<float*>(smem + L::raw);  // [d][row] fp32, the raw ring is idle by now
+    // Group 1 hands its state to group 0 through 64 KB of shared memory that is idle by
+    // now: the K images if they are large enough (every QK has completed once the last
+    // tile's K image has been released), else the raw ring (every producer has read it
+    // once the last tile's images are full).
+    constexpr int kParkBytes = kRGroup * kHeadDim * 4;
+    constexpr bool kParkInK = kRNK * kWideBytes >= kParkBytes;
+    static_assert(kParkInK || kRNR * kRawStageBytes >= kParkBytes, "no idle region holds the parked accumulator");
+    float* park = reinterpret_cast<float*>(smem + (kParkInK ? L::kimg : L::raw));  // [d][row] fp32
     if (g == 1) {
-      // every producer has finished reading the raw ring once the last tile's images are full
-      ok &= wait_or_abort(&bars[B::vfull + (n_tiles - 1) % kRNS], ((n_tiles - 1) / kRNS) & 1, abort_flag);
-      ok &= wait_or_abort(&bars[B::kfull + (n_tiles - 1) % kRNK], ((n_tiles - 1) / kRNK) & 1, abort_flag);
+      if constexpr (kParkInK) {
+        ok &= wait_or_abort(&bars[B::kempty + (n_tiles - 1) % kRNK], ((n_tiles - 1) / kRNK) & 1, abort_flag);
+      } else {
+        ok &= wait_or_abort(&bars[B::vfull + (n_tiles - 1) % kRNS], ((n_tiles - 1) / kRNS) & 1, abort_flag);
+        ok &= wait_or_abort(&bars[B::kfull + (n_tiles - 1) % kRNK], ((n_tiles - 1) / kRNK) & 1, abort_flag);
+      }
       park_m[row] = m_ref;
       park_l[row] = l;
       if (my_tiles > 0) {
@@ -592,6 +605,24 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
 // page copies) and takes bf16 queries.
 bool umma_rows_supports(const KernelParams& p, const char** why) { return umma_i8_supports(p, why); }
 
+namespace {
+template <int NK, int NR>
+cudaError_t launch_rows(const KernelParams& p, const CUtensorMap& map, dim3 grid, cudaStream_t stream) {
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    err = cudaFuncSetAttribute(umma_rows_attention_kernel<NK, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               RLayout<NK, NR>::total);
+    if (err != cudaSuccess) return err;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  umma_rows_attention_kernel<NK, NR><<<grid, kRThreads, RLayout<NK, NR>::total, stream>>>(p, map);
+  return cudaGetLastError();
+}
+}  // namespace
+
 cudaError_t launch_umma_rows_attention(const KernelParams& p_in, cudaStream_t stream) {
   KernelParams p = p_in;
   // Row tiles of 128 rows, whatever tile height the caller planned with: the partition of
@@ -601,18 +632,10 @@ cudaError_t launch_umma_rows_attention(const KernelParams& p_in, cudaStream_t st
   p.raw_mode = raw_mode_for(p);
   CUtensorMap map{};
   if (p.raw_mode == 1 && !make_page_map(p, p.num_blocks, &map)) return cudaErrorInvalidValue;
-  static bool configured[64] = {};
-  int dev = 0;
-  cudaError_t err = cudaGetDevice(&dev);
-  if (err != cudaSuccess) return err;
-  if (dev < 0 || dev >= 64 || !configured[dev]) {
-    err = cudaFuncSetAttribute(umma_rows_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RLayout::total);
-    if (err != cudaSuccess) return err;
-    if (dev >= 0 && dev < 64) configured[dev] = true;
-  }
+  // One K image and two raw stages.  (Two K images with a single raw stage measured
+  // slower on prefill: the producers then wait for the page copies.)
   const dim3 grid(p.num_q_tiles, p.num_kv_heads, p.num_splits);
-  umma_rows_attention_kernel<<<grid, kRThreads, RLayout::total, stream>>>(p, map);
-  return cudaGetLastError();
+  return launch_rows<1, 2>(p, map, grid, stream);
 }
 
 // Reads and clears this file's status word (device must be idle).
