@@ -81,8 +81,8 @@ constexpr int kGroupThreads = 128;                      // one softmax warpgroup
 constexpr int kSoftmaxThreads = 2 * kGroupThreads;      // warps 0-3 and 4-7
 constexpr int kProducerThreads = 128;                   // one producer group: one thread per key of a tile
 // Warps after the softmax groups: NP producer groups of four warps (group k realigns the
-// tiles j with j % NP == k), then the QK issuer, the PV issuer and the loader warp.
-__host__ __device__ constexpr int threads_for(int np) { return kSoftmaxThreads + np * kProducerThreads + 96; }
+// tiles j with j % NP == k), then the MMA issuer and the loader warp.
+__host__ __device__ constexpr int threads_for(int np) { return kSoftmaxThreads + np * kProducerThreads + 64; }
 constexpr int kStageScales = 2 * kKeys * 4;                 // k_scale[128], v_scale[128]
 constexpr int kVStageBytes = kImgBytes + kStageScales;      // V image and both scale vectors of one tile
 
@@ -132,9 +132,8 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
   constexpr int kRawStages = NR;
   constexpr int XMAX = (1 << (7 * PD)) - 1;
   constexpr int kThreads = threads_for(NP);
-  constexpr int kQkWarp = 8 + 4 * NP;   // lane 0 issues the S^T = K Q^T MMAs
-  constexpr int kPvWarp = kQkWarp + 1;  // lane 0 issues the O^T = V^T P MMAs
-  constexpr int kLoadWarp = kQkWarp + 2;  // issues the page copies
+  constexpr int kMmaWarp = 8 + 4 * NP;     // lane 0 issues every MMA
+  constexpr int kLoadWarp = kMmaWarp + 1;  // issues the page copies
   static_assert(RQ >= 1 && 4 * RQ <= NPAD, "RQ = groups of four rows the softmax handles (rows <= 4 RQ)");
   static_assert(NS >= 2, "two image stages: one feeding the MMAs, one being filled");
   STAT_ENTRY
@@ -244,7 +243,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
   bool ok = true;
   STAT_MARK(1)
 
-  if (warp >= 8 && warp < kQkWarp) {
+  if (warp >= 8 && warp < kMmaWarp) {
     // =========================== producers ====================================
     const int pgrp = (warp - 8) >> 2;                              // producer group
     const int pt = (tid - kSoftmaxThreads) & (kProducerThreads - 1);  // key of the tile this thread resolves
@@ -381,44 +380,62 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
         blk = blk_next;
       }
     }
-  } else if (warp == kQkWarp) {
-    // =========================== QK issuer ====================================
-    // Tile i belongs to softmax group g = i & 1; it is that group's k-th tile (k = i >> 1)
-    // and its S^T lands in the group's buffer k % SB.  This thread runs ahead of the softmax
-    // as far as the image stages and the S^T buffers allow.
+  } else if (warp == kMmaWarp) {
+    // =========================== MMA issuer ===================================
+    // ONE thread issues every tcgen05.mma of the CTA (two issuing threads, one for QK and
+    // one for PV, produced rare run-to-run differences).  It keeps two cursors and issues
+    // whichever MMA chain is ready, so a QK that waits for its images never holds up a PV
+    // whose P is complete, and the other way round:
+    //   QK(i): tile i is the k-th tile (k = i >> 1) of softmax group g = i & 1 and lands in
+    //          that group's S^T buffer k % SB; needs the tile's images (full) and that
+    //          buffer read by the softmax (s_free);
+    //   PV(i): needs the group's P image (p_ready) and its O^T buffer folded (o_free); its
+    //          completion frees the V stage.
     named_barrier(5, kSoftmaxThreads + 32);  // wait for the Q image
     if (lane == 0) {
       STAT_DECL
-      const uint32_t qimg_s = tc::smem_u32(qimg);
+      const uint32_t qimg_s = tc::smem_u32(qimg), pimg_s = tc::smem_u32(pimg);
+      int iq = 0, ip = 0;
+      uint32_t idle = 0;
+      const long long deadline = clock64() + (1ll << 33);
 #pragma unroll 1
-      for (int i = 0; i < n_tiles; ++i) {
-        const int g = i & 1, k = i >> 1, sb = k % SB;
-        STAT_WAIT(0, ok &= wait_or_abort(&bars[B::full + i % NS], (i / NS) & 1, abort_flag))
-        if (k >= SB) STAT_WAIT(1, ok &= wait_or_abort(&bars[B::s_free + 2 * g + sb], ((k / SB) - 1) & 1, abort_flag))
-        tc::fence_after_sync();
-        issue_qk_i8<NPAD>(tmem_base + (g * SB + sb) * L::s_cols, kstage0 + (i % NK) * kImgBytes, qimg_s);
-        tc::mma_commit(&bars[B::s_ready + 2 * g + sb]);
-        tc::mma_commit(&bars[B::kempty + i % NK]);  // the K image is dead once S^T exists
+      while (ip < n_tiles) {
+        bool issued = false;
+        if (iq < n_tiles) {
+          const int g = iq & 1, k = iq >> 1, sb = k % SB;
+          if (tc::mbar_test_wait(&bars[B::full + iq % NS], (iq / NS) & 1) &&
+              (k < SB || tc::mbar_test_wait(&bars[B::s_free + 2 * g + sb], ((k / SB) - 1) & 1))) {
+            tc::fence_after_sync();
+            issue_qk_i8<NPAD>(tmem_base + (g * SB + sb) * L::s_cols, kstage0 + (iq % NK) * kImgBytes, qimg_s);
+            tc::mma_commit(&bars[B::s_ready + 2 * g + sb]);
+            tc::mma_commit(&bars[B::kempty + iq % NK]);  // the K image is dead once S^T exists
+            ++iq;
+            issued = true;
+          }
+        }
+        if (ip < iq) {
+          const int g = ip & 1;
+          if (tc::mbar_test_wait(&bars[B::p_ready + g], (ip >> 1) & 1) &&
+              (ip < 2 || tc::mbar_test_wait(&bars[B::o_free + g], ((ip >> 1) - 1) & 1))) {
+            tc::fence_after_sync();
+            issue_pv_i8<NPAD, PD>(tmem_base + L::s_total + g * L::o_cols, vstage0 + (ip % NS) * kVStageBytes,
+                                  pimg_s + g * (PD * NPAD * kKeys));
+            tc::mma_commit(&bars[B::o_ready + g]);
+            tc::mma_commit(&bars[B::empty + ip % NS]);
+            ++ip;
+            issued = true;
+          }
+        }
+        if (!issued && (++idle & 63u) == 0u) {
+          // nothing ready for a while: check the abort flag and the deadline (about four seconds)
+          if (*abort_flag) break;
+          if (clock64() > deadline) {
+            *abort_flag = 1;
+            break;
+          }
+        }
       }
       STAT_FLUSH(1)
-    }
-  } else if (warp == kPvWarp) {
-    // =========================== PV issuer ====================================
-    // O^T of tile i goes to its group's TMEM buffer; its completion also frees the image
-    // stage (the QK of the same tile finished before the softmax could produce P).
-    if (lane == 0) {
-      const uint32_t pimg_s = tc::smem_u32(pimg);
-#pragma unroll 1
-      for (int i = 0; i < n_tiles; ++i) {
-        const int g = i & 1;
-        ok &= wait_or_abort(&bars[B::p_ready + g], (i >> 1) & 1, abort_flag);
-        if (i >= 2) ok &= wait_or_abort(&bars[B::o_free + g], ((i >> 1) - 1) & 1, abort_flag);
-        tc::fence_after_sync();
-        issue_pv_i8<NPAD, PD>(tmem_base + L::s_total + g * L::o_cols, vstage0 + (i % NS) * kVStageBytes,
-                              pimg_s + g * (PD * NPAD * kKeys));
-        tc::mma_commit(&bars[B::o_ready + g]);
-        tc::mma_commit(&bars[B::empty + i % NS]);
-      }
     }
   } else if (warp < 2 * 4) {
     // =========================== softmax ======================================
