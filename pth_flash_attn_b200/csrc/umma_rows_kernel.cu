@@ -235,7 +235,11 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
       const int st = j % kRNS;
       if (!v_part) {
         uint8_t* kdst = smem + L::kimg + (j % kRNK) * kWideBytes + pt * 16;
+#ifdef EXP_H
+        if (j >= 1) RSTAT(1, ok &= wait_or_abort(&bars[B::s_ready + ((j - 1) & 1)], ((j - 1) >> 1) & 1, abort_flag))
+#else
         if (j >= kRNK) RSTAT(1, ok &= wait_or_abort(&bars[B::kempty + j % kRNK], ((j / kRNK) - 1) & 1, abort_flag))
+#endif
         float* ksc = reinterpret_cast<float*>(smem + L::ksc) + (j % kRKsRing) * kTileKeys;
         if (!odd) {
 #pragma unroll
@@ -253,7 +257,11 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
       } else {
         uint8_t* vstage = smem + L::vst + st * kRVStage;
         uint8_t* vdst = vstage + pt * 16;
+#ifdef EXP_H
+        if (j >= 2) RSTAT(2, ok &= wait_or_abort(&bars[B::pv_done + (j & 1)], ((j >> 1) - 1) & 1, abort_flag))
+#else
         if (j >= kRNS) RSTAT(2, ok &= wait_or_abort(&bars[B::vempty + st], ((j / kRNS) - 1) & 1, abort_flag))
+#endif
         if (!odd) {
 #pragma unroll
           for (int c = 0; c < kChunks; ++c)
@@ -330,7 +338,12 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
         tc::fence_after_sync();
         issue_qk_rows(tmem_base + g * 128, qimg_s, kimg_s + (i % kRNK) * kWideBytes);
         tc::mma_commit(&bars[B::s_ready + g]);
+#ifndef EXP_H
         tc::mma_commit(&bars[B::kempty + i % kRNK]);
+#endif
+#ifdef EXP_E
+        ok &= wait_or_abort(&bars[B::s_ready + g], (i >> 1) & 1, abort_flag);
+#endif
       };
       issue_qk(0);
       if (n_tiles > 1) issue_qk(1);
@@ -338,10 +351,18 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
       for (int i = 0; i < n_tiles; ++i) {
         const int g = i & 1, k = i >> 1;
         RSTAT(2, ok &= wait_or_abort(&bars[B::p_ready + g], k & 1, abort_flag))
+#ifdef EXP_G
+        ok &= wait_or_abort(&bars[B::vfull + i % kRNS], (i / kRNS) & 1, abort_flag);
+#endif
         tc::fence_after_sync();
         issue_pv_rows(tmem_base + 256 + g * 128, tmem_base + g * 128, vst_s + (i % kRNS) * kRVStage, k > 0);
         tc::mma_commit(&bars[B::pv_done + g]);
+#ifndef EXP_H
         tc::mma_commit(&bars[B::vempty + i % kRNS]);
+#endif
+#ifdef EXP_E
+        ok &= wait_or_abort(&bars[B::pv_done + g], k & 1, abort_flag);
+#endif
         if (i + 2 < n_tiles) {
           // S(g) doubles as P(g): it is free once this PV has completed
           RSTAT(1, ok &= wait_or_abort(&bars[B::pv_done + g], k & 1, abort_flag))
@@ -392,6 +413,9 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
       const int pos0 = (tile_begin + i) * kTileKeys;
       const bool interior = pos0 >= mask_lo && pos0 + (kTileKeys - 1) <= mask_hi;
       RSTAT(0, ok &= wait_or_abort(&bars[B::s_ready + g], it & 1, abort_flag))
+#ifdef EXP_C
+      ok &= wait_or_abort(&bars[B::vfull + i % kRNS], (i / kRNS) & 1, abort_flag);
+#endif
       tc::fence_after_sync();
 #ifdef PTHB200_ROWS_STATS
       const long long tp1_ = clock64();
@@ -433,7 +457,11 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
 #endif
       // ---- move the reference maximum if the row has outgrown it ----
       const float m_new = fmaxf(m_ref, m_t);
+#ifdef EXP_A
+      const bool need = true;
+#else
       const bool need = m_t > m_ref + kRescaleGap;  // also true when m_ref is still -inf
+#endif
       if (it == 0) {
         m_ref = m_new;  // nothing accumulated yet
       } else if (__any_sync(0xffffffffu, need)) {
@@ -499,6 +527,15 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
       if (interior) pass2(std::false_type{}); else pass2(std::true_type{});
 #ifdef PTHB200_ROWS_STATS
       st_[3] += clock64() - tp3_;
+#endif
+#ifdef EXP_B
+      tc::tmem_st_wait();
+      named_barrier(1 + g, kRGroup);
+#endif
+#ifdef EXP_D
+      tc::tmem_st_wait();
+      tc::fence_async_smem();
+      __threadfence_block();
 #endif
       RSTAT(4, tc::tmem_st_wait(); tc::fence_before_sync(); mbar_arrive(&bars[B::p_ready + g]))  // P of tile i complete
     }
