@@ -5,8 +5,8 @@
 // (row, key).  This kernel gives every query row of a 128-row tile one softmax thread
 // (TMEM lane = row), so the row maximum and sum never leave that thread's registers:
 //
-//   loader     (1 warp)   TMA page copies of the raw cache cells into a ring of raw stages
-//                         (same scheme as the integer kernel);
+//   loader     (1 warp)   TMA page copies of the raw cache cells into a ring of raw half
+//                         stages of 64 keys (same scheme as the integer kernel);
 //   producers  (8 warps)  thread t of the K set / V set widens key t's int8 K / V bytes
 //                         exactly to bf16 into the K image / the V stage (canonical
 //                         no-swizzle layout), with k_scale * softmax_scale * log2 e and
@@ -54,17 +54,19 @@ constexpr int kRProducers = 256;         // warps 8-11 (K half) and 12-15 (V hal
 constexpr int kRMmaWarp = 16, kRLoadWarp = 17;
 constexpr int kRThreads = 576;
 constexpr int kRNS = 2;                  // V stages (V image + v_scale)
+constexpr int kHalfKeys = 64;            // keys of one raw half stage
+constexpr int kRawHalfBytes = kHalfKeys * kRawRow;   // 17,408 B
 constexpr int kRVStage = kWideBytes + kTileKeys * 4;  // V image + v_scale[128]
 constexpr int kRKsRing = 4;                          // tiles of scaled k_scale vectors kept
 constexpr float kRescaleGap = 8.0f;      // log2 units a row maximum may outgrow its reference
 
-template <int kRNK, int kRNR>  // K images, raw stages
+template <int kRNK, int kRNR>  // K images, raw HALF stages (64 keys each)
 struct RLayout {
   static constexpr int kimg = 0;
   static constexpr int vst = kimg + kRNK * kWideBytes;
   static constexpr int qimg = vst + kRNS * kRVStage;
   static constexpr int raw = qimg + kQImageBytes;
-  static constexpr int ksc = raw + kRNR * kRawStageBytes;      // float [kRKsRing][128]: k_scale * scale * log2 e
+  static constexpr int ksc = raw + kRNR * kRawHalfBytes;       // float [kRKsRing][128]: k_scale * scale * log2 e
   static constexpr int park_m = ksc + kRKsRing * kTileKeys * 4; // float [128]
   static constexpr int park_l = park_m + kRGroup * 4;          // float [128]
   static constexpr int bars = park_l + kRGroup * 4;            // uint64 [...]
@@ -115,6 +117,7 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // Row tile of this CTA: bisect a shared-memory copy of query_start_loc when it fits.
   constexpr int kQslCache = 4096;
+  static_assert(kRNR * kRawHalfBytes >= 2 * kQslCache * 4, "the raw ring holds the copies of query_start_loc and seq_lens");
   RowTile t;
   if (p.num_reqs + 1 <= kQslCache) {
     int* qsl_s = reinterpret_cast<int*>(smem + L::raw);
@@ -177,8 +180,8 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
       tc::mbar_init(&bars[B::pv_done + g], 1);
     }
     for (int s = 0; s < kRNR; ++s) {
-      tc::mbar_init(&bars[B::raw_full + s], kRawKeys >> p.block_shift);
-      tc::mbar_init(&bars[B::raw_free + s], kRProducers);
+      tc::mbar_init(&bars[B::raw_full + s], kHalfKeys >> p.block_shift);  // pages of a half stage
+      tc::mbar_init(&bars[B::raw_free + s], kRProducers / 2);             // 64 K-set + 64 V-set threads
     }
     *abort_flag = 0;
     tc::mbar_init_fence();
@@ -204,20 +207,24 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
     const uint8_t* kb = p.k.data + (int64_t)kvh * p.k.stride_head;
     const uint32_t delta = (uint32_t)(reinterpret_cast<uintptr_t>(kb) & 15);
     const int row_pitch = p.raw_mode == 1 ? kRawRow : 2 * kHeadDim + 8;
-    const int my_page = pt >> p.block_shift, my_slot = pt & (bs - 1);
-    const uint32_t cell_off = my_page * bs * kRawRow + my_slot * row_pitch + delta;  // inside a raw stage
+    // the raw ring is made of half stages of 64 keys: keys 0-63 of tile j are half stage
+    // u = 2 j, keys 64-127 are u = 2 j + 1; half stage u sits in slot u % kRNR
+    const int half = pt >> 6;
+    const int my_page = (pt & (kHalfKeys - 1)) >> p.block_shift, my_slot = pt & (bs - 1);
+    const uint32_t cell_off = my_page * bs * kRawRow + my_slot * row_pitch + delta;  // inside a half stage
     const bool odd = (cell_off & 8u) != 0;
     RSTAT_DECL
 #pragma unroll 1
     for (int j = 0; j < n_tiles; ++j) {
-      const int rs = j % kRNR;
+      const int u = 2 * j + half;
+      const int rs = u % kRNR;
       const int pos = (tile_begin + j) * kTileKeys + pt;
       const bool valid = pos >= range_begin && pos < range_end;
-      RSTAT(0, ok &= wait_or_abort(&bars[B::raw_full + rs], (j / kRNR) & 1, abort_flag))
+      RSTAT(0, ok &= wait_or_abort(&bars[B::raw_full + rs], (u / kRNR) & 1, abort_flag))
       // nine 16-byte chunks: raw words 0..35 (K half, k_scale) or 32..67 (k_scale, V half, v_scale)
       uint32_t w[36];
       if (valid) {
-        const uint4* row = reinterpret_cast<const uint4*>(smem + L::raw + rs * kRawStageBytes + (cell_off & ~15u)) +
+        const uint4* row = reinterpret_cast<const uint4*>(smem + L::raw + rs * kRawHalfBytes + (cell_off & ~15u)) +
                            (v_part ? 8 : 0);
 #pragma unroll
         for (int c = 0; c < 9; ++c) {
@@ -283,8 +290,8 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
     // One TMA copy per KV page of a tile, issued by lane `page`: a tiled tensor-map box of
     // [block_size slots] x [272 bytes] (raw_mode 1) or one bulk copy of a contiguous page
     // run (raw_mode 2); the next tile's block ids are fetched before waiting for the stage.
-    const int pages_per_tile = kRawKeys >> p.block_shift;
-    if (lane < pages_per_tile) {
+    const int pages_per_half = kHalfKeys >> p.block_shift;
+    if (lane < pages_per_half) {
       const int bs = p.block_size;
       const int32_t* bt = p.block_table + (int64_t)t.req * p.block_table_row_stride;
       const uint8_t* kb = p.k.data + (int64_t)kvh * p.k.stride_head;
@@ -292,20 +299,22 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
       const int tma_x = (int)((reinterpret_cast<uintptr_t>(kb) - delta -
                                (reinterpret_cast<uintptr_t>(p.k.data) & ~(uintptr_t)15)) >> 2);
       const uint32_t raw_s = tc::smem_u32(smem + L::raw);
-      auto page_block = [&](int tile) -> int {
-        const int pos0 = (tile_begin + tile) * kTileKeys + lane * bs;
-        if (tile >= n_tiles || pos0 >= range_end || pos0 + bs <= range_begin) return -1;
+      const int n_halves = 2 * n_tiles;
+      // block id of this lane's page of half stage u, -1 if no key of the page is in range
+      auto page_block = [&](int u) -> int {
+        const int pos0 = tile_begin * kTileKeys + u * kHalfKeys + lane * bs;
+        if (u >= n_halves || pos0 >= range_end || pos0 + bs <= range_begin) return -1;
         return __ldg(bt + (pos0 >> p.block_shift));
       };
       int blk = page_block(0);
 #pragma unroll 1
-      for (int j = 0; j < n_tiles; ++j) {
-        const int blk_next = page_block(j + 1);
-        const int rs = j % kRNR;
-        if (j >= kRNR) ok &= wait_or_abort(&bars[B::raw_free + rs], ((j / kRNR) - 1) & 1, abort_flag);
+      for (int u = 0; u < n_halves; ++u) {
+        const int blk_next = page_block(u + 1);
+        const int rs = u % kRNR;
+        if (u >= kRNR) ok &= wait_or_abort(&bars[B::raw_free + rs], ((u / kRNR) - 1) & 1, abort_flag);
         uint64_t* bar = &bars[B::raw_full + rs];
         if (blk >= 0 && ok) {
-          const uint32_t dst = raw_s + rs * kRawStageBytes + lane * bs * kRawRow;
+          const uint32_t dst = raw_s + rs * kRawHalfBytes + lane * bs * kRawRow;
           if (p.raw_mode == 1) {
             mbar_arrive_expect_tx(bar, bs * kRawRow);
             tma_load_3d(dst, &tmap, tma_x, 0, blk, bar);
@@ -553,7 +562,7 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
     // once the last tile's images are full).
     constexpr int kParkBytes = kRGroup * kHeadDim * 4;
     constexpr bool kParkInK = kRNK * kWideBytes >= kParkBytes;
-    static_assert(kParkInK || kRNR * kRawStageBytes >= kParkBytes, "no idle region holds the parked accumulator");
+    static_assert(kParkInK || kRNR * kRawHalfBytes >= kParkBytes, "no idle region holds the parked accumulator");
     float* park = reinterpret_cast<float*>(smem + (kParkInK ? L::kimg : L::raw));  // [d][row] fp32
     if (g == 1) {
       if constexpr (kParkInK) {
@@ -640,7 +649,14 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
 
 // The row-major kernel reads the cache like the integer kernel (packed cells through TMA
 // page copies) and takes bf16 queries.
-bool umma_rows_supports(const KernelParams& p, const char** why) { return umma_i8_supports(p, why); }
+bool umma_rows_supports(const KernelParams& p, const char** why) {
+  if (!umma_i8_supports(p, why)) return false;
+  if (p.block_shift > 6) {
+    *why = "pages of more than 64 keys";  // a raw half stage holds whole pages of 64 keys in total
+    return false;
+  }
+  return true;
+}
 
 namespace {
 template <int NK, int NR>
@@ -669,10 +685,12 @@ cudaError_t launch_umma_rows_attention(const KernelParams& p_in, cudaStream_t st
   p.raw_mode = raw_mode_for(p);
   CUtensorMap map{};
   if (p.raw_mode == 1 && !make_page_map(p, p.num_blocks, &map)) return cudaErrorInvalidValue;
-  // One K image and two raw stages.  (Two K images with a single raw stage measured
-  // slower on prefill: the producers then wait for the page copies.)
+  // Two K images and three raw half stages (64 keys each).  Consecutive QK MMAs must not read
+  // their K operand from the same shared-memory addresses: with a single K image that the
+  // producers rewrote between two QKs, results varied from run to run although every
+  // producer / consumer edge was ordered by an mbarrier and a proxy fence.
   const dim3 grid(p.num_q_tiles, p.num_kv_heads, p.num_splits);
-  return launch_rows<1, 2>(p, map, grid, stream);
+  return launch_rows<2, 3>(p, map, grid, stream);
 }
 
 // Reads and clears this file's status word (device must be idle).
