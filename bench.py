@@ -513,7 +513,9 @@ def main():
         roof = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                 "traffic": None}
     roof["peak_source"] = peak_src
-    roof["kernel"] = "umma_i8_attention_kernel"
+    # the library sends row tiles of more than 16 rows to the row-major bf16 kernel
+    rows_kernel = any(d.bq * (l["Hq"] // l["Hkv"]) > 16 for l, d in zip(launches, dls))
+    roof["kernel"] = "umma_rows_attention_kernel" if rows_kernel else "umma_i8_attention_kernel"
     roof["kernel_ms_per_step"] = attn_ms
     roof["algorithmic_bytes_per_step"] = step_bytes_local
     if not tensor_bound:
@@ -528,7 +530,7 @@ def main():
         line = {
             "metric": "kv_read_bandwidth", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "us_per_layer": ms_per_step * 1e3,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8",
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16" if rows_kernel else "int8",
             "data": "synthetic",
             "config": {"workload": args.config, "launches": [
                 {"batch": len(l["seq_lens"]), "context_max": max(l["seq_lens"]), "q_len": max(l["q_lens"]),
@@ -536,8 +538,10 @@ def main():
                 "Hq": launches[0]["Hq"], "Hkv": hkv_total, "D": D, "block_size": BS, "sharding": f"kv_heads/{world}",
                 "l2_policy": ("inputs larger than L2" if sets == 1 else f"rotation over {sets} cache sets (>= 4x L2)"),
                 "cuda_graph": bool(graphs),
-                "arithmetic": "int8 cache bytes and int8 digits of Q / P on tcgen05 kind::i8, int32 accumulators, "
-                              "fp32 softmax and output accumulation",
+                "arithmetic": ("int8 cache widened exactly to bf16 in shared memory, tcgen05 kind::f16 with fp32 "
+                               "accumulators in TMEM, fp32 softmax" if rows_kernel else
+                               "int8 cache bytes and int8 digits of Q / P on tcgen05 kind::i8, int32 accumulators, "
+                               "fp32 softmax and output accumulation"),
                 "kv_bytes_per_step": step_bytes_total, "flops_per_step": step_flops_total},
             "tflops": step_flops_total / (ms_per_step * 1e-3) / 1e12,
             "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": ms_e2e,
