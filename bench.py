@@ -59,6 +59,10 @@ def workload_launches(name: str, seed: int = 1001):
         return [dict(seq_lens=[8192] * 64, q_lens=[1] * 64, Hq=32, Hkv=8)]
     if name == "decode_h1":  # one KV head per GPU (the 8-GPU shard shape), same bytes as long_decode_b64
         return [dict(seq_lens=[8192] * 512, q_lens=[1] * 512, Hq=4, Hkv=1)]
+    if name == "shard8_b1":  # what one of 8 GPUs sees of long_decode's first launch
+        return [dict(seq_lens=[131072], q_lens=[1], Hq=4, Hkv=1)]
+    if name == "shard8_b64":  # ... and of its second launch
+        return [dict(seq_lens=[8192] * 64, q_lens=[1] * 64, Hq=4, Hkv=1)]
     if name == "verify4":  # BASELINE config 2a
         return [dict(seq_lens=rng.integers(16384, 32769, size=32).tolist(), q_lens=[4] * 32, Hq=32, Hkv=8)]
     if name == "drafter16":  # BASELINE config 2b

@@ -98,22 +98,22 @@ def test_layouts_and_offsets(layout, pad, offset):
     check_lse(res["lse"], ref.lse, what=layout)
 
 
-def test_combine_skips_garbage_and_padding_rows():
-    """Empty splits (-inf) may hold NaN partials; rows past qsl[R] keep their bytes."""
-    import ctypes
-
-    from pth_flash_attn_b200 import host
-
+@pytest.mark.parametrize("S,D", [(5, 128), (16, 128), (17, 128), (45, 64), (148, 128), (67, 256), (2, 256)])
+def test_combine_skips_garbage_and_padding_rows(S, D):
+    """Empty splits (-inf) may hold NaN partials; rows past qsl[R] keep their bytes.  Above
+    16 splits one CTA owns a row (a quarter of the splits per warp), below one warp does."""
     lib = capi.load_library()
-    S, T, Hq, D = 5, 6, 4, 128
-    rng = np.random.default_rng(1)
+    T, Hq = 6, 4
+    rng = np.random.default_rng(S * 1000 + D)
     ws_o = rng.standard_normal((S, T, Hq, D)).astype(np.float32)
     ws_lse = rng.standard_normal((S, T, Hq)).astype(np.float32) * 3
     ws_lse[1] = -np.inf
+    ws_lse[S - 1, 0] = -np.inf
+    if S > 40:
+        ws_lse[9:31, 1] = -np.inf  # a whole quarter of the splits empty for one token
     ws_lse[:, 2] = -np.inf  # a row with no keys at all
     want, want_l2 = orc.combine_partials(ws_o, ws_lse)
-    ws_o[1] = np.nan
-    ws_o[:, 2] = np.nan
+    ws_o[np.isneginf(ws_lse)] = np.nan
     dev = "cuda"
     o_t, l_t = torch.from_numpy(ws_o).to(dev), torch.from_numpy(ws_lse).to(dev)
     out = torch.full((T, Hq, D), 7.0, dtype=torch.float32, device=dev)
@@ -131,7 +131,7 @@ def test_combine_skips_garbage_and_padding_rows():
     assert lib.combine(a, options=opt) == capi.OK, lib.last_error()
     torch.cuda.synchronize()
     got, got_l = out.cpu().numpy(), lse.cpu().numpy()
-    np.testing.assert_allclose(got[:5], want[:5], rtol=2e-6, atol=2e-6)
+    np.testing.assert_allclose(got[:5], want[:5], rtol=4e-6, atol=4e-6)
     assert (got[2] == 0).all() and np.isneginf(got_l[2]).all()
     assert (got[5] == 7.0).all() and (got_l[5] == 7.0).all(), "padding row was written"
     fin = np.isfinite(want_l2[:5])
