@@ -106,7 +106,7 @@ class DeviceLaunch:
     per-step inputs for the end-to-end leg."""
 
     def __init__(self, torch, launch, hkv_local, hq_local, device, seed, num_sms, sets=1, splits=None, layout="NHD"):
-        from pth_flash_attn_b200 import host, planner
+        from pth_flash_attn_b200 import capi, host, planner
 
         self.torch = torch
         self.flags = 0
@@ -161,7 +161,13 @@ class DeviceLaunch:
         if self.S > 1:
             self.ws_o = torch.empty((self.S, T, hq_local, D), dtype=torch.float32, device=device)
             self.ws_lse = torch.empty((self.S, T, hq_local), dtype=torch.float32, device=device)
-        self.kernels = 1 + (1 if self.S > 1 else 0)
+        # as the torch op does: max_query_len within one row tile = one row tile per request
+        if q_max <= self.bq:
+            self.flags |= capi.FLAG_ONE_TILE_PER_REQUEST
+        # tall row tiles: the automatic choice runs the integer kernel (short requests) and the
+        # row-major kernel (the others) one after the other
+        pair = KERNEL_CHOICE == capi.KERNEL_AUTO and self.bq * G > 16
+        self.kernels = (2 if pair else 1) + (1 if self.S > 1 else 0)
         self.h2d = self.q_host.numel() * 2 + self.sets[0]["bt_host"].numel() * 4 + (2 * R + 1) * 4
         self.d2h = self.out_host.numel() * 2
 

@@ -165,6 +165,14 @@ enum {
                                    (prefill, wide verification); bf16 operands */
 };
 
+/* options.flags: the caller promises that no request of the launch has more than
+ * args.bq query tokens (max_query_len <= bq, e.g. every pure decode step), so each
+ * request is exactly one row tile: the grid is num_reqs tiles wide instead of the
+ * padded num_tokens / bq + num_reqs, and a CTA finds its request without a search.
+ * Same results; query tokens past bq of a request that breaks the promise are not
+ * computed. */
+#define PTHB200_FLAG_ONE_TILE_PER_REQUEST 1
+
 /* Options of the _ex entry points.  Zero-initialise, then set abi_version and
  * struct_bytes.  lse_out (optional) receives the natural-log log-sum-exp of the
  * scaled scores per (token, head), -inf for a row without keys: from the
@@ -173,7 +181,7 @@ typedef struct PthB200Options {
   int32_t abi_version;
   int32_t struct_bytes;
   int32_t kernel;
-  int32_t flags; /* reserved, 0 */
+  int32_t flags; /* PTHB200_FLAG_* bits */
   float* lse_out; /* [num_tokens, num_q_heads] fp32 or NULL */
   int64_t lse_stride_token;
   int64_t lse_stride_head;

@@ -18,6 +18,8 @@ ABI_VERSION = 2
 F32, F16, BF16 = 0, 1, 2
 OK, EINVAL, ECUDA, ENOCUDA = 0, -1, -2, -3
 KERNEL_AUTO, KERNEL_SCALAR, KERNEL_UMMA, KERNEL_UMMA_BF16, KERNEL_UMMA_ROWS = 0, 1, 2, 3, 4
+# options.flags: no request has more than bq query tokens, so row tile x is request x
+FLAG_ONE_TILE_PER_REQUEST = 1
 
 LIBRARY_PATH = Path(__file__).with_name("libpthb200_attn.so")
 

@@ -48,6 +48,7 @@ int32_t check_options(const PthB200Options* o) {
   PTHB_REQUIRE(o->abi_version == PTH_ATTN_ABI_VERSION, "options.abi_version does not match the library");
   PTHB_REQUIRE(o->struct_bytes == (int32_t)sizeof(PthB200Options), "options.struct_bytes != sizeof(PthB200Options)");
   PTHB_REQUIRE(o->kernel >= PTHB200_KERNEL_AUTO && o->kernel <= PTHB200_KERNEL_UMMA_ROWS, "options.kernel is not a kernel family");
+  PTHB_REQUIRE((o->flags & ~PTHB200_FLAG_ONE_TILE_PER_REQUEST) == 0, "options.flags has unknown bits");
   if (o->lse_out != nullptr) {
     PTHB_REQUIRE(aligned(o->lse_out, 4), "options.lse_out must be 4-byte aligned");
     PTHB_REQUIRE(o->lse_stride_token % 4 == 0 && o->lse_stride_head % 4 == 0 && o->lse_stride_token >= 0 &&
@@ -158,7 +159,8 @@ int32_t build_attention(const PthAttnArgs* a, const PthB200Options* opt, KernelP
   p.num_q_heads = a->num_q_heads;
   p.group = group;
   p.bq = a->bq;
-  p.num_q_tiles = a->num_tokens / a->bq + a->num_reqs;
+  p.tile_map = (opt != nullptr && (opt->flags & PTHB200_FLAG_ONE_TILE_PER_REQUEST) != 0) ? 1 : 0;
+  p.num_q_tiles = p.tile_map == 1 ? a->num_reqs : a->num_tokens / a->bq + a->num_reqs;
   p.num_splits = a->num_splits;
   p.window = a->window;
   p.causal = a->causal;
@@ -166,7 +168,11 @@ int32_t build_attention(const PthAttnArgs* a, const PthB200Options* opt, KernelP
   return PTH_ATTN_OK;
 }
 
-// Kernel family for these parameters (a PTHB200_KERNEL_* value other than AUTO).
+// Internal family of the automatic choice: integer kernel for the short requests of the
+// launch, then the row-major kernel for the others.
+constexpr int32_t kFamilyPair = 100;
+
+// Kernel family for these parameters (a PTHB200_KERNEL_* value other than AUTO, or kFamilyPair).
 int32_t choose_family(const KernelParams& p, const PthB200Options* opt, int32_t* family) {
   const int32_t want = opt ? opt->kernel : PTHB200_KERNEL_AUTO;
   const char* why = "";
@@ -188,10 +194,12 @@ int32_t choose_family(const KernelParams& p, const PthB200Options* opt, int32_t*
   } else {
     // Tall row tiles (prefill chunks, wide verification: more than 16 rows per KV head and
     // tile) go to the row-major kernel, short ones (decode, narrow verification) to the
-    // token-major integer kernel.
+    // token-major integer kernel.  A launch that may hold both (its tile height only bounds
+    // the longest request) runs the two kernels one after the other, each serving its own
+    // requests: a decode request inside a prefill batch is not padded to a 128-row tile.
     const char* why_rows = "";
     const bool tall = (int64_t)p.bq * p.group > 16;
-    *family = (tall && umma_rows_supports(p, &why_rows)) ? PTHB200_KERNEL_UMMA_ROWS
+    *family = (tall && umma_rows_supports(p, &why_rows)) ? (i8_ok ? kFamilyPair : PTHB200_KERNEL_UMMA_ROWS)
               : i8_ok                                   ? PTHB200_KERNEL_UMMA
               : umma_ok                                 ? PTHB200_KERNEL_UMMA_BF16
                                                         : PTHB200_KERNEL_SCALAR;
@@ -207,7 +215,16 @@ int32_t attention_impl(const PthAttnArgs* a, const PthB200Options* opt, void* st
   if (int32_t rc = choose_family(p, opt, &family)) return rc;
   if (!launch) return PTH_ATTN_OK;
   cudaError_t err;
-  if (family == PTHB200_KERNEL_UMMA) {
+  if (family == kFamilyPair) {
+    KernelParams ps = p;
+    ps.row_class = 1;
+    ps.class_rows = p.group > 16 ? p.group : 16;
+    err = launch_umma_i8_attention(ps, static_cast<cudaStream_t>(stream));
+    if (err == cudaSuccess) {
+      ps.row_class = 2;
+      err = launch_umma_rows_attention(ps, static_cast<cudaStream_t>(stream));
+    }
+  } else if (family == PTHB200_KERNEL_UMMA) {
     err = launch_umma_i8_attention(p, static_cast<cudaStream_t>(stream));
   } else if (family == PTHB200_KERNEL_UMMA_ROWS) {
     err = launch_umma_rows_attention(p, static_cast<cudaStream_t>(stream));

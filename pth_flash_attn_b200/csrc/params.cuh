@@ -53,7 +53,20 @@ struct KernelParams {
   // integer kernel: how the raw cache bytes are fetched (set by its launcher)
   int32_t raw_mode;        // 1 = tiled TMA box per page, 2 = bulk copy per contiguous page run
   int32_t num_blocks;      // blocks in the cache views
+  // How grid index x maps to a row tile, and which requests this launch serves.
+  int32_t tile_map;    // 0 = padded tile grid (bisection over query_start_loc); 1 = row tile x is request x
+                       //     (valid when no request has more than bq query tokens): num_q_tiles = num_reqs
+  int32_t row_class;   // 0 = every request; 1 = only requests with q_len * group <= class_rows; 2 = only the others
+  int32_t class_rows;
 };
+
+// Re-tiles a launch to `bq` query tokens per row tile.  The caller's promise behind
+// tile_map = 1 (no request longer than its bq) survives only while bq does not shrink.
+inline void set_row_tile(KernelParams& p, int bq) {
+  if (bq < p.bq) p.tile_map = 0;
+  p.bq = bq;
+  p.num_q_tiles = p.tile_map == 1 ? p.num_reqs : p.num_tokens / p.bq + p.num_reqs;
+}
 
 // A row tile resolved on the device.
 struct RowTile {
@@ -69,22 +82,31 @@ struct RowTile {
 // The start index is strictly increasing in r, so the owner is found by
 // bisection; tiles that fall between two requests are surplus (req = -1).
 // `qsl(i)` reads query_start_loc[i] and `len(r)` seq_lens[r] (from global memory, or from
-// copies of them).
+// copies of them).  With tile_map = 1 the caller has promised that no request has more than
+// bq query tokens, so tile x is simply request x (tokens past bq would be left out, never
+// written past the tile).  row_class filters requests by their row count, which lets two
+// kernels share one launch: each resolves every tile and drops the other's requests.
 template <class LoadQsl, class LoadLen>
 __device__ __forceinline__ RowTile resolve_row_tile_with(const KernelParams& p, int x, LoadQsl qsl, LoadLen len) {
   RowTile t;
   t.req = -1;
   int lo = 0, hi = p.num_reqs - 1;
-  while (lo < hi) {
-    const int mid = (lo + hi + 1) >> 1;
-    const int first = qsl(mid) / p.bq + mid;
-    if (first <= x) lo = mid; else hi = mid - 1;
+  if (p.tile_map == 1) {
+    if (x >= p.num_reqs) return t;
+    lo = x;
+  } else {
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      const int first = qsl(mid) / p.bq + mid;
+      if (first <= x) lo = mid; else hi = mid - 1;
+    }
   }
   const int q0 = qsl(lo);
   const int q1 = qsl(lo + 1);
-  const int j = x - (q0 / p.bq + lo);
+  const int j = p.tile_map == 1 ? 0 : x - (q0 / p.bq + lo);
   const int q_len = q1 - q0;
   if (j < 0 || j * p.bq >= q_len) return t;
+  if (p.row_class != 0 && (((int64_t)q_len * p.group <= p.class_rows) != (p.row_class == 1))) return t;
   t.req = lo;
   t.first_idx = j * p.bq;
   t.tok0 = q0 + t.first_idx;

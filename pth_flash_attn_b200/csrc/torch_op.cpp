@@ -300,6 +300,8 @@ void run(Tensor& out, const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
   PthB200Options opt{};
   opt.abi_version = PTH_ATTN_ABI_VERSION;
   opt.struct_bytes = static_cast<int32_t>(sizeof(PthB200Options));
+  // max_query_len bounds every request: when it fits one row tile, each request is one tile
+  if (max_query_len >= 1 && max_query_len <= bq) opt.flags |= PTHB200_FLAG_ONE_TILE_PER_REQUEST;
   if (lse != nullptr) {
     opt.lse_out = static_cast<float*>(lse->data_ptr());
     opt.lse_stride_token = bytes(*lse, 0);

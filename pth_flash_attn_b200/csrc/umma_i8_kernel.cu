@@ -156,7 +156,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
   // shared memory with one round of coalesced loads and bisects there.
   constexpr int kQslCache = 4096;
   RowTile t;
-  if (p.num_reqs + 1 <= kQslCache) {
+  if (p.tile_map == 0 && p.num_reqs + 1 <= kQslCache) {
     int* qsl_s = reinterpret_cast<int*>(smem + L::raw);
     int* len_s = qsl_s + kQslCache;
     for (int i = tid; i <= p.num_reqs; i += kThreads) {
@@ -803,9 +803,15 @@ bool umma_i8_supports(const KernelParams& p, const char** why) {
 
 cudaError_t launch_umma_i8_attention(const KernelParams& p_in, cudaStream_t stream) {
   KernelParams p = p_in;
-  const int cap = 64 / p.group;
-  if (p.bq > cap) p.bq = cap;
-  p.num_q_tiles = p.num_tokens / p.bq + p.num_reqs;
+  if (p.row_class == 1) {
+    // Only requests of at most class_rows rows: each is one row tile, tile x is request x.
+    p.bq = p.class_rows / p.group > 0 ? p.class_rows / p.group : 1;
+    p.tile_map = 1;
+    p.num_q_tiles = p.num_reqs;
+  } else {
+    const int cap = 64 / p.group;
+    set_row_tile(p, p.bq > cap ? cap : p.bq);
+  }
   p.raw_mode = raw_mode_for(p);
   CUtensorMap map{};
   if (p.raw_mode == 1 && !make_page_map(p, p.num_blocks, &map)) return cudaErrorInvalidValue;

@@ -487,8 +487,7 @@ cudaError_t launch_umma_attention(const KernelParams& p_in, cudaStream_t stream)
   KernelParams p = p_in;
   // Row tiles of at most 64 rows: shorten bq if the caller's tile is taller.
   const int cap = 64 / p.group;
-  if (p.bq > cap) p.bq = cap;
-  p.num_q_tiles = p.num_tokens / p.bq + p.num_reqs;
+  set_row_tile(p, p.bq > cap ? cap : p.bq);
   const int rows = p.bq * p.group;
   if (rows <= 16) return launch_npad<16>(p, stream);
   if (rows <= 32) return launch_npad<32>(p, stream);

@@ -119,7 +119,7 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
   constexpr int kQslCache = 4096;
   static_assert(kRNR * kRawHalfBytes >= 2 * kQslCache * 4, "the raw ring holds the copies of query_start_loc and seq_lens");
   RowTile t;
-  if (p.num_reqs + 1 <= kQslCache) {
+  if (p.tile_map == 0 && p.num_reqs + 1 <= kQslCache) {
     int* qsl_s = reinterpret_cast<int*>(smem + L::raw);
     int* len_s = qsl_s + kQslCache;
     for (int i = tid; i <= p.num_reqs; i += kRThreads) {
@@ -680,8 +680,7 @@ cudaError_t launch_umma_rows_attention(const KernelParams& p_in, cudaStream_t st
   KernelParams p = p_in;
   // Row tiles of 128 rows, whatever tile height the caller planned with: the partition of
   // the query tokens into row tiles is internal to a launch.
-  p.bq = 128 / p.group > 0 ? 128 / p.group : 1;
-  p.num_q_tiles = p.num_tokens / p.bq + p.num_reqs;
+  set_row_tile(p, 128 / p.group > 0 ? 128 / p.group : 1);
   p.raw_mode = raw_mode_for(p);
   CUtensorMap map{};
   if (p.raw_mode == 1 && !make_page_map(p, p.num_blocks, &map)) return cudaErrorInvalidValue;

@@ -121,3 +121,50 @@ def test_rows_kernel_window_and_auto_choice():
         res = run_case(c, q, qsl, scale, bq=16, num_splits=2, window=4096, kernel=kernel)
         check_out(res["out"], ref.out, what="rows window 4096")
         check_lse(res["lse"], ref.lse, what="rows window 4096")
+
+
+@pytest.mark.parametrize("kernel", [capi.KERNEL_SCALAR] + KERNELS + [capi.KERNEL_AUTO])
+@pytest.mark.parametrize("qlens,bq,S", [([1, 1, 1, 1, 1], 1, 3), ([4, 1, 3, 4], 4, 1), ([16, 9, 16], 16, 2)])
+def test_one_tile_per_request_flag_gives_the_same_bytes(qlens, bq, S, kernel):
+    """The caller's promise that no request exceeds bq tokens only changes how a CTA finds its
+    request (tile x = request x, no padded grid): outputs are byte-equal with and without it."""
+    from tests.gpu_util import run_case
+
+    lens = [700 + 300 * i for i in range(len(qlens))]
+    c, q, qsl = _seeded(lens, qlens, 8, 2, seed=90 + bq)
+    scale = 128 ** -0.5
+    a = run_case(c, q, qsl, scale, bq=bq, num_splits=S, kernel=kernel)
+    b = run_case(c, q, qsl, scale, bq=bq, num_splits=S, kernel=kernel, flags=capi.FLAG_ONE_TILE_PER_REQUEST)
+    assert capi.load_library().device_status() == 0
+    assert (a["out_bytes"] == b["out_bytes"]).all()
+    assert np.array_equal(a["lse"], b["lse"])
+    ref = orc.ref_attention_paged(q, c, qsl, scale)
+    check_out(b["out"], ref.out, what=f"flag q{qlens}")
+
+
+@pytest.mark.parametrize("S", [1, 3])
+@pytest.mark.parametrize("G", [4, 8])
+def test_mixed_launch_runs_each_request_on_its_kernel(G, S):
+    """Decode, verification and prefill requests in one launch: the automatic choice serves
+    the requests of at most 16 rows with the integer kernel and the others with the row-major
+    kernel, so each request's rows equal the bytes of the launch forced to that kernel."""
+    from tests.gpu_util import run_case
+
+    qlens = [1, 40, 16 // G, 1, 300, 16 // G + 1, 1]
+    lens = [3000, 900, 2100, 64, 1500, 5000, 129]
+    c, q, qsl = _seeded(lens, qlens, 2 * G, 2, seed=120 + G)
+    scale = 128 ** -0.5
+    bq = 64 // G
+    auto = run_case(c, q, qsl, scale, bq=bq, num_splits=S)
+    assert capi.load_library().device_status() == 0
+    ref = orc.ref_attention_paged(q, c, qsl, scale)
+    check_out(auto["out"], ref.out, what=f"mixed G{G} S{S}")
+    check_lse(auto["lse"], ref.lse, what=f"mixed G{G} S{S}")
+    assert auto["tail_intact"]
+    rows = run_case(c, q, qsl, scale, bq=bq, num_splits=S, kernel=capi.KERNEL_UMMA_ROWS)
+    # the integer kernel alone, tiled as the mixed launch tiles its requests
+    i8 = run_case(c, q, qsl, scale, bq=16 // G, num_splits=S, kernel=capi.KERNEL_UMMA)
+    for r, ql in enumerate(qlens):
+        sl = slice(int(qsl[r]), int(qsl[r + 1]))
+        want = i8 if ql * G <= 16 else rows
+        assert (auto["out_bytes"][sl] == want["out_bytes"][sl]).all(), (r, ql)
