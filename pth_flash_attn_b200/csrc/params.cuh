@@ -103,6 +103,7 @@ __device__ __forceinline__ RowTile resolve_row_tile_with(const KernelParams& p, 
   }
   const int q0 = qsl(lo);
   const int q1 = qsl(lo + 1);
+  const int seq_len = len(lo);  // issued with the two loads above, not after the checks below
   const int j = p.tile_map == 1 ? 0 : x - (q0 / p.bq + lo);
   const int q_len = q1 - q0;
   if (j < 0 || j * p.bq >= q_len) return t;
@@ -112,7 +113,7 @@ __device__ __forceinline__ RowTile resolve_row_tile_with(const KernelParams& p, 
   t.tok0 = q0 + t.first_idx;
   t.ntok = min(p.bq, q_len - t.first_idx);
   t.q_len = q_len;
-  t.seq_len = len(lo);
+  t.seq_len = seq_len;
   return t;
 }
 

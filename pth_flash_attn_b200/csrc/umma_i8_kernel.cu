@@ -56,6 +56,8 @@ __device__ unsigned int g_i8_status = 0;
 #ifdef PTHB200_WAIT_STATS
 // Debug build only: cycles that one thread of each role of CTA (0,0,0) spent in each wait.
 __device__ long long g_wait_stats[4][12];
+__device__ long long g_timeline[16][16];
+#define TL(tile, ev) if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tile) >= 24 && (tile) < 40) g_timeline[(tile) - 24][ev] = clock64() - k_entry_;
 #define STAT_DECL long long st_[12] = {0}; const long long st_begin_ = clock64();
 #define STAT_WAIT(slot, expr) { const long long t0_ = clock64(); expr; st_[slot] += clock64() - t0_; }
 #define STAT_ADD(slot, v) st_[slot] += (v);
@@ -65,6 +67,7 @@ __device__ long long g_wait_stats[4][12];
 #define STAT_EXIT if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { unsigned long long e_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(e_)); g_wait_stats[3][10] = (long long)(e_ - k_ns_); }
 #define STAT_FLUSH(role) if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { st_[11] = clock64() - st_begin_; for (int q_ = 0; q_ < 12; ++q_) g_wait_stats[role][q_] = st_[q_]; }
 #else
+#define TL(tile, ev)
 #define STAT_DECL
 #define STAT_WAIT(slot, expr) { expr; }
 #define STAT_ADD(slot, v)
@@ -123,6 +126,11 @@ struct Bars {
   static constexpr int raw_free = 2 * NS + 14 + NR;  // [NR] producers -> loader, 128 arrivals
   static constexpr int kempty = 2 * NS + 14 + 2 * NR; // [NK] QK issuer (tcgen05.commit) -> producers
 };
+
+// Key of a tile held by row `r` of its operand images (see the producers).
+__device__ __forceinline__ int tile_key(const KernelParams& p, int r) {
+  return p.raw_mode == 2 ? 2 * (r & 63) + (r >> 6) : r;
+}
 
 template <int NPAD, int PD, int NS, int NK, int NR, int SB, int RQ, int NP>
 __global__ void __launch_bounds__(threads_for(NP), 1)
@@ -257,13 +265,19 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     const uint8_t* kb = p.k.data + (int64_t)kvh * p.k.stride_head;
     const uint32_t delta = (uint32_t)(reinterpret_cast<uintptr_t>(kb) & 15);
     const int row_pitch = p.raw_mode == 1 ? kRawRow : 2 * kHeadDimI8 + 8;
-    const int my_page = pt >> p.block_shift, my_slot = pt & (bs - 1);
+    // Row pt of the operand images holds key `key` of the tile.  With a 264-byte pitch
+    // (raw_mode 2) consecutive cells alternate between the two 8-byte alignments: taking the
+    // even cells in the first two warps and the odd ones in the last two keeps a warp on one
+    // code path and its 16-byte loads 528 bytes apart (free of bank conflicts).  The order of
+    // the keys inside a tile has no effect on the integer sums; the softmax masks by `key`.
+    const int key = tile_key(p, pt);
+    const int my_page = key >> p.block_shift, my_slot = key & (bs - 1);
     const uint32_t cell_off = my_page * bs * kRawRow + my_slot * row_pitch + delta;  // inside a raw stage
     const bool odd = (cell_off & 8u) != 0;
 #pragma unroll 1
     for (int j = pgrp; j < n_tiles; j += NP) {
       const int rs = j % kRawStages;
-      const int pos = (tile_begin + j) * kKeys + pt;
+      const int pos = (tile_begin + j) * kKeys + key;
       const bool valid = pos >= range_begin && pos < range_end;
       if constexpr (NP > 1) {
         // A raw stage is shared by the producer groups in turn (NR is not a multiple of NP).
@@ -272,7 +286,9 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
         // first wait until that tile has been taken out of the stage.
         if (j >= kRawStages) ok &= wait_or_abort(&bars[B::raw_free + rs], ((j / kRawStages) - 1) & 1, abort_flag);
       }
+      if (pt == 0) { TL(j, 0) }
       STAT_WAIT(2, ok &= wait_or_abort(&bars[B::raw_full + rs], (j / kRawStages) & 1, abort_flag))
+      if (pt == 0) { TL(j, 1) }
       STAT_T(tP0_)
       uint32_t w[kRawRow / 4];
       if (valid) {
@@ -296,6 +312,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       const int st = j % NS;
       if (j >= NS) STAT_WAIT(0, ok &= wait_or_abort(&bars[B::empty + st], ((j / NS) - 1) & 1, abort_flag))
       if (j >= NK) STAT_WAIT(1, ok &= wait_or_abort(&bars[B::kempty + j % NK], ((j / NK) - 1) & 1, abort_flag))
+      if (pt == 0) { TL(j, 2) }
       STAT_T(tP4_)
       uint8_t* stage = smem + L::vstages + st * kVStageBytes;  // V image, then the scales
       uint8_t* krow = smem + L::kstages + (j % NK) * kImgBytes + pt * 16;
@@ -324,6 +341,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       STAT_T(tP5_)
       tc::fence_async_smem();
       mbar_arrive(&bars[B::full + st]);
+      if (pt == 0) { TL(j, 3) }
       STAT_ADD(8, clock64() - tP5_)
     }
     if (pt == 0 && pgrp == 0) { STAT_FLUSH(0) }
@@ -382,60 +400,74 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     }
   } else if (warp == kMmaWarp) {
     // =========================== MMA issuer ===================================
-    // ONE thread issues every tcgen05.mma of the CTA (two issuing threads, one for QK and
-    // one for PV, produced rare run-to-run differences).  It keeps two cursors and issues
-    // whichever MMA chain is ready, so a QK that waits for its images never holds up a PV
-    // whose P is complete, and the other way round:
+    // ONE thread (lane 0) issues every tcgen05.mma of the CTA, in a fixed order (two issuing
+    // threads, one for QK and one for PV, produced rare run-to-run differences):
+    //   QK(0), QK(1), then for i = 0, 1, ...: QK(i + 2), PV(i).
     //   QK(i): tile i is the k-th tile (k = i >> 1) of softmax group g = i & 1 and lands in
     //          that group's S^T buffer k % SB; needs the tile's images (full) and that
     //          buffer read by the softmax (s_free);
     //   PV(i): needs the group's P image (p_ready) and its O^T buffer folded (o_free); its
     //          completion frees the V stage.
+    // Every condition of a step depends only on MMAs issued earlier in this order, so the
+    // order cannot deadlock, and QK runs two tiles ahead of PV, which is as far as the S^T
+    // buffers allow.  The two barriers of a step are waited for by lanes 0 and 1 in the same
+    // instruction: a look at an mbarrier costs 100-200 cycles on the busy shared-memory pipe,
+    // and four looks in a row per tile made this thread the bottleneck of the CTA.
     named_barrier(5, kSoftmaxThreads + 32);  // wait for the Q image
-    if (lane == 0) {
+    {
       STAT_DECL
       const uint32_t qimg_s = tc::smem_u32(qimg), pimg_s = tc::smem_u32(pimg);
-      int iq = 0, ip = 0;
-      uint32_t idle = 0;
-      const long long deadline = clock64() + (1ll << 33);
+      // lane 0 waits for (bar0, par0); lane 1 for (bar1, par1) if need1; true when both are complete
+      auto wait_pair = [&](uint64_t* bar0, uint32_t par0, uint64_t* bar1, uint32_t par1, bool need1) -> bool {
+        uint64_t* mine = lane == 0 ? bar0 : bar1;
+        const uint32_t par = lane == 0 ? par0 : par1;
+        const bool need = lane == 0 || (lane == 1 && need1);
+        const bool done = !need || wait_or_abort(mine, par, abort_flag);
+        return __all_sync(0xffffffffu, done);
+      };
+      auto qk_step = [&](int q) -> bool {
+        const int g = q & 1, k = q >> 1, sb = k % SB;
+        const bool go = wait_pair(&bars[B::full + q % NS], (q / NS) & 1, &bars[B::s_free + 2 * g + sb],
+                                  ((k / SB) - 1) & 1, k >= SB);
+        if (go && lane == 0) {
+          TL(q, 13)
+          tc::fence_after_sync();
+          TL(q, 4)
+          issue_qk_i8<NPAD>(tmem_base + (g * SB + sb) * L::s_cols, kstage0 + (q % NK) * kImgBytes, qimg_s);
+          TL(q, 9)
+          tc::mma_commit(&bars[B::s_ready + 2 * g + sb]);
+          tc::mma_commit(&bars[B::kempty + q % NK]);  // the K image is dead once S^T exists
+          TL(q, 10)
+        }
+        __syncwarp();
+        return go;
+      };
+      auto pv_step = [&](int i) -> bool {
+        const int g = i & 1;
+        const bool go = wait_pair(&bars[B::p_ready + g], (i >> 1) & 1, &bars[B::o_free + g], ((i >> 1) - 1) & 1, i >= 2);
+        if (go && lane == 0) {
+          TL(i, 14)
+          tc::fence_after_sync();
+          TL(i, 8)
+          issue_pv_i8<NPAD, PD>(tmem_base + L::s_total + g * L::o_cols, vstage0 + (i % NS) * kVStageBytes,
+                                pimg_s + g * (PD * NPAD * kKeys));
+          TL(i, 11)
+          tc::mma_commit(&bars[B::o_ready + g]);
+          tc::mma_commit(&bars[B::empty + i % NS]);
+          TL(i, 12)
+        }
+        __syncwarp();
+        return go;
+      };
+      bool go = qk_step(0);
+      if (go && n_tiles > 1) go = qk_step(1);
 #pragma unroll 1
-      while (ip < n_tiles) {
-        bool issued = false;
-        if (iq < n_tiles) {
-          const int g = iq & 1, k = iq >> 1, sb = k % SB;
-          if (tc::mbar_test_wait(&bars[B::full + iq % NS], (iq / NS) & 1) &&
-              (k < SB || tc::mbar_test_wait(&bars[B::s_free + 2 * g + sb], ((k / SB) - 1) & 1))) {
-            tc::fence_after_sync();
-            issue_qk_i8<NPAD>(tmem_base + (g * SB + sb) * L::s_cols, kstage0 + (iq % NK) * kImgBytes, qimg_s);
-            tc::mma_commit(&bars[B::s_ready + 2 * g + sb]);
-            tc::mma_commit(&bars[B::kempty + iq % NK]);  // the K image is dead once S^T exists
-            ++iq;
-            issued = true;
-          }
-        }
-        if (ip < iq) {
-          const int g = ip & 1;
-          if (tc::mbar_test_wait(&bars[B::p_ready + g], (ip >> 1) & 1) &&
-              (ip < 2 || tc::mbar_test_wait(&bars[B::o_free + g], ((ip >> 1) - 1) & 1))) {
-            tc::fence_after_sync();
-            issue_pv_i8<NPAD, PD>(tmem_base + L::s_total + g * L::o_cols, vstage0 + (ip % NS) * kVStageBytes,
-                                  pimg_s + g * (PD * NPAD * kKeys));
-            tc::mma_commit(&bars[B::o_ready + g]);
-            tc::mma_commit(&bars[B::empty + ip % NS]);
-            ++ip;
-            issued = true;
-          }
-        }
-        if (!issued && (++idle & 63u) == 0u) {
-          // nothing ready for a while: check the abort flag and the deadline (about four seconds)
-          if (*abort_flag) break;
-          if (clock64() > deadline) {
-            *abort_flag = 1;
-            break;
-          }
-        }
+      for (int i = 0; i < n_tiles && go; ++i) {
+        if (i + 2 < n_tiles) go = qk_step(i + 2);
+        if (go) go = pv_step(i);
       }
-      STAT_FLUSH(1)
+      ok &= go;
+      if (lane == 0) { STAT_FLUSH(1) }
     }
   } else if (warp < 2 * 4) {
     // =========================== softmax ======================================
@@ -569,13 +601,15 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       float* wred_i = wred_g + b * 4 * (NPAD + 1);
       const uint8_t* scales = smem + L::vstages + (i % NS) * kVStageBytes + kImgBytes;
       const int sb = it % SB;
+      if (gt == 0) { TL(i, 5) }
       STAT_WAIT(0, ok &= wait_or_abort(&bars[B::s_ready + 2 * g + sb], (it / SB) & 1, abort_flag))
       tc::fence_after_sync();
+      if (gt == 0) { TL(i, 6) }
       STAT_T(tS0_)
       const float ks_cur = reinterpret_cast<const float*>(scales)[gt];
       const float vs_cur = reinterpret_cast<const float*>(scales)[kKeys + gt];
       const uint32_t s_tmem = tmem_base + (g * SB + sb) * L::s_cols + lane_addr;
-      const int pos = (tile_begin + i) * kKeys + gt;
+      const int pos = (tile_begin + i) * kKeys + tile_key(p, gt);
       const bool interior = (tile_begin + i) * kKeys >= mask_lo && (tile_begin + i) * kKeys + (kKeys - 1) <= mask_hi;
       const float mult = ks_cur * p.scale_log2;
       float s[NROW];
@@ -671,6 +705,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       STAT_T(tS4_)
       tc::fence_async_smem();
       mbar_arrive(&bars[B::p_ready + g]);  // P image of tile i complete
+      if (gt == 0) { TL(i, 7) }
       STAT_ADD(7, clock64() - tS4_)
     }
     if (it > 0) fold_o(g + 2 * (it - 1));
@@ -827,6 +862,9 @@ cudaError_t launch_umma_i8_attention(const KernelParams& p_in, cudaStream_t stre
 }
 
 #ifdef PTHB200_WAIT_STATS
+extern "C" int pthb200_debug_timeline(long long* out) {
+  return cudaMemcpyFromSymbol(out, g_timeline, sizeof(long long) * 256) == cudaSuccess ? 0 : -1;
+}
 extern "C" int pthb200_debug_wait_stats(long long* out) {
   return cudaMemcpyFromSymbol(out, g_wait_stats, sizeof(long long) * 48) == cudaSuccess ? 0 : -1;
 }
