@@ -51,36 +51,24 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   if (tc::mbar_try_wait(bar, parity)) return true;
   const long long deadline = clock64() + (1ll << 32);
-#if defined(PTHB200_WAIT_MODE) && PTHB200_WAIT_MODE == 1
-  for (;;) {
-    for (int i = 0; i < 64; ++i)
-      if (tc::mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (clock64() > deadline) break;
-  }
-#elif defined(PTHB200_WAIT_MODE) && PTHB200_WAIT_MODE == 2
-  for (;;) {
-    for (int i = 0; i < 256; ++i)
-      if (tc::mbar_test_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (clock64() > deadline) break;
-  }
-#elif defined(PTHB200_WAIT_MODE) && PTHB200_WAIT_MODE == 3
-  for (;;) {
-    for (int i = 0; i < 64; ++i) {
-      if (tc::mbar_test_wait(bar, parity)) return true;
-      __nanosleep(32);
-    }
-    if (*abort_flag) return false;
-    if (clock64() > deadline) break;
-  }
-#else
   for (;;) {
     if (tc::mbar_try_wait_hint(bar, parity, 100000u)) return true;
     if (*abort_flag) return false;
     if (clock64() > deadline) break;
   }
-#endif
+  *abort_flag = 1;
+  return false;
+}
+
+// The same wait with the barrier given as a shared-memory address.
+__device__ __forceinline__ bool wait_or_abort_s(uint32_t bar_s, uint32_t parity, volatile int* abort_flag) {
+  if (tc::mbar_try_wait_s(bar_s, parity)) return true;
+  const long long deadline = clock64() + (1ll << 32);
+  for (;;) {
+    if (tc::mbar_try_wait_hint_s(bar_s, parity, 100000u)) return true;
+    if (*abort_flag) return false;
+    if (clock64() > deadline) break;
+  }
   *abort_flag = 1;
   return false;
 }

@@ -126,4 +126,53 @@ __device__ __forceinline__ void issue_pv_i8(uint32_t o_tmem, uint32_t vimg, uint
   }
 }
 
+// ---- the same MMA chains for an issuing thread that keeps its descriptors in registers ----
+// The start address (in 16-byte units) sits in the low word of a shared-memory descriptor, so
+// moving an operand by `bytes` (a multiple of 16, inside shared memory) adds bytes / 16 to
+// that word.  Building four descriptors per chain from scratch costs the single issuing
+// thread about a hundred dependent instructions; this form costs two additions per MMA.
+struct DescWords {
+  uint32_t lo, hi;
+};
+__device__ __forceinline__ DescWords desc_words(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  const uint64_t d = tc::smem_desc(saddr, lbo_bytes, sbo_bytes);
+  return DescWords{(uint32_t)d, (uint32_t)(d >> 32)};
+}
+template <bool kAccumulate>
+__device__ __forceinline__ void mma_i8_words(uint32_t d_tmem, uint32_t alo, uint32_t ahi, uint32_t blo, uint32_t bhi,
+                                             uint32_t idesc) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "r"(alo), "r"(ahi), "r"(blo), "r"(bhi), "r"(idesc), "n"(kAccumulate ? 1 : 0)
+      : "memory");
+}
+// k = descriptor words of the K image (desc_words(kimg, kImgChunk, 128)), q = of the Q image
+// (desc_words(qimg, 2 NPAD 16, 128)).
+template <int NPAD>
+__device__ __forceinline__ void issue_qk_i8_words(uint32_t s_tmem, DescWords k, DescWords q) {
+  constexpr uint32_t idesc = idesc_i8(128, 2 * NPAD, 0, 0);
+  constexpr uint32_t ka = (2 * kImgChunk) >> 4, qa = (2 * (2 * NPAD * 16)) >> 4;
+  mma_i8_words<false>(s_tmem, k.lo, k.hi, q.lo, q.hi, idesc);
+  mma_i8_words<true>(s_tmem, k.lo + ka, k.hi, q.lo + qa, q.hi, idesc);
+  mma_i8_words<true>(s_tmem, k.lo + 2 * ka, k.hi, q.lo + 2 * qa, q.hi, idesc);
+  mma_i8_words<true>(s_tmem, k.lo + 3 * ka, k.hi, q.lo + 3 * qa, q.hi, idesc);
+}
+// v = desc_words(vimg, 128, kImgChunk), pd = desc_words(pimg, 128, kDigitChunk).
+template <int NPAD, int PD>
+__device__ __forceinline__ void issue_pv_i8_words(uint32_t o_tmem, DescWords v, DescWords pd) {
+  constexpr uint32_t idesc = idesc_i8(128, PD * NPAD, 1, 1);
+  constexpr uint32_t step = (4 * 128) >> 4;
+  mma_i8_words<false>(o_tmem, v.lo, v.hi, pd.lo, pd.hi, idesc);
+  mma_i8_words<true>(o_tmem, v.lo + step, v.hi, pd.lo + step, pd.hi, idesc);
+  mma_i8_words<true>(o_tmem, v.lo + 2 * step, v.hi, pd.lo + 2 * step, pd.hi, idesc);
+  mma_i8_words<true>(o_tmem, v.lo + 3 * step, v.hi, pd.lo + 3 * step, pd.hi, idesc);
+}
+
 }  // namespace pthb200

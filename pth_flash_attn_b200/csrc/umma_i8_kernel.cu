@@ -413,50 +413,59 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     // buffers allow.  The two barriers of a step are waited for by lanes 0 and 1 in the same
     // instruction: a look at an mbarrier costs 100-200 cycles on the busy shared-memory pipe,
     // and four looks in a row per tile made this thread the bottleneck of the CTA.
+    // This thread's own instruction stream is the narrowest part of the CTA (a few hundred
+    // dependent instructions per tile took as long as the tile), so everything it needs is
+    // kept in registers: barrier addresses as shared-memory offsets, operand descriptors as
+    // word pairs that move by one addition per MMA.
     named_barrier(5, kSoftmaxThreads + 32);  // wait for the Q image
     {
       STAT_DECL
-      const uint32_t qimg_s = tc::smem_u32(qimg), pimg_s = tc::smem_u32(pimg);
-      // lane 0 waits for (bar0, par0); lane 1 for (bar1, par1) if need1; true when both are complete
-      auto wait_pair = [&](uint64_t* bar0, uint32_t par0, uint64_t* bar1, uint32_t par1, bool need1) -> bool {
-        uint64_t* mine = lane == 0 ? bar0 : bar1;
+      const uint32_t bars_s = tc::smem_u32(bars);
+      const DescWords qd = desc_words(tc::smem_u32(qimg), 2 * NPAD * 16, 128);
+      const DescWords kd = desc_words(kstage0, kImgChunk, 128);
+      const DescWords vd = desc_words(vstage0, 128, kImgChunk);
+      const DescWords pd = desc_words(tc::smem_u32(pimg), 128, kDigitChunk);
+      // lane 0 waits for barrier i0 (parity par0); lane 1 for barrier i1 if need1; true when both are complete
+      auto wait_pair = [&](int i0, uint32_t par0, int i1, uint32_t par1, bool need1) -> bool {
+        const uint32_t mine = bars_s + 8u * (uint32_t)(lane == 0 ? i0 : i1);
         const uint32_t par = lane == 0 ? par0 : par1;
         const bool need = lane == 0 || (lane == 1 && need1);
-        const bool done = !need || wait_or_abort(mine, par, abort_flag);
+        const bool done = !need || wait_or_abort_s(mine, par, abort_flag);
         return __all_sync(0xffffffffu, done);
       };
       auto qk_step = [&](int q) -> bool {
         const int g = q & 1, k = q >> 1, sb = k % SB;
-        const bool go = wait_pair(&bars[B::full + q % NS], (q / NS) & 1, &bars[B::s_free + 2 * g + sb],
-                                  ((k / SB) - 1) & 1, k >= SB);
+        const bool go = wait_pair(B::full + q % NS, (q / NS) & 1, B::s_free + 2 * g + sb, ((k / SB) - 1) & 1, k >= SB);
         if (go && lane == 0) {
           TL(q, 13)
           tc::fence_after_sync();
           TL(q, 4)
-          issue_qk_i8<NPAD>(tmem_base + (g * SB + sb) * L::s_cols, kstage0 + (q % NK) * kImgBytes, qimg_s);
+          DescWords kq = kd;
+          kq.lo += (uint32_t)(q % NK) * (kImgBytes >> 4);
+          issue_qk_i8_words<NPAD>(tmem_base + (g * SB + sb) * L::s_cols, kq, qd);
           TL(q, 9)
-          tc::mma_commit(&bars[B::s_ready + 2 * g + sb]);
-          tc::mma_commit(&bars[B::kempty + q % NK]);  // the K image is dead once S^T exists
+          tc::mma_commit_s(bars_s + 8u * (B::s_ready + 2 * g + sb));
+          tc::mma_commit_s(bars_s + 8u * (B::kempty + q % NK));  // the K image is dead once S^T exists
           TL(q, 10)
         }
-        __syncwarp();
         return go;
       };
       auto pv_step = [&](int i) -> bool {
         const int g = i & 1;
-        const bool go = wait_pair(&bars[B::p_ready + g], (i >> 1) & 1, &bars[B::o_free + g], ((i >> 1) - 1) & 1, i >= 2);
+        const bool go = wait_pair(B::p_ready + g, (i >> 1) & 1, B::o_free + g, ((i >> 1) - 1) & 1, i >= 2);
         if (go && lane == 0) {
           TL(i, 14)
           tc::fence_after_sync();
           TL(i, 8)
-          issue_pv_i8<NPAD, PD>(tmem_base + L::s_total + g * L::o_cols, vstage0 + (i % NS) * kVStageBytes,
-                                pimg_s + g * (PD * NPAD * kKeys));
+          DescWords vi = vd, pi = pd;
+          vi.lo += (uint32_t)(i % NS) * (kVStageBytes >> 4);
+          pi.lo += (uint32_t)g * ((PD * NPAD * kKeys) >> 4);
+          issue_pv_i8_words<NPAD, PD>(tmem_base + L::s_total + g * L::o_cols, vi, pi);
           TL(i, 11)
-          tc::mma_commit(&bars[B::o_ready + g]);
-          tc::mma_commit(&bars[B::empty + i % NS]);
+          tc::mma_commit_s(bars_s + 8u * (B::o_ready + g));
+          tc::mma_commit_s(bars_s + 8u * (B::empty + i % NS));
           TL(i, 12)
         }
-        __syncwarp();
         return go;
       };
       bool go = qk_step(0);
@@ -467,6 +476,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
         if (go) go = pv_step(i);
       }
       ok &= go;
+      __syncwarp();
       if (lane == 0) { STAT_FLUSH(1) }
     }
   } else if (warp < 2 * 4) {
