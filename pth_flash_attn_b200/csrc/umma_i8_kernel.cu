@@ -124,7 +124,7 @@ struct Bars {
   static constexpr int p_ready = 2 * NS + 12; // [2] softmax -> MMA, 128 arrivals
   static constexpr int raw_full = 2 * NS + 14;// [NR] page copies -> producers
   static constexpr int raw_free = 2 * NS + 14 + NR;  // [NR] producers -> loader, 128 arrivals
-  static constexpr int kempty = 2 * NS + 14 + 2 * NR; // [NK] QK issuer (tcgen05.commit) -> producers
+  static constexpr int kempty = 2 * NS + 14 + 2 * NR; // [NK] unused (the producers wait on s_ready)
 };
 
 // Key of a tile held by row `r` of its operand images (see the producers).
@@ -311,7 +311,14 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       mbar_arrive(&bars[B::raw_free + rs]);
       const int st = j % NS;
       if (j >= NS) STAT_WAIT(0, ok &= wait_or_abort(&bars[B::empty + st], ((j / NS) - 1) & 1, abort_flag))
-      if (j >= NK) STAT_WAIT(1, ok &= wait_or_abort(&bars[B::kempty + j % NK], ((j / NK) - 1) & 1, abort_flag))
+      // K image j % NK is free once QK(j - NK) has completed, which is what S^T of that tile
+      // being ready means: the producers wait on the s_ready barrier the softmax group waits
+      // on (one commit less per tile for the issuing thread).  That barrier completes next
+      // for a tile whose images this group writes after this wait, so the parity is unambiguous.
+      if (j >= NK) {
+        const int q = j - NK, qk = q >> 1;
+        STAT_WAIT(1, ok &= wait_or_abort(&bars[B::s_ready + 2 * (q & 1) + qk % SB], (qk / SB) & 1, abort_flag))
+      }
       if (pt == 0) { TL(j, 2) }
       STAT_T(tP4_)
       uint8_t* stage = smem + L::vstages + st * kVStageBytes;  // V image, then the scales
@@ -445,7 +452,6 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
           issue_qk_i8_words<NPAD>(tmem_base + (g * SB + sb) * L::s_cols, kq, qd);
           TL(q, 9)
           tc::mma_commit_s(bars_s + 8u * (B::s_ready + 2 * g + sb));
-          tc::mma_commit_s(bars_s + 8u * (B::kempty + q % NK));  // the K image is dead once S^T exists
           TL(q, 10)
         }
         return go;
