@@ -3,24 +3,28 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--config NAME] [--impl reference]
 
-A "step" is one pass of the hot path over one synthetic batch.  The default
-workload is the long-context split-KV decode configuration: one launch of
-batch 1 at context 131072 plus one launch of batch 64 at context 8192
-(Hq = 32, Hkv = 8, D = 128, block size 16, one query token per request), each
-launch being the attention kernel and, when the planner splits the KV range,
-the combine kernel.  The metric is the achieved cache read bandwidth: the
-algorithmic KV bytes of a step (every visible (token, KV head) cell once,
-2 D + 8 bytes each) divided by the device time of the step.
+One "pass" is one call of the op over one synthetic batch (the attention launch and, when
+the key range is split, the combine launch, for every launch of the workload).  A "step" is
+`passes_per_step` passes, chosen at start-up so that the K timed steps take about one
+second whatever K is; every number is reported per pass (= per layer of a model).
 
-With N > 1 (one process per GPU, started by torch.distributed.run) the KV heads
-are sharded: rank g owns Hkv / N KV heads, the matching query heads and its own
-cache; there is no collective on the data path.  Total work is fixed, so the
-line says "strong" scaling; `value` is the whole job's bytes over the slowest
-rank's time.
+The headline workload is the long-context split-KV decode configuration: one launch of
+batch 1 at context 131072 plus one launch of batch 64 at context 8192 (Hq = 32, Hkv = 8,
+D = 128, block size 16, one query token per request).  The metric is the achieved cache
+read bandwidth: the algorithmic KV bytes of a pass (every visible (token, KV head) cell
+once, 2 D + 8 bytes each) divided by the device time of the pass.  The line's `per_config`
+block holds the same measurement for every other configuration (decode, verification,
+windowed drafter in GB/s; chunked prefill in TFLOP/s; the mixed batch in both), each with
+the roofline that bounds it and a sampled check of its output against the CPU oracle.
 
-Inputs are synthetic: random int8 cells with plausible fp32 scales written
-directly in vLLM's int8_per_token_head page layout on the device, bf16 N(0,1)
-queries, seeded random block tables.  Values do not change the memory traffic.
+With N > 1 (one process per GPU, started by torch.distributed.run) the KV heads are
+sharded: rank g owns Hkv / N KV heads, the matching query heads and its own cache; there is
+no collective on the data path.  Total work is fixed, so the line says "strong" scaling;
+`value` is the whole job's bytes over the slowest rank's time.
+
+Inputs are synthetic: K and V are N(0, 1) values quantised per (token, KV head) to int8 with
+scale absmax / 127, written in vLLM's int8_per_token_head page layout on the device; bf16
+N(0, 1) queries; seeded random block tables.
 """
 from __future__ import annotations
 
@@ -40,37 +44,34 @@ sys.path.insert(0, str(REPO))
 
 HQ, HKV, D, BS = 32, 8, 128, 16
 CELL = 2 * D + 8
+HEADLINE = "long_decode"
+PER_CONFIG = ("decode_small", "long_decode", "verify4", "drafter16", "chunked_prefill", "mixed")
+TENSOR_BOUND = ("chunked_prefill",)
 
 
 # --------------------------------------------------------------------------
 # workloads
 # --------------------------------------------------------------------------
 def workload_launches(name: str, seed: int = 1001):
-    """Returns a list of launches: dict(seq_lens, q_lens, window, causal, Hq, Hkv)."""
+    """The launches of a workload: dict(seq_lens, q_lens, Hq, Hkv[, window, prefill])."""
     rng = np.random.default_rng(seed)
-    if name == "decode_small":  # BASELINE config 0
+    if name == "decode_small":  # batch 8, contexts uniform in [1, 4096]
         return [dict(seq_lens=rng.integers(1, 4097, size=8).tolist(), q_lens=[1] * 8, Hq=32, Hkv=8)]
-    if name == "long_decode":  # BASELINE config 1 (default)
+    if name == "long_decode":  # the headline: 1 x 131072, then 64 x 8192
         return [dict(seq_lens=[131072], q_lens=[1], Hq=32, Hkv=8),
                 dict(seq_lens=[8192] * 64, q_lens=[1] * 64, Hq=32, Hkv=8)]
-    if name == "long_decode_b1":
+    if name == "long_decode_b1":  # the first launch of the headline alone
         return [dict(seq_lens=[131072], q_lens=[1], Hq=32, Hkv=8)]
-    if name == "long_decode_b64":
+    if name == "long_decode_b64":  # the second launch of the headline alone
         return [dict(seq_lens=[8192] * 64, q_lens=[1] * 64, Hq=32, Hkv=8)]
-    if name == "decode_h1":  # one KV head per GPU (the 8-GPU shard shape), same bytes as long_decode_b64
-        return [dict(seq_lens=[8192] * 512, q_lens=[1] * 512, Hq=4, Hkv=1)]
-    if name == "shard8_b1":  # what one of 8 GPUs sees of long_decode's first launch
-        return [dict(seq_lens=[131072], q_lens=[1], Hq=4, Hkv=1)]
-    if name == "shard8_b64":  # ... and of its second launch
-        return [dict(seq_lens=[8192] * 64, q_lens=[1] * 64, Hq=4, Hkv=1)]
-    if name == "verify4":  # BASELINE config 2a
+    if name == "verify4":  # speculative verification, 4 draft tokens
         return [dict(seq_lens=rng.integers(16384, 32769, size=32).tolist(), q_lens=[4] * 32, Hq=32, Hkv=8)]
-    if name == "drafter16":  # BASELINE config 2b
+    if name == "drafter16":  # windowed drafter, 16 tokens, window 4096
         return [dict(seq_lens=rng.integers(16384, 32769, size=32).tolist(), q_lens=[16] * 32, Hq=32,
                      Hkv=8, window=4096)]
-    if name == "chunked_prefill":  # BASELINE config 3
+    if name == "chunked_prefill":  # 4 chunks of 2048 tokens over 30720 cached tokens
         return [dict(seq_lens=[32768] * 4, q_lens=[2048] * 4, Hq=64, Hkv=8, prefill=True)]
-    if name == "mixed":  # BASELINE config 4, one launch
+    if name == "mixed":  # 48 decode + 8 verify + 2 prefill requests in one launch
         dec = rng.integers(4096, 131073, size=48).tolist()
         return [dict(seq_lens=dec + [32768] * 8 + [17408] * 2, q_lens=[1] * 48 + [4] * 8 + [1024] * 2,
                      Hq=64, Hkv=8, prefill=True)]
@@ -99,121 +100,258 @@ def attn_flops(launch, hq_local):
 
 
 # --------------------------------------------------------------------------
-# device-side synthetic cache
+# one launch, resident on the device
 # --------------------------------------------------------------------------
+def _align(n, a=256):
+    return (n + a - 1) // a * a
+
+
 class DeviceLaunch:
-    """One launch with everything resident on the device, plus pinned host copies of the
-    per-step inputs for the end-to-end leg."""
+    """One launch of a workload for one rank: its KV-head shard of the cache, generated on
+    the device, the op's per-call inputs as views of ONE device staging buffer with a pinned
+    host twin (the end-to-end leg copies it with a single transfer), and the plan."""
 
-    def __init__(self, torch, launch, hkv_local, hq_local, device, seed, num_sms, sets=1, splits=None, layout="NHD"):
-        from pth_flash_attn_b200 import capi, host, planner
+    def __init__(self, torch, launch, rank, world, device, seed, num_sms, sets=1):
+        from pth_flash_attn_b200 import capi, host, planner, sharding
 
-        self.torch = torch
-        self.flags = 0
-        g = torch.Generator(device="cpu").manual_seed(seed)
+        self.torch, self.launch_spec = torch, launch
+        shard = sharding.head_shard(rank, world, launch["Hq"], launch["Hkv"])
+        hkv, hq = shard.num_kv_heads, shard.num_q_heads
+        self.hkv, self.hq, self.G = hkv, hq, hq // hkv
+        gen = torch.Generator(device="cpu").manual_seed(seed)
         lens, qlens = launch["seq_lens"], launch["q_lens"]
         R, T = len(lens), int(sum(qlens))
         self.R, self.T = R, T
         self.window, self.causal = launch.get("window", 0), launch.get("causal", True)
-        G = hq_local // hkv_local
         nblk = [-(-L // BS) for L in lens]
-        need = sum(nblk)
-        page = BS * hkv_local * CELL
-        self.sets = []
+        need, width = sum(nblk), max(nblk)
         q_max = max(qlens)
         is_prefill = bool(launch.get("prefill", False))
-        w_ts = planner.workspace_token_splits(max_num_seqs=max(R, 1), q_dec_max=q_max, Hkv=hkv_local, D=D,
-                                              num_sms=num_sms)
-        plan = planner.plan_launch(num_tokens=T, num_reqs=R, max_query_len=q_max, G=G, Hkv=hkv_local, D=D,
+        w_ts = planner.workspace_token_splits(max_num_seqs=R, q_dec_max=q_max, Hkv=hkv, D=D, num_sms=num_sms)
+        plan = planner.plan_launch(num_tokens=T, num_reqs=R, max_query_len=q_max, G=self.G, Hkv=hkv, D=D,
                                    num_sms=num_sms, is_prefill=is_prefill, ws_token_splits=w_ts,
                                    window=self.window)
-        self.S = int(splits) if splits else plan.num_splits
-        self.bq = min(plan.bq, q_max) if not is_prefill else plan.bq
-        self.plan = plan
+        self.plan, self.S = plan, plan.num_splits
+        self.bq = plan.bq if is_prefill else min(plan.bq, q_max)
+        # as the torch op does: max_query_len within one row tile = one row tile per request
+        self.flags = capi.FLAG_ONE_TILE_PER_REQUEST if q_max <= self.bq else 0
+
+        # staging layout: q | block_table | seq_lens | query_start_loc
+        off_q = 0
+        off_bt = _align(off_q + T * hq * D * 2)
+        off_len = _align(off_bt + R * width * 4)
+        off_qsl = _align(off_len + R * 4)
+        self.h2d = _align(off_qsl + (R + 1) * 4)
+        qsl = torch.zeros(R + 1, dtype=torch.int32)
+        qsl[1:] = torch.tensor(qlens, dtype=torch.int64).cumsum(0).to(torch.int32)
+        q_host = torch.randn((T, hq, D), generator=gen).to(torch.bfloat16)
+
+        def carve(buf):
+            return (buf[off_q:off_q + T * hq * D * 2].view(torch.bfloat16).view(T, hq, D),
+                    buf[off_bt:off_bt + R * width * 4].view(torch.int32).view(R, width),
+                    buf[off_len:off_len + R * 4].view(torch.int32),
+                    buf[off_qsl:off_qsl + (R + 1) * 4].view(torch.int32))
+
+        page = BS * hkv * CELL
+        self.sets = []
         for s in range(sets):
-            storage = torch.randint(0, 256, (need * page,), dtype=torch.uint8, device=device,
-                                    generator=torch.Generator(device=device).manual_seed(seed + 7 * s))
-            words = storage.view(torch.float32).view(need, BS, hkv_local, CELL // 4)
-            scale = torch.rand((need, BS, hkv_local), device=device) * 0.02 + 0.01
-            words[..., D // 4] = scale
-            words[..., CELL // 4 - 1] = scale
-            perm = (torch.arange(need) if os.environ.get("BENCH_SEQUENTIAL_BLOCKS") else torch.randperm(need, generator=g)).to(torch.int32)
-            bt = torch.zeros((R, max(nblk)), dtype=torch.int32)
+            storage = self._quantised_cache(torch, need, hkv, device, seed + 7 * s)
+            perm = torch.randperm(need, generator=gen).to(torch.int32)
+            bt = torch.zeros((R, width), dtype=torch.int32)
             k = 0
             for r, nb in enumerate(nblk):
                 bt[r, :nb] = perm[k:k + nb]
                 k += nb
+            stage_host = torch.zeros(self.h2d, dtype=torch.uint8).pin_memory()
+            hq_, hbt, hlen, hqsl = carve(stage_host)
+            hq_.copy_(q_host)
+            hbt.copy_(bt)
+            hlen.copy_(torch.tensor(lens, dtype=torch.int32))
+            hqsl.copy_(qsl)
+            stage_dev = stage_host.to(device)
+            dq, dbt, dlen, dqsl = carve(stage_dev)
             base = storage.data_ptr()
-            slot, head = (hkv_local * CELL, CELL) if layout == "NHD" else (CELL, BS * CELL)
+            slot, head = hkv * CELL, CELL
             views = host.CacheViews((base, page, slot, head), (base + D + 4, page, slot, head),
                                     (base + D, page, slot, head), (base + 2 * D + 4, page, slot, head),
-                                    need, BS, hkv_local, D)
-            self.sets.append(dict(storage=storage, views=views, bt_host=bt.pin_memory(), bt=bt.to(device)))
-        self.q_host = torch.randn((T, hq_local, D), generator=g).to(torch.bfloat16).pin_memory()
-        self.q = self.q_host.to(device)
-        qsl = torch.zeros(R + 1, dtype=torch.int32)
-        qsl[1:] = torch.tensor(qlens, dtype=torch.int64).cumsum(0).to(torch.int32)
-        self.qsl_host, self.lens_host = qsl.pin_memory(), torch.tensor(lens, dtype=torch.int32).pin_memory()
-        self.qsl, self.lens = self.qsl_host.to(device), self.lens_host.to(device)
-        self.out = torch.zeros((T, hq_local, D), dtype=torch.bfloat16, device=device)
-        self.out_host = torch.empty((T, hq_local, D), dtype=torch.bfloat16).pin_memory()
+                                    need, BS, hkv, D)
+            self.sets.append(dict(storage=storage, views=views, stage_host=stage_host, stage_dev=stage_dev,
+                                  q=dq, bt=dbt, lens=dlen, qsl=dqsl))
+        self.out = torch.zeros((T, hq, D), dtype=torch.bfloat16, device=device)
+        self.out_host = torch.empty((T, hq, D), dtype=torch.bfloat16).pin_memory()
+        self.d2h = self.out_host.numel() * 2
         self.ws_o = self.ws_lse = None
         if self.S > 1:
-            self.ws_o = torch.empty((self.S, T, hq_local, D), dtype=torch.float32, device=device)
-            self.ws_lse = torch.empty((self.S, T, hq_local), dtype=torch.float32, device=device)
-        # as the torch op does: max_query_len within one row tile = one row tile per request
-        if q_max <= self.bq:
-            self.flags |= capi.FLAG_ONE_TILE_PER_REQUEST
-        # tall row tiles: the automatic choice runs the integer kernel (short requests) and the
-        # row-major kernel (the others) one after the other
-        pair = KERNEL_CHOICE == capi.KERNEL_AUTO and self.bq * G > 16
-        self.kernels = (2 if pair else 1) + (1 if self.S > 1 else 0)
-        self.h2d = self.q_host.numel() * 2 + self.sets[0]["bt_host"].numel() * 4 + (2 * R + 1) * 4
-        self.d2h = self.out_host.numel() * 2
+            self.ws_o = torch.empty((self.S, T, hq, D), dtype=torch.float32, device=device)
+            self.ws_lse = torch.empty((self.S, T, hq), dtype=torch.float32, device=device)
+        a = self._args(0)
+        self.attention_kernels, self.combine_kernels = capi.load_library().launch_count(a)
+        self.kernels = self.attention_kernels + self.combine_kernels
 
-    def launch(self, which=0):
+    @staticmethod
+    def _quantised_cache(torch, num_blocks, hkv, device, seed):
+        """N(0, 1) K and V quantised per (token, KV head) like the cache writer does (scale =
+        max(absmax / 127, 1e-6), round half away from zero), in the packed NHD page layout."""
+        gen = torch.Generator(device=device).manual_seed(seed)
+        storage = torch.empty(num_blocks * BS * hkv * CELL, dtype=torch.uint8, device=device)
+        cells = storage.view(num_blocks, BS, hkv, CELL)
+        step = max(1, (64 << 20) // (BS * hkv * D))  # 256 MB of fp32 at a time
+        for b0 in range(0, num_blocks, step):
+            b1 = min(num_blocks, b0 + step)
+            for off in (0, D + 4):  # K half, V half of the cell
+                x = torch.randn((b1 - b0, BS, hkv, D), device=device, generator=gen)
+                scale = (x.abs().amax(-1) / 127.0).clamp_min(1e-6)
+                v = x * (1.0 / scale).unsqueeze(-1)
+                v = torch.where(v >= 0, v + 0.5, v - 0.5).clamp(-128.0, 127.0).trunc().to(torch.int8)
+                cells[b0:b1, :, :, off:off + D] = v.view(torch.uint8)
+                cells[b0:b1, :, :, off + D:off + D + 4] = scale.contiguous().view(torch.uint8).view(b1 - b0, BS, hkv, 4)
+        return storage
+
+    def _args(self, which, out=None):
         from pth_flash_attn_b200 import host
 
         s = self.sets[which % len(self.sets)]
-        host.attention_forward(self.q, self.out, s["views"], s["bt"], self.lens, self.qsl, bq=self.bq,
-                               num_splits=self.S, softmax_scale=D ** -0.5, ws_o=self.ws_o, ws_lse=self.ws_lse,
-                               window=self.window, causal=self.causal, flags=self.flags, kernel=KERNEL_CHOICE)
+        return host.fill_attn_args(s["q"], self.out if out is None else out, s["views"], s["bt"], s["lens"], s["qsl"],
+                                   bq=self.bq, num_splits=self.S, softmax_scale=D ** -0.5, ws_o=self.ws_o,
+                                   ws_lse=self.ws_lse, window=self.window, causal=self.causal)
 
-    def launch_attention_only(self, which=0):
-        """Only the attention kernel (for the per-kernel roofline timing)."""
-        from pth_flash_attn_b200 import capi, host
+    def launch(self, which=0, lse_out=None):
+        from pth_flash_attn_b200 import host
 
         s = self.sets[which % len(self.sets)]
-        a = host.fill_attn_args(self.q, self.out, s["views"], s["bt"], self.lens, self.qsl, bq=self.bq,
-                                num_splits=self.S, softmax_scale=D ** -0.5, ws_o=self.ws_o, ws_lse=self.ws_lse,
-                                window=self.window, causal=self.causal)
+        host.attention_forward(s["q"], self.out, s["views"], s["bt"], s["lens"], s["qsl"], bq=self.bq,
+                               num_splits=self.S, softmax_scale=D ** -0.5, ws_o=self.ws_o, ws_lse=self.ws_lse,
+                               window=self.window, causal=self.causal, flags=self.flags, lse_out=lse_out)
+
+    def launch_attention_only(self, which=0):
+        """Only the attention kernel(s) of the launch (for the per-kernel roofline timing)."""
+        from pth_flash_attn_b200 import capi
+
         lib = capi.load_library()
-        rc = lib.attention(a, options=capi.make_options(KERNEL_CHOICE, self.flags),
+        rc = lib.attention(self._args(which), options=capi.make_options(capi.KERNEL_AUTO, self.flags),
                            stream=self.torch.cuda.current_stream().cuda_stream)
         if rc != 0:
             raise RuntimeError(lib.last_error())
 
-    def e2e_step(self, which=0):
-        """Host buffers in, host buffer out: pinned H2D of the step's inputs, the launch, D2H of out."""
+    def e2e_pass(self, which=0):
+        """Host buffers in, host buffer out: ONE pinned H2D copy of the call's inputs (queries,
+        block table, lengths), the launch, D2H of out."""
         s = self.sets[which % len(self.sets)]
-        self.q.copy_(self.q_host, non_blocking=True)
-        s["bt"].copy_(s["bt_host"], non_blocking=True)
-        self.lens.copy_(self.lens_host, non_blocking=True)
-        self.qsl.copy_(self.qsl_host, non_blocking=True)
+        s["stage_dev"].copy_(s["stage_host"], non_blocking=True)
         self.launch(which)
         self.out_host.copy_(self.out, non_blocking=True)
+
+    def parity(self, which=0, picks_per_launch=12, seed=0):
+        """Runs the launch once more, with the log-sum-exp output, on the buffers that were
+        timed, and compares sampled (token, head) rows with the fp64 CPU oracle reading the
+        same cache bytes.  Returns (max |d out|, mean |d out|, max |d lse|, rows)."""
+        from oracle import paged_int8_attention as orc
+
+        torch = self.torch
+        s = self.sets[which % len(self.sets)]
+        lse = torch.full((self.T, self.hq), float("nan"), dtype=torch.float32, device=self.out.device)
+        self.out.fill_(float("nan"))
+        self.launch(which, lse_out=lse)
+        torch.cuda.synchronize()
+        storage = s["storage"].cpu().numpy()
+        page = BS * self.hkv * CELL
+        k, v, ks, vs = orc.stream_views(D, self.hkv, BS, "NHD", page, 0)
+        lens = np.asarray(self.launch_spec["seq_lens"], dtype=np.int32)
+        cache = orc.PagedInt8Cache(storage=storage, k=k, v=v, ks=ks, vs=vs, block_table=s["bt"].cpu().numpy(),
+                                   seq_lens=lens, num_blocks=s["views"].num_blocks, block_size=BS, Hkv=self.hkv,
+                                   D=D, layout="NHD", page_bytes=page, storage_offset_bytes=0)
+        qsl = s["qsl"].cpu().numpy().astype(np.int64)
+        rng = np.random.default_rng(seed)
+        reqs = {int(np.argmax(lens)), int(np.argmin(lens)), 0, self.R - 1}
+        reqs |= set(rng.integers(0, self.R, size=picks_per_launch).tolist())
+        picks = []
+        for r in sorted(reqs)[:picks_per_launch]:
+            for tok in {int(qsl[r]), int(qsl[r + 1]) - 1, int(rng.integers(qsl[r], qsl[r + 1]))}:
+                picks.append((tok, int(rng.integers(0, self.hq))))
+        q = s["q"].float().cpu().numpy()
+        ref_out, ref_lse = orc.ref_attention_rows(q, cache, qsl, D ** -0.5, picks, window=self.window,
+                                                  causal=self.causal)
+        out = self.out.float().cpu().numpy()
+        lse_h = lse.cpu().numpy()
+        got = np.stack([out[t, h] for t, h in picks])
+        got_lse = np.array([lse_h[t, h] for t, h in picks])
+        whole_finite = bool(np.isfinite(out).all())
+        d = np.abs(got - ref_out)
+        return dict(max_abs=float(d.max()), mean_abs=float(d.mean()), lse_abs=float(np.abs(got_lse - ref_lse).max()),
+                    rows=len(picks), all_rows_written=whole_finite)
+
+
+class Workload:
+    """All launches of a configuration for this rank, with CUDA graphs of a whole pass and of
+    the attention kernels alone (one graph per cache set; sets rotate so that a pass never
+    finds its cache in L2)."""
+
+    def __init__(self, torch, name, rank, world, device, num_sms, l2_bytes, seed=1234):
+        self.torch, self.name, self.world = torch, name, world
+        self.launches = workload_launches(name)
+        hkv_total = self.launches[0]["Hkv"]
+        if hkv_total % world:
+            raise SystemExit(f"Hkv={hkv_total} does not shard over {world} GPUs")
+        self.bytes_local = sum(kv_bytes(l, l["Hkv"] // world) for l in self.launches)
+        self.bytes_total = sum(kv_bytes(l, l["Hkv"]) for l in self.launches)
+        self.flops_total = sum(attn_flops(l, l["Hq"]) for l in self.launches)
+        self.flops_local = self.flops_total // world
+        sets = 1 if self.bytes_local >= 4 * l2_bytes else int(-(-4 * l2_bytes // self.bytes_local))
+        self.num_sets = min(sets, 64)
+        self.dls = [DeviceLaunch(torch, l, rank, world, device, seed + 100 * i + rank, num_sms, sets=self.num_sets)
+                    for i, l in enumerate(self.launches)]
+        self.kernels_per_pass = sum(d.kernels for d in self.dls)
+        for d in self.dls:  # one eager pass: sets kernel attributes, builds the page maps
+            d.launch(0)
+        torch.cuda.synchronize()
+        self.graphs = self._capture(lambda d, s: d.launch(s))
+        self.attn_graphs = self._capture(lambda d, s: d.launch_attention_only(s))
+
+    def _capture(self, fn):
+        torch = self.torch
+        graphs, side = [], torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            for s in range(self.num_sets):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    for d in self.dls:
+                        fn(d, s)
+                graphs.append(g)
+        torch.cuda.synchronize()
+        return graphs
+
+    def run_pass(self, i):
+        self.graphs[i % self.num_sets].replay()
+
+    def run_attention(self, i):
+        self.attn_graphs[i % self.num_sets].replay()
+
+    def run_e2e(self, i):
+        for d in self.dls:
+            d.e2e_pass(i % self.num_sets)
+
+    def describe(self):
+        return [{"batch": len(l["seq_lens"]), "context_max": max(l["seq_lens"]), "q_len": max(l["q_lens"]),
+                 "window": l.get("window", 0), "num_splits_bound": d.S, "bq": d.bq}
+                for l, d in zip(self.launches, self.dls)]
+
+    def parity(self):
+        worst = dict(max_abs=0.0, mean_abs=0.0, lse_abs=0.0, rows=0, all_rows_written=True)
+        for i, d in enumerate(self.dls):
+            r = d.parity(which=0, seed=17 + i)
+            worst["max_abs"] = max(worst["max_abs"], r["max_abs"])
+            worst["mean_abs"] = max(worst["mean_abs"], r["mean_abs"])
+            worst["lse_abs"] = max(worst["lse_abs"], r["lse_abs"])
+            worst["rows"] += r["rows"]
+            worst["all_rows_written"] &= r["all_rows_written"]
+        worst["within_tolerance"] = bool(worst["max_abs"] <= 2e-2 and worst["mean_abs"] <= 2e-3 and
+                                         worst["lse_abs"] <= 1e-3 and worst["all_rows_written"])
+        return worst
 
 
 # --------------------------------------------------------------------------
 # clocks
 # --------------------------------------------------------------------------
-# Kernel family of the C ABI options (0 = the library's own choice); --kernel overrides it for exploration.
-KERNEL_CHOICE = 0
-
-# Measured with ncu on the batch-64 decode launch (see profiles/).
-DRAM_BYTES_PER_ALGORITHMIC_BYTE = 1.22
-
-
 class ClockSampler:
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -246,16 +384,10 @@ class ClockSampler:
             except subprocess.TimeoutExpired:
                 self.proc.kill()
 
-    def summary(self, t0=None, t1=None):
-        """Median SM clock and the throttle reasons seen.  With (t0, t1) only the samples
-        taken inside that host-time window count, if there are at least three of them; a
-        shorter timed region falls back to every sample taken while the GPU was under the
-        benchmark's load (warm-up, timed steps, end-to-end and per-kernel passes)."""
-        rows, window = [r for _, r in self.rows], "whole load phase"
-        if t0 is not None:
-            inside = [r for t, r in self.rows if t0 <= t <= t1]
-            if len(inside) >= 3:
-                rows, window = inside, "timed region"
+    def summary(self, t0, t1):
+        """Median SM clock and the throttle reasons seen by the samples taken between the host
+        times t0 and t1 (the timed region)."""
+        rows = [r for t, r in self.rows if t0 <= t <= t1]
         sm, mx, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for r in rows:
@@ -268,14 +400,14 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm), "window": window}
+                "reasons": sorted(reasons), "samples": len(sm), "window": "timed region"}
 
 
 # --------------------------------------------------------------------------
 # CPU baselines
 # --------------------------------------------------------------------------
 def cpu_port_baseline(seconds_target=12.0):
-    """The numpy fp64 oracle on a bounded sample of the default workload: decode requests at
+    """The numpy fp64 oracle on a bounded sample of the headline workload: decode requests at
     context 8192 (Hq 32, Hkv 8), as many as fit the time target."""
     from oracle import paged_int8_attention as orc
 
@@ -299,7 +431,7 @@ def cpu_port_baseline(seconds_target=12.0):
     except Exception:
         threads = os.cpu_count() or 1
     return {"value": gbs, "unit": "GB/s", "cores": int(threads), "kind": "port",
-            "sample": f"{reqs} decode requests of the default workload (context {L}, Hq {HQ}, Hkv {HKV}, D {D}) "
+            "sample": f"{reqs} decode requests of the headline workload (context {L}, Hq {HQ}, Hkv {HKV}, D {D}) "
                       f"through the numpy fp64 oracle incl. the paged gather, {done:.1f} s; cache build {t_build:.1f} s"}
 
 
@@ -354,7 +486,7 @@ def reference_arm(args):
     ref = orc.ref_attention_paged(orc.f32_from_bf16_bits(q), c, [0, 1], D ** -0.5)
     assert np.abs(out - ref.out).max() < 1e-3, "reference library disagrees with the oracle"
     gbs = L * HKV * CELL / dt / 1e9
-    base.update({"value": gbs, "ms_per_step": dt * 1e3, "gpu_launches": 0,
+    base.update({"value": gbs, "ms_per_step": dt * 1e3, "gpu_launches": 0, "same_config": False,
                  "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": 32, "kind": "reference",
                                   "sample": f"one decode request truncated to {L} keys (Hq {HQ}, Hkv {HKV}, D {D}) per "
                                             "step through pth_ref_attention_host; the library always runs 32 lock-step "
@@ -364,25 +496,118 @@ def reference_arm(args):
 
 
 # --------------------------------------------------------------------------
+# timing
+# --------------------------------------------------------------------------
+# DRAM bytes the attention kernel moves per algorithmic byte, from the ncu capture of the
+# batch-64 decode launch (dram__bytes_read + dram__bytes_write over 1.107 GB of KV).
+DRAM_BYTES_PER_ALGORITHMIC_BYTE = 1.22
+
+
+class Timer:
+    def __init__(self, torch, dist, device, world):
+        self.torch, self.dist, self.device, self.world = torch, dist, device, world
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, ms):
+        if self.world > 1:
+            t = self.torch.tensor([ms], device=self.device, dtype=self.torch.float64)
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    def passes_per_step(self, fn, steps, target_s):
+        """Passes per step so that `steps` steps last about target_s (the same on every rank)."""
+        torch = self.torch
+        for i in range(3):
+            fn(i)
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(10):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        pass_ms = self.max_over_ranks(e0.elapsed_time(e1) / 10)
+        return max(1, int(round(target_s * 1e3 / max(steps, 1) / max(pass_ms, 1e-3))))
+
+    def timed(self, fn, steps, warmup, pps):
+        """Exactly `steps` steps of `pps` passes between two barriers; device time by CUDA events
+        on the launching stream, maximum over ranks.  Returns ms per pass and the spread of the
+        steps on this rank."""
+        torch = self.torch
+        c = 0
+        for _ in range(warmup):
+            for _ in range(pps):
+                fn(c)
+                c += 1
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        self.barrier()
+        t0 = time.monotonic()
+        evs[0].record()
+        for k in range(steps):
+            for _ in range(pps):
+                fn(c)
+                c += 1
+            evs[k + 1].record()
+        self.barrier()
+        t1 = time.monotonic()
+        total = self.max_over_ranks(evs[0].elapsed_time(evs[-1]))
+        per = sorted(evs[k].elapsed_time(evs[k + 1]) / pps for k in range(steps))
+        return dict(ms_per_pass=total / (steps * pps), ms_per_step=total / steps, t0=t0, t1=t1,
+                    spread={"min": per[0], "median": per[len(per) // 2], "max": per[-1]})
+
+
+def roofline_of(wl, world, attn_ms, pass_ms, hbm_peak, tc_peak, tc_sustained, peak_src):
+    """The roofline block of a workload on this rank: achieved = algorithmic bytes (flops) of
+    the rank's shard over the time of its attention kernels alone."""
+    t_bytes = wl.bytes_local / (hbm_peak * 1e9) * 1e3       # ms at the HBM peak
+    t_flops = wl.flops_local / (tc_peak * 1e12) * 1e3       # ms at the tensor peak
+    gbs = wl.bytes_local / (attn_ms * 1e-3) / 1e9
+    tfs = wl.flops_local / (attn_ms * 1e-3) / 1e12
+    if wl.name in TENSOR_BOUND:
+        roof = {"bound": "tensor", "achieved": tfs, "peak": tc_peak, "unit": "TFLOP/s", "frac": tfs / tc_peak,
+                "frac_of_sustained_peak": tfs / tc_sustained if tc_sustained else None, "traffic": None,
+                "kernel": "umma_rows_attention_kernel"}
+    elif wl.name == "mixed":
+        # two kernels one after the other: the integer kernel reads the decode and verify requests'
+        # cache (HBM-bound), the row-major kernel computes the prefill chunks (tensor-bound); the
+        # launch can be no faster than the larger of its two bounds
+        bound_ms = max(t_bytes, t_flops)
+        roof = {"bound": "hbm" if t_bytes >= t_flops else "tensor", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s",
+                "frac": bound_ms / attn_ms, "tflops": tfs, "bound_ms": bound_ms, "traffic": None,
+                "kernel": "umma_i8_attention_kernel + umma_rows_attention_kernel"}
+    else:
+        rows_kernel = all(d.attention_kernels == 1 and d.bq * d.G > 16 for d in wl.dls)
+        roof = {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
+                "traffic": None if rows_kernel else DRAM_BYTES_PER_ALGORITHMIC_BYTE * wl.bytes_local,
+                "kernel": "umma_rows_attention_kernel" if rows_kernel else "umma_i8_attention_kernel"}
+        if not rows_kernel:
+            roof["traffic_source"] = "ncu capture of long_decode_b64, scaled by bytes"
+    roof.update({"peak_source": peak_src, "kernel_ms_per_pass": attn_ms, "pass_ms": pass_ms,
+                 "algorithmic_bytes_per_pass": wl.bytes_local, "flops_per_pass": wl.flops_local,
+                 "frac_of_nominal_8TBs": gbs / 8000.0 if roof["bound"] == "hbm" else None})
+    return roof
+
+
+# --------------------------------------------------------------------------
 # main
 # --------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1000)
-    ap.add_argument("--warmup", type=int, default=20)
-    ap.add_argument("--config", default="long_decode")
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--config", default=HEADLINE, help="workload of the headline numbers")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--splits", type=int, default=0, help="override the planner's split count (exploration)")
-    ap.add_argument("--kernel", type=int, default=0, help="kernel family of the C ABI (exploration; 0 = automatic)")
-    ap.add_argument("--layout", default="NHD", choices=["NHD", "HND"], help="physical order inside a page")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-per-config", action="store_true", help="only the headline workload")
     ap.add_argument("--profile", action="store_true",
                     help="three eager passes over the workload and exit (the command to run under ncu)")
     args = ap.parse_args()
-    global KERNEL_CHOICE
-    KERNEL_CHOICE = args.kernel
     if args.impl == "reference":
         reference_arm(args)
         return
@@ -407,162 +632,123 @@ def main():
     props = torch.cuda.get_device_properties(device)
     num_sms = props.multi_processor_count
     l2_bytes = getattr(props, "L2_cache_size", 126 * 2 ** 20)
+    timer = Timer(torch, dist, device, world)
+    steps, warmup = max(args.steps, 1), max(args.warmup, 3)
 
-    launches = workload_launches(args.config)
-    hkv_total = launches[0]["Hkv"]
-    if hkv_total % world:
-        raise SystemExit(f"Hkv={hkv_total} does not shard over {world} GPUs")
-    step_bytes_local = sum(kv_bytes(l, l["Hkv"] // world) for l in launches)
-    sets = 1 if step_bytes_local >= 4 * l2_bytes else int(-(-4 * l2_bytes // step_bytes_local))
-    sets = min(sets, 64)
-    dls = [DeviceLaunch(torch, l, l["Hkv"] // world, l["Hq"] // world, device, 1234 + 100 * i + rank, num_sms,
-                        sets=sets, splits=args.splits, layout=args.layout) for i, l in enumerate(launches)]
-    step_bytes_total = sum(kv_bytes(l, l["Hkv"]) for l in launches)
-    step_flops_total = sum(attn_flops(l, l["Hq"]) for l in launches)
-    kernels_per_step = sum(d.kernels for d in dls)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # one eager pass (also sets kernel attributes), then one CUDA graph per cache set
-    for d in dls:
-        d.launch(0)
-    torch.cuda.synchronize()
-    if args.profile:
-        for i in range(2):
-            for d in dls:
-                d.launch(i)
-        torch.cuda.synchronize()
-        print(json.dumps({"profile": args.config, "launches_per_pass": kernels_per_step, "passes": 3}))
-        return
-    graphs = []
-    if not args.no_graph:
-        side = torch.cuda.Stream()
-        with torch.cuda.stream(side):
-            for s in range(sets):
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=side):
-                    for d in dls:
-                        d.launch(s)
-                graphs.append(g)
-        torch.cuda.synchronize()
-
-    def run_step(i):
-        if graphs:
-            graphs[i % sets].replay()
-        else:
-            for d in dls:
-                d.launch(i % sets)
-
-    def timed(fn, steps):
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(steps):
-            fn(i)
-        e1.record()
-        barrier()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device=device)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
-
-    clk = ClockSampler(local_rank)
-    clk.__enter__()
-    for i in range(max(args.warmup, 3)):
-        run_step(i)
-    t_begin = time.monotonic()
-    ms_total = timed(run_step, args.steps)
-    t_end = time.monotonic()
-    ms_per_step = ms_total / args.steps
-    value = step_bytes_total / (ms_per_step * 1e-3) / 1e9
-
-    # end to end through the host-buffer call
-    def e2e(i):
-        for d in dls:
-            d.e2e_step(i % sets)
-
-    for i in range(3):
-        e2e(i)
-    ms_e2e = timed(e2e, args.steps) / args.steps
-    e2e_value = step_bytes_total / (ms_e2e * 1e-3) / 1e9
-
-    # per-kernel timing of the dominant kernel (attention) for the roofline line
-    attn_ms = 0.0
-    reps = max(10, min(args.steps, 50))
-    evs = []
-    torch.cuda.synchronize()
-    for i in range(reps):
-        for d in dls:
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            d.launch_attention_only(i % sets)
-            b.record()
-            evs.append((a, b))
-    torch.cuda.synchronize()
-    attn_ms = sum(a.elapsed_time(b) for a, b in evs) / reps  # all attention launches of one step
-    clk.__exit__()
-    clocks = clk.summary(t_begin, t_end)
     peaks_path = REPO / "MEASURED_PEAKS.json"
     if peaks_path.is_file():
         peaks, peak_src = json.loads(peaks_path.read_text()), "measured"
         hbm_peak, tc_peak = float(peaks["hbm_gbs"]), float(peaks["bf16_tflops"])
+        tc_sustained = float(peaks.get("bf16_tflops_sustained", 0.0))
     else:
-        hbm_peak, tc_peak, peak_src = 6650.0, 1590.0, "fallback"
-    tensor_bound = args.config in ("chunked_prefill",)
-    if tensor_bound:
-        achieved = (step_flops_total / world) / (attn_ms * 1e-3) / 1e12
-        roof = {"bound": "tensor", "achieved": achieved, "peak": tc_peak, "unit": "TFLOP/s",
-                "frac": achieved / tc_peak, "traffic": None}
-    else:
-        achieved = step_bytes_local / (attn_ms * 1e-3) / 1e9
-        roof = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                "traffic": None}
-    roof["peak_source"] = peak_src
-    # the library sends row tiles of more than 16 rows to the row-major bf16 kernel
-    rows_kernel = any(d.bq * (l["Hq"] // l["Hkv"]) > 16 for l, d in zip(launches, dls))
-    roof["kernel"] = "umma_rows_attention_kernel" if rows_kernel else "umma_i8_attention_kernel"
-    roof["kernel_ms_per_step"] = attn_ms
-    roof["algorithmic_bytes_per_step"] = step_bytes_local
-    if not tensor_bound:
-        # DRAM bytes per algorithmic byte of the attention kernel, from the ncu capture of the
-        # batch-64 decode launch summarised under profiles/ (dram__bytes_read + write over
-        # 1.107 GB of KV); traffic grows in proportion to the keys read, so the ratio scales to
-        # the workload's bytes.
-        roof["traffic"] = DRAM_BYTES_PER_ALGORITHMIC_BYTE * step_bytes_local
-        roof["traffic_source"] = "ncu capture of long_decode_b64, scaled by bytes"
+        hbm_peak, tc_peak, tc_sustained, peak_src = 6650.0, 1590.0, 1400.0, "fallback"
+
+    wl = Workload(torch, args.config, rank, world, device, num_sms, l2_bytes)
+    if args.profile:
+        for i in range(2):
+            for d in wl.dls:
+                d.launch(i)
+        torch.cuda.synchronize()
+        print(json.dumps({"profile": args.config, "launches_per_pass": wl.kernels_per_pass, "passes": 3}))
+        return
+
+    clk = ClockSampler(local_rank)
+    clk.__enter__()
+    pps = timer.passes_per_step(wl.run_pass, steps, 1.0)
+    main_t = timer.timed(wl.run_pass, steps, warmup, pps)
+    clocks = clk.summary(main_t["t0"], main_t["t1"])
+    clk.__exit__()
+    ms_pass = main_t["ms_per_pass"]
+    value = wl.bytes_total / (ms_pass * 1e-3) / 1e9
+
+    # the attention kernels alone, in graphs of their own (for the roofline of the dominant kernel)
+    pps_a = timer.passes_per_step(wl.run_attention, steps, 0.3)
+    attn_ms = timer.timed(wl.run_attention, steps, 3, pps_a)["ms_per_pass"]
+    # a graph of fewer kernels cannot take longer than the whole pass; jitter of two runs aside
+    attn_ms = min(attn_ms, ms_pass)
+
+    # end to end through the host-buffer call: pipelined (no synchronisation between passes)...
+    pps_e = timer.passes_per_step(wl.run_e2e, steps, 0.5)
+    e2e_t = timer.timed(wl.run_e2e, steps, 3, pps_e)
+    e2e_value = wl.bytes_total / (e2e_t["ms_per_pass"] * 1e-3) / 1e9
+    # ... and one call at a time: host clock from the copy-in to the result on the host
+    lat = []
+    for i in range(40):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        wl.run_e2e(i)
+        torch.cuda.synchronize()
+        lat.append((time.perf_counter() - t0) * 1e3)
+    lat_ms = timer.max_over_ranks(float(np.median(lat[5:])))
+
+    roof = roofline_of(wl, world, attn_ms, ms_pass, hbm_peak, tc_peak, tc_sustained, peak_src)
+    parity = wl.parity()
+    tensor_headline = args.config in TENSOR_BOUND
+    line = {
+        "metric": "attention_tflops" if tensor_headline else "kv_read_bandwidth",
+        "value": wl.flops_total / (ms_pass * 1e-3) / 1e12 if tensor_headline else value,
+        "unit": "TFLOP/s" if tensor_headline else "GB/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+        "passes_per_step": pps, "ms_per_step": main_t["ms_per_step"], "ms_per_pass": ms_pass,
+        "us_per_layer": ms_pass * 1e3, "ms_per_pass_spread": main_t["spread"],
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int8" if roof["kernel"].startswith("umma_i8") else "bf16", "data": "synthetic",
+        "config": {"workload": args.config, "launches": wl.describe(), "Hq": wl.launches[0]["Hq"],
+                   "Hkv": wl.launches[0]["Hkv"], "D": D, "block_size": BS, "sharding": f"kv_heads/{world}",
+                   "l2_policy": ("inputs larger than L2" if wl.num_sets == 1 else
+                                 f"rotation over {wl.num_sets} cache sets (>= 4x L2)"),
+                   "cuda_graph": True,
+                   "arithmetic": "int8 cache bytes and int8 digits of Q / P on tcgen05 kind::i8 with int32 accumulators "
+                                 "(short row tiles); int8 cache widened exactly to bf16, tcgen05 kind::f16 with fp32 "
+                                 "accumulators (tall row tiles); fp32 softmax",
+                   "kv_bytes_per_pass": wl.bytes_total, "flops_per_pass": wl.flops_total},
+        "tflops": wl.flops_total / (ms_pass * 1e-3) / 1e12,
+        "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_pass": e2e_t["ms_per_pass"],
+                "h2d_bytes_per_step": sum(d.h2d for d in wl.dls) * pps_e,
+                "d2h_bytes_per_step": sum(d.d2h for d in wl.dls) * pps_e, "passes_per_step": pps_e,
+                "h2d_bytes_per_pass": sum(d.h2d for d in wl.dls), "d2h_bytes_per_pass": sum(d.d2h for d in wl.dls),
+                "mode": "pipelined throughput: passes are enqueued back to back, no synchronisation between them",
+                "sync_latency_ms_per_pass": lat_ms,
+                "sync_latency_note": "one pass at a time: copy-in, launches, copy-out, stream synchronised (host clock, median)"},
+        "gpu_launches": wl.kernels_per_pass * pps * steps,
+        "gpu_launches_per_pass": wl.kernels_per_pass,
+        "clocks": clocks, "roofline": roof,
+        "parity_checked": parity["within_tolerance"], "parity": parity,
+    }
+    del wl
+    torch.cuda.empty_cache()
+
+    if not args.no_per_config:
+        per = {}
+        for name in PER_CONFIG:
+            if name == args.config:
+                per[name] = {"ms_per_pass": ms_pass, "kv_gbs": value, "tflops": line["tflops"],
+                             "roofline_frac": roof["frac"], "bound": roof["bound"], "kernel_ms_per_pass": attn_ms,
+                             "parity_checked": parity["within_tolerance"]}
+                continue
+            w = Workload(torch, name, rank, world, device, num_sms, l2_bytes)
+            p1 = timer.passes_per_step(w.run_pass, 5, 0.4)
+            t = timer.timed(w.run_pass, 5, 3, p1)
+            p2 = timer.passes_per_step(w.run_attention, 5, 0.2)
+            a_ms = min(timer.timed(w.run_attention, 5, 3, p2)["ms_per_pass"], t["ms_per_pass"])
+            r = roofline_of(w, world, a_ms, t["ms_per_pass"], hbm_peak, tc_peak, tc_sustained, peak_src)
+            par = w.parity()
+            per[name] = {"ms_per_pass": t["ms_per_pass"], "us_per_layer": t["ms_per_pass"] * 1e3,
+                         "kv_gbs": w.bytes_total / (t["ms_per_pass"] * 1e-3) / 1e9,
+                         "tflops": w.flops_total / (t["ms_per_pass"] * 1e-3) / 1e12,
+                         "roofline_frac": r["frac"], "bound": r["bound"], "unit": r["unit"], "achieved": r["achieved"],
+                         "peak": r["peak"], "kernel": r["kernel"], "kernel_ms_per_pass": a_ms,
+                         "launches": w.describe(), "l2_sets": w.num_sets, "gpu_launches_per_pass": w.kernels_per_pass,
+                         "parity_checked": par["within_tolerance"], "parity": par}
+            del w
+            torch.cuda.empty_cache()
+        line["per_config"] = per
 
     if rank == 0:
-        line = {
-            "metric": "kv_read_bandwidth", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "us_per_layer": ms_per_step * 1e3,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16" if rows_kernel else "int8",
-            "data": "synthetic",
-            "config": {"workload": args.config, "launches": [
-                {"batch": len(l["seq_lens"]), "context_max": max(l["seq_lens"]), "q_len": max(l["q_lens"]),
-                 "window": l.get("window", 0), "num_splits": d.S, "bq": d.bq} for l, d in zip(launches, dls)],
-                "Hq": launches[0]["Hq"], "Hkv": hkv_total, "D": D, "block_size": BS, "sharding": f"kv_heads/{world}",
-                "l2_policy": ("inputs larger than L2" if sets == 1 else f"rotation over {sets} cache sets (>= 4x L2)"),
-                "cuda_graph": bool(graphs),
-                "arithmetic": ("int8 cache widened exactly to bf16 in shared memory, tcgen05 kind::f16 with fp32 "
-                               "accumulators in TMEM, fp32 softmax" if rows_kernel else
-                               "int8 cache bytes and int8 digits of Q / P on tcgen05 kind::i8, int32 accumulators, "
-                               "fp32 softmax and output accumulation"),
-                "kv_bytes_per_step": step_bytes_total, "flops_per_step": step_flops_total},
-            "tflops": step_flops_total / (ms_per_step * 1e-3) / 1e12,
-            "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": ms_e2e,
-                    "h2d_bytes_per_step": sum(d.h2d for d in dls), "d2h_bytes_per_step": sum(d.d2h for d in dls)},
-            "gpu_launches": kernels_per_step * args.steps,
-            "clocks": clocks, "roofline": roof,
-        }
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_port_baseline()
         print(json.dumps(line))
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

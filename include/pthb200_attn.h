@@ -207,7 +207,9 @@ int32_t pthb200_combine_ex(const PthAttnCombineArgs* args, const PthB200Options*
 
 /* Attention + combine in one call that performs NO allocation: the split partials
  * live in a fixed 8 MiB array inside this library (a __device__ array of the loaded
- * module, one instance per GPU) instead of a caller workspace; args->ws_o / ws_lse
+ * module, one instance per GPU; the instance used is that of the CURRENT device of the
+ * calling thread, which must be the device `stream` belongs to) instead of a caller
+ * workspace; args->ws_o / ws_lse
  * and their strides are ignored.  It has no counterpart in the reference, whose op
  * always takes the workspace from its caller.  It is for callers that have no way
  * to obtain device memory at the point of the call: an engine that has handed all
@@ -264,6 +266,17 @@ int32_t pthb200_test_tile_i8(const void* k, const void* q, const void* v, const 
  * TMEM; s_out fp32 [128 rows][128 keys] = q k^T, o_out fp32 [128 rows][128] = pm v. */
 int32_t pthb200_test_tile_rows(const void* k, const void* q, const void* v, const void* pm,
                                float* s_out, float* o_out, void* stream);
+/* The work-item schedule of the persistent integer kernel, computed on the HOST from host
+ * copies of query_start_loc [num_reqs + 1] and seq_lens [num_reqs] by the same functions
+ * the device runs: out [max_items][8] int32 receives, CTA by CTA and in running order,
+ * {cta, request, row tile, KV head, split, splits of the request, first KV tile, end KV
+ * tile}.  Returns the number of items (only the first max_items are stored), or
+ * PTH_ATTN_EINVAL.  Counterpart of the reference's geometry unit tests
+ * (tests/cpp/test_geometry.cpp:298-451: split partition, tile numbering). */
+int32_t pthb200_test_schedule(const int32_t* query_start_loc, const int32_t* seq_lens, int32_t num_reqs,
+                              int32_t group, int32_t num_kv_heads, int32_t bq, int32_t num_splits,
+                              int32_t window, int32_t causal, int32_t row_class, int32_t class_rows,
+                              int32_t num_ctas, int32_t* out, int32_t max_items);
 /* Synchronises the device, returns and clears the status word in which a
  * kernel records a bounded wait that gave up (0 = none). */
 int32_t pthb200_device_status(int32_t* status);

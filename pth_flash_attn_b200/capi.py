@@ -130,6 +130,7 @@ EXPORTED_SYMBOLS = (
     "pthb200_tile_tokens",
     "pthb200_check_call",
     "pthb200_launch_count",
+    "pthb200_test_schedule",
     "pthb200_test_tile",
     "pthb200_test_tile_i8",
     "pthb200_test_tile_rows",
@@ -179,6 +180,9 @@ class B200Lib:
         lib.pthb200_launch_count.restype = ctypes.c_int32
         lib.pthb200_launch_count.argtypes = [ap, ctypes.POINTER(ctypes.c_int32),
                                              ctypes.POINTER(ctypes.c_int32)]
+        lib.pthb200_test_schedule.restype = ctypes.c_int32
+        lib.pthb200_test_schedule.argtypes = ([ctypes.c_void_p] * 2 + [ctypes.c_int32] * 10
+                                              + [ctypes.c_void_p, ctypes.c_int32])
         lib.pthb200_test_tile.restype = ctypes.c_int32
         lib.pthb200_test_tile.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int32, ctypes.c_void_p]
         lib.pthb200_test_tile_i8.restype = ctypes.c_int32
@@ -232,6 +236,28 @@ class B200Lib:
         if rc != OK:
             raise RuntimeError("pthb200_device_status failed")
         return v.value
+
+    def schedule(self, query_start_loc, seq_lens, *, group: int, num_kv_heads: int, bq: int,
+                 num_splits: int, num_ctas: int, window: int = 0, causal: bool = True,
+                 row_class: int = 0, class_rows: int = 0):
+        """The persistent kernel's work-item schedule, computed on the host (no device access).
+
+        Returns an int32 array ``[items, 8]`` of ``(cta, request, row tile, KV head, split,
+        splits of the request, first KV tile, end KV tile)`` in the order the CTAs run them.
+        """
+        import numpy as np
+
+        qsl = np.ascontiguousarray(query_start_loc, dtype=np.int32)
+        lens = np.ascontiguousarray(seq_lens, dtype=np.int32)
+        args = (qsl.ctypes.data, lens.ctypes.data, len(lens), group, num_kv_heads, bq, num_splits, window,
+                int(causal), row_class, class_rows, num_ctas)
+        probe = np.zeros((1, 8), dtype=np.int32)
+        n = int(self.lib.pthb200_test_schedule(*args, probe.ctypes.data, 0))
+        if n < 0:
+            raise RuntimeError(self.last_error())
+        out = np.zeros((max(n, 1), 8), dtype=np.int32)
+        self.lib.pthb200_test_schedule(*args, out.ctypes.data, n)
+        return out[:n]
 
     def launch_count(self, args: PthAttnArgs) -> tuple[int, int]:
         a, c = ctypes.c_int32(0), ctypes.c_int32(0)

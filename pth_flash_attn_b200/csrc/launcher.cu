@@ -9,6 +9,7 @@
 #include <string>
 
 #include "params.cuh"
+#include "sched.cuh"
 
 namespace pthb200 {
 namespace {
@@ -207,12 +208,14 @@ int32_t choose_family(const KernelParams& p, const PthB200Options* opt, int32_t*
   return PTH_ATTN_OK;
 }
 
-int32_t attention_impl(const PthAttnArgs* a, const PthB200Options* opt, void* stream, bool launch) {
+int32_t attention_impl(const PthAttnArgs* a, const PthB200Options* opt, void* stream, bool launch,
+                       int32_t* kernels = nullptr) {
   g_last_error.clear();
   KernelParams p;
   if (int32_t rc = build_attention(a, opt, &p)) return rc;
   int32_t family = 0;
   if (int32_t rc = choose_family(p, opt, &family)) return rc;
+  if (kernels != nullptr) *kernels = family == kFamilyPair ? 2 : 1;
   if (!launch) return PTH_ATTN_OK;
   cudaError_t err;
   if (family == kFamilyPair) {
@@ -238,7 +241,7 @@ int32_t attention_impl(const PthAttnArgs* a, const PthB200Options* opt, void* st
   return PTH_ATTN_OK;
 }
 
-int32_t combine_impl(const PthAttnCombineArgs* a, const PthB200Options* opt, void* stream) {
+int32_t combine_impl(const PthAttnCombineArgs* a, const PthB200Options* opt, void* stream, bool launch = true) {
   g_last_error.clear();
   PTHB_REQUIRE(a != nullptr, "args is NULL");
   PTHB_REQUIRE(a->abi_version == PTH_ATTN_ABI_VERSION, "args.abi_version does not match the library");
@@ -286,6 +289,7 @@ int32_t combine_impl(const PthAttnCombineArgs* a, const PthB200Options* opt, voi
   c.num_q_heads = a->num_q_heads;
   c.head_size = a->head_size;
   c.num_splits = a->num_splits;
+  if (!launch) return PTH_ATTN_OK;
   const cudaError_t err = launch_combine_kernel(c, static_cast<cudaStream_t>(stream));
   if (err != cudaSuccess) return fail(PTH_ATTN_ECUDA, std::string("combine launch failed: ") + cudaGetErrorString(err));
   return PTH_ATTN_OK;
@@ -337,11 +341,71 @@ int32_t pthb200_tile_tokens(int32_t wm, int32_t group, int32_t max_query_len) {
 int32_t pthb200_check_call(const PthAttnArgs* args) { return pthb200::attention_impl(args, nullptr, nullptr, false); }
 
 int32_t pthb200_launch_count(const PthAttnArgs* args, int32_t* attention_kernels, int32_t* combine_kernels) {
-  const int32_t rc = pthb200::attention_impl(args, nullptr, nullptr, false);
+  int32_t kernels = 0;
+  const int32_t rc = pthb200::attention_impl(args, nullptr, nullptr, false, &kernels);
   if (rc != PTH_ATTN_OK) return rc;
-  if (attention_kernels) *attention_kernels = 1;
+  if (attention_kernels) *attention_kernels = kernels;  // 2: short requests and tall ones on their own kernels
   if (combine_kernels) *combine_kernels = args->num_splits > 1 ? 1 : 0;
   return PTH_ATTN_OK;
+}
+
+// Host restatement of the persistent kernel's work-item schedule, built from the same
+// functions the device runs (sched.cuh): the items each of `num_ctas` CTAs would run, in
+// the order it would run them.
+int32_t pthb200_test_schedule(const int32_t* query_start_loc, const int32_t* seq_lens, int32_t num_reqs,
+                              int32_t group, int32_t num_kv_heads, int32_t bq, int32_t num_splits, int32_t window,
+                              int32_t causal, int32_t row_class, int32_t class_rows, int32_t num_ctas, int32_t* out,
+                              int32_t max_items) {
+  using namespace pthb200;
+  g_last_error.clear();
+  PTHB_REQUIRE(query_start_loc != nullptr && seq_lens != nullptr && out != nullptr, "NULL argument");
+  PTHB_REQUIRE(num_reqs >= 1 && group >= 1 && num_kv_heads >= 1 && bq >= 1 && num_splits >= 1 && num_ctas >= 1 &&
+                   max_items >= 0,
+               "counts must be >= 1");
+  SchedShape sh{group, num_kv_heads, bq, num_splits, window, causal, row_class, class_rows};
+  unsigned long long total = 0;
+  for (int r = 0; r < num_reqs; ++r) {
+    const int q_len = query_start_loc[r + 1] - query_start_loc[r];
+    total += (unsigned long long)req_row_tiles(sh, q_len) * (unsigned long long)req_kv_tiles(sh, q_len, seq_lens[r]);
+  }
+  const int t_star = item_tiles(total * (unsigned long long)num_kv_heads, num_ctas);
+  int32_t count = 0;
+  for (int cta = 0; cta < num_ctas; ++cta) {
+    int r = 0;
+    long long first = 0;  // item index of request r's first item
+    for (long long idx = cta;; idx += num_ctas) {
+      int q_len = 0, splits = 1;
+      long long n = 0;
+      for (; r < num_reqs; ++r) {
+        q_len = query_start_loc[r + 1] - query_start_loc[r];
+        splits = req_splits(req_kv_tiles(sh, q_len, seq_lens[r]), t_star, num_splits);
+        n = req_items(req_row_tiles(sh, q_len), splits, num_kv_heads);
+        if (idx < first + n) break;
+        first += n;
+      }
+      if (r >= num_reqs) break;
+      const ItemCoord c = item_coord((int)(idx - first), num_kv_heads, splits);
+      const int first_idx = c.row_tile * bq;
+      const int ntok = sched_min(bq, q_len - first_idx);
+      int lo0, hi0, lo1, hi1, tb, te;
+      visible_bounds(window, causal, seq_lens[r], q_len, first_idx, &lo0, &hi0);
+      visible_bounds(window, causal, seq_lens[r], q_len, first_idx + ntok - 1, &lo1, &hi1);
+      split_tile_span(lo0, sched_max(hi0, hi1) + 1, c.split, splits, &tb, &te);
+      if (count < max_items) {
+        int32_t* o = out + (int64_t)count * 8;
+        o[0] = cta;
+        o[1] = r;
+        o[2] = c.row_tile;
+        o[3] = c.kvh;
+        o[4] = c.split;
+        o[5] = splits;
+        o[6] = tb;
+        o[7] = te;
+      }
+      ++count;
+    }
+  }
+  return count;
 }
 
 }  // extern "C"
@@ -373,9 +437,11 @@ constexpr int kMaxDevices = 64;
 std::mutex g_builtin_ws_mutex;
 unsigned char* g_builtin_ws_ptr[kMaxDevices] = {};
 
-// Device address of the array on the CURRENT device.  Looked up once per device (the
-// lookup may load the module on that device, which is why a first call belongs before
-// any stream capture); later calls only read the cached pointer.
+// Device address of the array on the CURRENT device (cudaGetDevice), not on the device
+// that owns `stream`: the caller makes the stream's device current before the call, as for
+// every launch.  Looked up once per device (the lookup may load the module on that device,
+// which is why a first call belongs before any stream capture); later calls only read the
+// cached pointer.
 int32_t builtin_ws(unsigned char** out) {
   int dev = -1;
   cudaError_t err = cudaGetDevice(&dev);
@@ -405,18 +471,23 @@ extern "C" int32_t pthb200_attention_noalloc(const PthAttnArgs* args, void* stre
   PTHB_REQUIRE(args->abi_version == PTH_ATTN_ABI_VERSION, "args.abi_version does not match the library");
   PTHB_REQUIRE(args->struct_bytes == (int32_t)sizeof(PthAttnArgs), "args.struct_bytes != sizeof(PthAttnArgs)");
   if (args->num_splits <= 1) return attention_impl(args, nullptr, stream, true);  // no partials at all
+  PTHB_REQUIRE(args->num_splits <= 65535, "num_splits must be in [1, 65535]");
   PTHB_REQUIRE(args->num_tokens >= 1 && args->num_q_heads >= 1 && is_head_size(args->head_size),
                "num_tokens and num_q_heads must be >= 1 and head_size 64, 128 or 256");
-  // dense partials: o [S][T][Hq][D] fp32, then lse [S][T][Hq] fp32 at the next 256-byte boundary
-  const int64_t rows = (int64_t)args->num_splits * args->num_tokens * args->num_q_heads;
-  const int64_t o_bytes = (rows * args->head_size * 4 + 255) / 256 * 256;
-  const int64_t need = o_bytes + rows * 4;
-  if (need > (int64_t)PTHB200_BUILTIN_WS_BYTES) {
+  // dense partials: o [S][T][Hq][D] fp32, then lse [S][T][Hq] fp32 at the next 256-byte boundary.
+  // The products are taken step by step so that no intermediate can overflow: S * T < 2^47,
+  // and a row count beyond the array's capacity in floats ends the sum early.
+  const int64_t cap = (int64_t)PTHB200_BUILTIN_WS_BYTES;
+  int64_t rows = (int64_t)args->num_splits * args->num_tokens;
+  if (rows <= cap) rows *= args->num_q_heads;
+  const int64_t o_bytes = rows <= cap ? (rows * args->head_size * 4 + 255) / 256 * 256 : 0;
+  const int64_t need = rows <= cap ? o_bytes + rows * 4 : INT64_MAX;
+  if (need > cap) {
     return fail(PTH_ATTN_EINVAL,
-                "pthb200_attention_noalloc: the split partials of this call need " + std::to_string(need) +
+                "pthb200_attention_noalloc: the split partials of this call need " +
+                    (need == INT64_MAX ? std::string("more than 2^63") : std::to_string(need)) +
                     " bytes (num_splits * num_tokens * num_q_heads * (head_size + 1) * 4), the built-in array holds " +
-                    std::to_string((int64_t)PTHB200_BUILTIN_WS_BYTES) +
-                    "; use fewer splits, or pthb200_attention with a workspace of your own");
+                    std::to_string(cap) + "; use fewer splits, or pthb200_attention with a workspace of your own");
   }
   unsigned char* ws = nullptr;
   if (int32_t rc = builtin_ws(&ws)) return rc;
@@ -429,7 +500,6 @@ extern "C" int32_t pthb200_attention_noalloc(const PthAttnArgs* args, void* stre
   a.ws_lse_stride_head = 4;
   a.ws_lse_stride_token = (int64_t)4 * a.num_q_heads;
   a.ws_lse_stride_split = a.ws_lse_stride_token * a.num_tokens;
-  if (int32_t rc = attention_impl(&a, nullptr, stream, true)) return rc;
   PthAttnCombineArgs c{};
   c.abi_version = PTH_ATTN_ABI_VERSION;
   c.struct_bytes = (int32_t)sizeof(PthAttnCombineArgs);
@@ -451,5 +521,9 @@ extern "C" int32_t pthb200_attention_noalloc(const PthAttnArgs* args, void* stre
   c.num_q_heads = a.num_q_heads;
   c.head_size = a.head_size;
   c.num_splits = a.num_splits;
+  // every check of both launches first: a refusal must not leave half the work enqueued
+  if (int32_t rc = attention_impl(&a, nullptr, nullptr, false)) return rc;
+  if (int32_t rc = combine_impl(&c, nullptr, nullptr, false)) return rc;
+  if (int32_t rc = attention_impl(&a, nullptr, stream, true)) return rc;
   return combine_impl(&c, nullptr, stream);
 }

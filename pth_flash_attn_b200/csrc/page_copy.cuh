@@ -10,6 +10,8 @@
 
 #include <cuda.h>
 
+#include <mutex>
+
 #include "params.cuh"
 #include "tcgen05.cuh"
 
@@ -111,11 +113,62 @@ bool make_page_map(const KernelParams& p, int num_blocks, CUtensorMap* map) {
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The page map of a cache, built once and kept: encoding a map is a driver call of several
+// microseconds, which a decode launch of some tens of microseconds pays on every call
+// otherwise.  A map depends only on the cache view (address, strides, page size, block
+// count), and a serving engine calls with the same few views for its whole life.  Returns
+// nullptr if the driver refuses the geometry; the pointer stays valid (entries are only
+// ever added; once the table is full, further views are encoded per call into a
+// thread-local map).
+const CUtensorMap* cached_page_map(const KernelParams& p) {
+  struct Entry {
+    uintptr_t base;
+    int64_t stride_slot, stride_block;
+    int32_t block_size, num_blocks;
+    CUtensorMap map;
+  };
+  constexpr int kEntries = 64;
+  static Entry entries[kEntries];
+  static int used = 0;
+  static std::mutex mu;
+  const uintptr_t base = reinterpret_cast<uintptr_t>(p.k.data) & ~(uintptr_t)15;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    for (int i = 0; i < used; ++i) {
+      const Entry& e = entries[i];
+      if (e.base == base && e.stride_slot == p.k.stride_slot && e.stride_block == p.k.stride_block &&
+          e.block_size == p.block_size && e.num_blocks == p.num_blocks) {
+        return &e.map;
+      }
+    }
+    if (used < kEntries) {
+      Entry& e = entries[used];
+      if (!make_page_map(p, p.num_blocks, &e.map)) return nullptr;
+      e.base = base;
+      e.stride_slot = p.k.stride_slot;
+      e.stride_block = p.k.stride_block;
+      e.block_size = p.block_size;
+      e.num_blocks = p.num_blocks;
+      ++used;
+      return &e.map;
+    }
+  }
+  thread_local CUtensorMap scratch;
+  return make_page_map(p, p.num_blocks, &scratch) ? &scratch : nullptr;
+}
+
 // 1 = tiled TMA per page, 2 = bulk copy per contiguous page run, 0 = neither applies.
 int raw_mode_for(const KernelParams& p) {
   if (p.block_shift < 4 || p.block_shift > 7) return 0;  // 16 .. 128 keys per page, a power of two
   if (p.k.stride_block % 16 != 0) return 0;
-  if (p.k.stride_slot == 2 * p.head_size + 8) return 2;
+  if (p.k.stride_slot == 2 * p.head_size + 8) {
+    // A bulk copy starts and ends on 16-byte boundaries: the page run of every head must
+    // itself be 16-byte aligned, so that the copy never reads a byte outside the run.
+    const bool aligned_runs = reinterpret_cast<uintptr_t>(p.k.data) % 16 == 0 &&
+                              (p.num_kv_heads == 1 || p.k.stride_head % 16 == 0) &&
+                              ((int64_t)p.block_size * p.k.stride_slot) % 16 == 0;
+    return aligned_runs ? 2 : 0;
+  }
   if (p.k.stride_slot % 16 == 0 && p.k.stride_slot >= kRawRow) return 1;
   return 0;
 }

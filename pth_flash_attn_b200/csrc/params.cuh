@@ -197,6 +197,8 @@ cudaError_t launch_scalar_attention(const KernelParams& p, cudaStream_t stream);
 cudaError_t launch_umma_attention(const KernelParams& p, cudaStream_t stream);
 cudaError_t launch_umma_i8_attention(const KernelParams& p, cudaStream_t stream);
 cudaError_t launch_umma_rows_attention(const KernelParams& p, cudaStream_t stream);
+// CTAs the persistent integer kernel is launched with on a device of `sms` SMs (-1: too many items).
+int umma_i8_num_ctas(const KernelParams& p, int sms);
 cudaError_t read_i8_status(unsigned int* v);
 cudaError_t read_rows_status(unsigned int* v);
 cudaError_t launch_combine_kernel(const CombineParams& p, cudaStream_t stream);

@@ -1,4 +1,4 @@
-// Integer tcgen05 attention kernel, head size 128, token-major orientation.
+// Integer tcgen05 attention kernel, head size 128, token-major orientation, persistent CTAs.
 //
 // The cache holds int8 K and V, so both contractions run on the int8 tensor path
 // (tcgen05.mma.kind::i8, int32 accumulators in TMEM) with the cache bytes used AS
@@ -16,115 +16,116 @@
 // (relative 2^-16 of the row maximum) and the 7 PD-bit quantisation of
 // p * v_scale (relative 2^-(7 PD + 1) of the tile maximum).
 //
-// One CTA per SM = one work item (row tile x KV head x split).  Its warps have six
-// roles that meet only through mbarriers (tile = 128 consecutive keys):
+// One CTA per SM runs work items (row tile x KV head x split) one after the other
+// (sched.cuh says which).  Its warps have seven roles that meet only through mbarriers
+// (tile = 128 consecutive keys); the rings of the data path are indexed by a tile count
+// that runs on across items, so the copies of the next item's first tiles are in flight
+// while the last tiles of the current item are still being computed:
+//   scheduler  (1 warp)  walks the requests, finds this CTA's next item, writes -inf
+//              markers for splits a request does not use and the result of an item
+//              without keys, and for every other item publishes a descriptor together
+//              with the item's Q digit image, row scales and row masks (two slots, so the
+//              next item is staged while the current one runs);
 //   loader     (1 warp)  lane `page` issues one TMA copy per KV page of a tile - a
 //              [block_size slots] x [272 bytes] box of a tiled tensor map, or a bulk
 //              copy when a page's cells are contiguous - into a ring of NR raw stages;
 //              block ids are fetched one tile ahead;
-//   producers  (NP groups of 4 warps; group k takes the tiles j with j % NP == k)
+//   producers  (NP groups of 4 warps; group k takes the tiles g with g % NP == k)
 //              thread t reads the 272 raw bytes around key t's cell into registers,
 //              releases the raw stage, and writes them 16 bytes at a time into the
 //              canonical (no-swizzle) operand images: K into a ring of NK K images,
 //              V and the two scale vectors into a ring of NS V stages.  A cell is only
 //              8-byte aligned and V starts 132 bytes into it, which is why the bytes
 //              pass through registers once;
-//   QK issuer  (1 thread) S^T of tile i into one of SB buffers per softmax group, as far
-//              ahead of the softmax as the images and buffers allow; its commit also
-//              frees the K image;
-//   PV issuer  (1 thread) O^T of tile i once its P image is complete; its commit also
-//              frees the V stage;
-//   softmax    (2 groups of 4 warps; group g owns the tiles with i % 2 == g and its own
-//              running maximum, sum and accumulator) thread t owns key t of S^T
-//              (scores -> tile maximum -> probabilities -> digits of P) and output
+//   MMA issuer (1 thread) per item, in a fixed order: QK(0), QK(1), then QK(i + 2), PV(i);
+//              S^T of a tile lands in one of SB buffers of the tile's softmax group, O^T in
+//              the group's O^T buffer; its commits signal the softmax and free the images;
+//   softmax    (2 groups of 4 warps; group g owns the tiles whose running count is g mod 2,
+//              with its own running maximum, sum and accumulator) thread t owns key t of
+//              S^T (scores -> tile maximum -> probabilities -> digits of P) and output
 //              column d = t of O^T, which it folds tile by tile into an fp32 register
 //              accumulator (acc = acc * alpha + O^T * u), so TMEM never holds a value
 //              that needs rescaling.  Per-row factors live in lanes and travel by
-//              shuffle.  The two groups' states are merged in the epilogue.
+//              shuffle.  The two groups' states are merged at the end of every item.
 // Every mbarrier wait is bounded: a wait that gives up raises a CTA-wide abort
 // flag (all later waits return at once), sets bit 2 of the status word, and the
 // CTA still finishes and frees its TMEM.
 #include <cuda.h>
 
 #include "params.cuh"
+#include "sched.cuh"
 #include "umma_i8.cuh"
 #include "page_copy.cuh"
 
 namespace pthb200 {
 
 __device__ unsigned int g_i8_status = 0;
-#ifdef PTHB200_WAIT_STATS
-// Debug build only: cycles that one thread of each role of CTA (0,0,0) spent in each wait.
-__device__ long long g_wait_stats[4][12];
-__device__ long long g_timeline[16][16];
-#define TL(tile, ev) if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tile) >= 24 && (tile) < 40) g_timeline[(tile) - 24][ev] = clock64() - k_entry_;
-#define STAT_DECL long long st_[12] = {0}; const long long st_begin_ = clock64();
-#define STAT_WAIT(slot, expr) { const long long t0_ = clock64(); expr; st_[slot] += clock64() - t0_; }
-#define STAT_ADD(slot, v) st_[slot] += (v);
-#define STAT_T(name) const long long name = clock64();
-#define STAT_ENTRY const long long k_entry_ = clock64(); unsigned long long k_ns_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(k_ns_));
-#define STAT_MARK(slot) if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) g_wait_stats[3][slot] = clock64() - k_entry_;
-#define STAT_EXIT if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { unsigned long long e_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(e_)); g_wait_stats[3][10] = (long long)(e_ - k_ns_); }
-#define STAT_FLUSH(role) if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { st_[11] = clock64() - st_begin_; for (int q_ = 0; q_ < 12; ++q_) g_wait_stats[role][q_] = st_[q_]; }
-#else
-#define TL(tile, ev)
-#define STAT_DECL
-#define STAT_WAIT(slot, expr) { expr; }
-#define STAT_ADD(slot, v)
-#define STAT_T(name)
-#define STAT_FLUSH(role)
-#define STAT_ENTRY
-#define STAT_MARK(slot)
-#define STAT_EXIT
-#endif
 
 namespace {
 
 constexpr int kGroupThreads = 128;                      // one softmax warpgroup
 constexpr int kSoftmaxThreads = 2 * kGroupThreads;      // warps 0-3 and 4-7
 constexpr int kProducerThreads = 128;                   // one producer group: one thread per key of a tile
-// Warps after the softmax groups: NP producer groups of four warps (group k realigns the
-// tiles j with j % NP == k), then the MMA issuer and the loader warp.
-__host__ __device__ constexpr int threads_for(int np) { return kSoftmaxThreads + np * kProducerThreads + 64; }
+constexpr int kItemSlots = 2;                           // item descriptors (and Q images) in flight
+// Warps after the softmax groups: NP producer groups of four warps, then the MMA issuer,
+// the loader and the scheduler.
+__host__ __device__ constexpr int threads_for(int np) { return kSoftmaxThreads + np * kProducerThreads + 96; }
 constexpr int kStageScales = 2 * kKeys * 4;                 // k_scale[128], v_scale[128]
 constexpr int kVStageBytes = kImgBytes + kStageScales;      // V image and both scale vectors of one tile
+
+// What the scheduler publishes for one item (shared memory, one per slot).
+struct ItemDesc {
+  int32_t n_tiles;      // KV tiles of the item; 0 = no more items
+  int32_t req, kvh, split;
+  int32_t tok0, ntok;   // first query token (row of q / out) and query tokens of the row tile
+  int32_t tile_begin;   // first KV tile
+  int32_t range_begin, range_end;  // keys the rows of the tile see together
+  int32_t mask_lo, mask_hi;        // keys EVERY live row sees: tiles inside need no mask
+  int32_t pad;
+};
 
 template <int NPAD, int PD, int NS, int NK, int NR, int SB>
 struct Layout {
   static constexpr int kstages = 0;                                 // [NK] K images
   static constexpr int vstages = kstages + NK * kImgBytes;          // [NS] V image + scales
-  static constexpr int qimg = vstages + NS * kVStageBytes;          // [8][2 NPAD][16]
-  static constexpr int pimg = qimg + 8 * 2 * NPAD * 16;             // [2 groups][PD NPAD / 16][128][16]
-  static constexpr int raw = pimg + 2 * PD * NPAD * kKeys;          // [NR][128][272] raw cells
-  static constexpr int wred = raw + NR * kRawStageBytes;                            // float [2 groups][2][4][NPAD + 1]
+  static constexpr int qimg = vstages + NS * kVStageBytes;          // [slots][8][2 NPAD][16]
+  static constexpr int qimg_bytes = 8 * 2 * NPAD * 16;
+  static constexpr int pimg = qimg + kItemSlots * qimg_bytes;       // [2 groups][PD NPAD / 16][128][16]
+  static constexpr int pimg_bytes = 2 * PD * NPAD * kKeys;
+  static constexpr int raw = pimg + pimg_bytes;                     // [NR][128][272] raw cells
+  static constexpr int wred = raw + NR * kRawStageBytes;            // float [2 groups][2][4][NPAD + 1]
   static constexpr int mrun = wred + 2 * 2 * 4 * (NPAD + 1) * 4;    // float [2 groups][2 NPAD], first NPAD used
-  static constexpr int sq = mrun + 2 * 2 * NPAD * 4;                // float [NPAD]
-  static constexpr int rlo = sq + NPAD * 4;                         // int [NPAD]
-  static constexpr int rhi = rlo + NPAD * 4;                        // int [NPAD]
-  static constexpr int bars = (rhi + NPAD * 4 + 7) / 8 * 8;         // uint64 [2 NS + 10 + NR]
-  static constexpr int misc = bars + (2 * NS + NK + 14 + 2 * NR) * 8;    // abort flag, TMEM slot
-  static constexpr int total = misc + 16;
+  static constexpr int sq = mrun + 2 * 2 * NPAD * 4;                // float [slots][NPAD]
+  static constexpr int rlo = sq + kItemSlots * NPAD * 4;            // int [slots][NPAD]
+  static constexpr int rhi = rlo + kItemSlots * NPAD * 4;           // int [slots][NPAD]
+  static constexpr int desc = (rhi + kItemSlots * NPAD * 4 + 15) / 16 * 16;  // ItemDesc [slots]
+  static constexpr int bars = desc + kItemSlots * (int)sizeof(ItemDesc);
+  static constexpr int n_bars = 2 * NS + 14 + 2 * NR + 2 * kItemSlots;
+  static constexpr int misc = bars + n_bars * 8;                    // abort flag, TMEM slot, total work
+  static constexpr int total = misc + 32;
   static constexpr int s_cols = 2 * NPAD;
   static constexpr int o_cols = PD * NPAD;
   static constexpr int s_total = 2 * SB * s_cols;                   // [2 groups][SB] S^T buffers
   static constexpr int tmem_need = s_total + 2 * o_cols;
   static constexpr int tmem_alloc = tmem_need <= 32 ? 32 : tmem_need <= 64 ? 64 : tmem_need <= 128 ? 128
                                     : tmem_need <= 256 ? 256 : 512;
+  static_assert(sizeof(ItemDesc) % 16 == 0, "descriptor slots stay 16-byte aligned");
 };
 
 // Barrier indices inside the barrier array.
-template <int NS, int NK, int NR>
+template <int NS, int NR>
 struct Bars {
   static constexpr int full = 0;             // [NS] producers -> MMA, 128 arrivals
   static constexpr int empty = NS;           // [NS] PV issuer (tcgen05.commit) -> producers: V stage free
-  static constexpr int s_ready = 2 * NS;      // [2 groups][2] MMA -> softmax
+  static constexpr int s_ready = 2 * NS;      // [2 groups][2] MMA -> softmax (and producers: K image free)
   static constexpr int s_free = 2 * NS + 4;   // [2 groups][2] softmax -> MMA, 128 arrivals
   static constexpr int o_ready = 2 * NS + 8;  // [2] MMA -> softmax
   static constexpr int o_free = 2 * NS + 10;  // [2] softmax -> MMA, 128 arrivals
   static constexpr int p_ready = 2 * NS + 12; // [2] softmax -> MMA, 128 arrivals
   static constexpr int raw_full = 2 * NS + 14;// [NR] page copies -> producers
   static constexpr int raw_free = 2 * NS + 14 + NR;  // [NR] producers -> loader, 128 arrivals
-  static constexpr int kempty = 2 * NS + 14 + 2 * NR; // [NK] unused (the producers wait on s_ready)
+  static constexpr int item_full = 2 * NS + 14 + 2 * NR;               // [slots] scheduler -> every other role
+  static constexpr int item_empty = 2 * NS + 14 + 2 * NR + kItemSlots; // [slots] every other role -> scheduler
 };
 
 // Key of a tile held by row `r` of its operand images (see the producers).
@@ -132,89 +133,58 @@ __device__ __forceinline__ int tile_key(const KernelParams& p, int r) {
   return p.raw_mode == 2 ? 2 * (r & 63) + (r >> 6) : r;
 }
 
+// Barrier over `count` threads that also ORs a predicate over them (uniform result).
+__device__ __forceinline__ bool named_barrier_or(int id, int count, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %3, 0;\n\t"
+      "bar.red.or.pred q, %1, %2, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t"
+      "}\n"
+      : "=r"(r)
+      : "r"(id), "r"(count), "r"((uint32_t)pred)
+      : "memory");
+  return r != 0;
+}
+
 template <int NPAD, int PD, int NS, int NK, int NR, int SB, int RQ, int NP>
 __global__ void __launch_bounds__(threads_for(NP), 1)
 umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_constant__ CUtensorMap tmap) {
   using L = Layout<NPAD, PD, NS, NK, NR, SB>;
-  using B = Bars<NS, NK, NR>;
+  using B = Bars<NS, NR>;
   constexpr int kRawStages = NR;
   constexpr int XMAX = (1 << (7 * PD)) - 1;
   constexpr int kThreads = threads_for(NP);
   constexpr int kMmaWarp = 8 + 4 * NP;     // lane 0 issues every MMA
   constexpr int kLoadWarp = kMmaWarp + 1;  // issues the page copies
+  constexpr int kSchedWarp = kMmaWarp + 2; // finds and stages the items
+  // arrivals that free an item slot: every softmax and producer thread, the issuer, the loader
+  constexpr int kItemReaders = kSoftmaxThreads + NP * kProducerThreads + 2;
   static_assert(RQ >= 1 && 4 * RQ <= NPAD, "RQ = groups of four rows the softmax handles (rows <= 4 RQ)");
   static_assert(NS >= 2, "two image stages: one feeding the MMAs, one being filled");
-  STAT_ENTRY
+  static_assert(PD * NPAD >= 8 * RQ, "the P images hold the parked accumulator of one softmax group");
   extern __shared__ __align__(128) uint8_t smem[];
-  uint8_t* qimg = smem + L::qimg;
   uint8_t* pimg = smem + L::pimg;
   float* wred = reinterpret_cast<float*>(smem + L::wred);
   float* mrun = reinterpret_cast<float*>(smem + L::mrun);
-  float* sq = reinterpret_cast<float*>(smem + L::sq);
-  int* rlo = reinterpret_cast<int*>(smem + L::rlo);
-  int* rhi = reinterpret_cast<int*>(smem + L::rhi);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::bars);
+  volatile ItemDesc* descs = reinterpret_cast<volatile ItemDesc*>(smem + L::desc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::misc);
   uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + L::misc + 8);
+  unsigned long long* total_s = reinterpret_cast<unsigned long long*>(smem + L::misc + 16);
 
-  const int kvh = blockIdx.y, split = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // Row tile of this CTA.  The bisection over query_start_loc is a chain of dependent
-  // loads: when the arrays fit, the CTA first copies them (and seq_lens) into still unused
-  // shared memory with one round of coalesced loads and bisects there.
-  constexpr int kQslCache = 4096;
-  RowTile t;
-  if (p.tile_map == 0 && p.num_reqs + 1 <= kQslCache) {
-    int* qsl_s = reinterpret_cast<int*>(smem + L::raw);
-    int* len_s = qsl_s + kQslCache;
-    for (int i = tid; i <= p.num_reqs; i += kThreads) {
-      qsl_s[i] = __ldg(p.query_start_loc + i);
-      if (i < p.num_reqs) len_s[i] = __ldg(p.seq_lens + i);
-    }
-    __syncthreads();
-    t = resolve_row_tile_with(p, blockIdx.x, [&](int i) { return qsl_s[i]; }, [&](int r) { return len_s[r]; });
-    __syncthreads();  // the copy is dead: the raw ring may be filled
-  } else {
-    t = resolve_row_tile(p, blockIdx.x);
-  }
-  if (t.req < 0) return;
-  const int rows = t.ntok * p.group;  // <= NPAD by construction of bq
-  int tile_begin, tile_end, range_begin, range_end;
-  split_tiles(p, t, split, &tile_begin, &tile_end, &range_begin, &range_end);
-
-  if (tile_begin >= tile_end) {
-    // No keys for this work item: zero output, log-sum-exp -inf.
-    if (tid < kHeadDimI8) {
-      for (int n = 0; n < rows; ++n) {
-        int token, head;
-        row_target(p, t, kvh, n, &token, &head);
-        if (p.num_splits == 1) {
-          store_out_elem(p.out + (int64_t)token * p.out_stride_token + (int64_t)head * p.out_stride_head, tid,
-                         p.out_dtype, 0.f);
-        } else {
-          reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.ws_o) + (int64_t)split * p.ws_o_stride_split +
-                                   (int64_t)token * p.ws_o_stride_token + (int64_t)head * p.ws_o_stride_head)[tid] = 0.f;
-        }
-      }
-    }
-    if (tid < rows) {
-      int token, head;
-      row_target(p, t, kvh, tid, &token, &head);
-      if (p.num_splits > 1) {
-        *reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.ws_lse) + (int64_t)split * p.ws_lse_stride_split +
-                                  (int64_t)token * p.ws_lse_stride_token + (int64_t)head * p.ws_lse_stride_head) =
-            -INFINITY;
-      } else if (p.lse_out != nullptr) {
-        *reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.lse_out) + (int64_t)token * p.lse_stride_token +
-                                  (int64_t)head * p.lse_stride_head) = -INFINITY;
-      }
-    }
-    return;
-  }
-
-  STAT_MARK(0)
-  const int n_tiles = tile_end - tile_begin;
-  const uint32_t kstage0 = tc::smem_u32(smem + L::kstages), vstage0 = tc::smem_u32(smem + L::vstages);
+  SchedShape shape;
+  shape.group = p.group;
+  shape.num_kv_heads = p.num_kv_heads;
+  shape.bq = p.bq;
+  shape.num_splits = p.num_splits;
+  shape.window = p.window;
+  shape.causal = p.causal;
+  shape.row_class = p.row_class;
+  shape.class_rows = p.class_rows;
 
   // ---- set-up by all threads -------------------------------------------------
   if (tid == 0) {
@@ -222,7 +192,6 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       tc::mbar_init(&bars[B::full + s], kProducerThreads);
       tc::mbar_init(&bars[B::empty + s], 1);
     }
-    for (int s = 0; s < NK; ++s) tc::mbar_init(&bars[B::kempty + s], 1);
     for (int b = 0; b < 2; ++b) {
       for (int k = 0; k < 2; ++k) {
         tc::mbar_init(&bars[B::s_ready + 2 * b + k], 1);
@@ -236,34 +205,301 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       tc::mbar_init(&bars[B::raw_full + s], kKeys >> p.block_shift);
       tc::mbar_init(&bars[B::raw_free + s], kProducerThreads);
     }
+    for (int s = 0; s < kItemSlots; ++s) {
+      tc::mbar_init(&bars[B::item_full + s], 32);
+      tc::mbar_init(&bars[B::item_empty + s], kItemReaders);
+    }
     *abort_flag = 0;
+    *total_s = 0ull;
     tc::mbar_init_fence();
   }
   if (warp == 0) {
     tc::tmem_alloc(tslot, L::tmem_alloc);
     tc::tmem_relinquish();
   }
+  __syncthreads();
+  {
+    // total work of the launch in KV tiles (every CTA computes the same number)
+    unsigned long long w = 0;
+    for (int r = tid; r < p.num_reqs; r += kThreads) {
+      const int q0 = __ldg(p.query_start_loc + r), q1 = __ldg(p.query_start_loc + r + 1);
+      const int len = __ldg(p.seq_lens + r);
+      w += (unsigned long long)req_row_tiles(shape, q1 - q0) * (unsigned long long)req_kv_tiles(shape, q1 - q0, len);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) w += __shfl_xor_sync(0xffffffffu, w, o);
+    if (lane == 0 && w != 0) atomicAdd(total_s, w);
+  }
   tc::fence_before_sync();
   tc::fence_async_smem();
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem_base = *tslot;
+  const int t_star = item_tiles(*total_s * (unsigned long long)p.num_kv_heads, (int)gridDim.x);
+  const uint32_t kstage0 = tc::smem_u32(smem + L::kstages), vstage0 = tc::smem_u32(smem + L::vstages);
   bool ok = true;
-  STAT_MARK(1)
 
-  if (warp >= 8 && warp < kMmaWarp) {
+  if (warp == kSchedWarp) {
+    // =========================== scheduler ====================================
+    // Walks the requests in blocks of 32 (lane l holds request base + l and the items of the
+    // requests before it), so this CTA's items c, c + CTAs, ... are found in one pass.
+    const int S = p.num_splits, hkv = p.num_kv_heads;
+    int base = 0;
+    long long blk_first = 0;
+    int blk_total = 0;
+    int my_q0 = 0, my_qlen = 0, my_len = 0, my_splits = 1, my_n = 0, my_excl = 0;
+    auto load_block = [&](int b) {
+      const int r = b + lane;
+      my_n = 0;
+      my_q0 = my_qlen = my_len = 0;
+      my_splits = 1;
+      if (r < p.num_reqs) {
+        my_q0 = __ldg(p.query_start_loc + r);
+        my_qlen = __ldg(p.query_start_loc + r + 1) - my_q0;
+        my_len = __ldg(p.seq_lens + r);
+        const int rt = req_row_tiles(shape, my_qlen);
+        my_splits = req_splits(req_kv_tiles(shape, my_qlen, my_len), t_star, S);
+        my_n = (int)req_items(rt, my_splits, hkv);
+      }
+      int v = my_n;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += u;
+      }
+      my_excl = v - my_n;
+      blk_total = __shfl_sync(0xffffffffu, v, 31);
+    };
+    load_block(0);
+    int pub = 0;  // items published so far
+    for (long long idx = blockIdx.x;; idx += gridDim.x) {
+      bool done = false;
+      while (idx >= blk_first + blk_total) {
+        blk_first += blk_total;
+        base += 32;
+        if (base >= p.num_reqs) {
+          done = true;
+          break;
+        }
+        load_block(base);
+      }
+      if (done) break;
+      const int rel = (int)(idx - blk_first);
+      const bool mine = rel >= my_excl && rel < my_excl + my_n;
+      const int src = __ffs(__ballot_sync(0xffffffffu, mine)) - 1;
+      const int req = base + src;
+      const int q0 = __shfl_sync(0xffffffffu, my_q0, src), q_len = __shfl_sync(0xffffffffu, my_qlen, src);
+      const int seq_len = __shfl_sync(0xffffffffu, my_len, src), splits = __shfl_sync(0xffffffffu, my_splits, src);
+      const ItemCoord c = item_coord(rel - __shfl_sync(0xffffffffu, my_excl, src), hkv, splits);
+      const int first_idx = c.row_tile * p.bq;
+      const int ntok = min(p.bq, q_len - first_idx), tok0 = q0 + first_idx;
+      const int rows = ntok * p.group;
+      int lo_first, hi_first, lo_last, hi_last;
+      visible_bounds(p.window, p.causal, seq_len, q_len, first_idx, &lo_first, &hi_first);
+      visible_bounds(p.window, p.causal, seq_len, q_len, first_idx + ntok - 1, &lo_last, &hi_last);
+      const int range_begin = lo_first, range_end = max(hi_first, hi_last) + 1;  // lo and hi grow with the token
+      int tile_begin, tile_end;
+      split_tile_span(range_begin, range_end, c.split, splits, &tile_begin, &tile_end);
+      auto lse_slot = [&](int s, int n) -> float* {
+        const int token = tok0 + n / p.group, head = c.kvh * p.group + n % p.group;
+        return reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.ws_lse) + (int64_t)s * p.ws_lse_stride_split +
+                                        (int64_t)token * p.ws_lse_stride_token + (int64_t)head * p.ws_lse_stride_head);
+      };
+      if (c.split == 0 && S > splits) {
+        // splits this request does not use: no keys
+        for (int i = lane; i < rows * (S - splits); i += 32) *lse_slot(splits + i / rows, i % rows) = -INFINITY;
+      }
+      if (tile_begin >= tile_end) {
+        // No keys for this item: zero output, log-sum-exp -inf.
+        if (S == 1) {
+          for (int i = lane; i < rows * kHeadDimI8; i += 32) {
+            const int n = i >> 7, token = tok0 + n / p.group, head = c.kvh * p.group + n % p.group;
+            store_out_elem(p.out + (int64_t)token * p.out_stride_token + (int64_t)head * p.out_stride_head, i & 127,
+                           p.out_dtype, 0.f);
+          }
+        }
+        for (int n = lane; n < rows; n += 32) {
+          if (S > 1) {
+            *lse_slot(c.split, n) = -INFINITY;
+          } else if (p.lse_out != nullptr) {
+            const int token = tok0 + n / p.group, head = c.kvh * p.group + n % p.group;
+            *reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.lse_out) + (int64_t)token * p.lse_stride_token +
+                                      (int64_t)head * p.lse_stride_head) = -INFINITY;
+          }
+        }
+        continue;
+      }
+      const int slot = pub % kItemSlots;
+      if (pub >= kItemSlots) {
+        ok &= wait_or_abort(&bars[B::item_empty + slot], ((pub / kItemSlots) - 1) & 1, abort_flag);
+        if (!ok) break;
+      }
+      if (lane == 0) {
+        volatile ItemDesc* d = descs + slot;
+        d->n_tiles = tile_end - tile_begin;
+        d->req = req;
+        d->kvh = c.kvh;
+        d->split = c.split;
+        d->tok0 = tok0;
+        d->ntok = ntok;
+        d->tile_begin = tile_begin;
+        d->range_begin = range_begin;
+        d->range_end = range_end;
+        d->mask_lo = lo_last;
+        d->mask_hi = hi_first;
+      }
+      {
+        float* sq = reinterpret_cast<float*>(smem + L::sq) + slot * NPAD;
+        int* rlo = reinterpret_cast<int*>(smem + L::rlo) + slot * NPAD;
+        int* rhi = reinterpret_cast<int*>(smem + L::rhi) + slot * NPAD;
+        uint8_t* qimg = smem + L::qimg + slot * L::qimg_bytes;
+        for (int n = lane; n < NPAD; n += 32) {
+          int lo = 0, hi = -1;
+          if (n < rows) visible_bounds(p.window, p.causal, seq_len, q_len, first_idx + n / p.group, &lo, &hi);
+          rlo[n] = lo;
+          rhi[n] = hi;
+        }
+        // Q digits: 8 lanes per row, 16 elements each (4 rows per pass).
+        for (int nb = 0; nb < NPAD; nb += 4) {
+          const int n = nb + (lane >> 3), part = lane & 7;
+          float v[16];
+          if (n < rows) {
+            const int token = tok0 + n / p.group, head = c.kvh * p.group + n % p.group;
+            const uint4* srcq = reinterpret_cast<const uint4*>(p.q + (int64_t)token * p.q_stride_token +
+                                                               (int64_t)head * p.q_stride_head + part * 32);
+            const uint4 a = __ldg(srcq), b = __ldg(srcq + 1);
+            const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            if (p.q_dtype == PTH_ATTN_BF16) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                v[2 * e] = __uint_as_float(w[e] << 16);
+                v[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+                v[2 * e] = f.x;
+                v[2 * e + 1] = f.y;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) v[e] = 0.f;
+          }
+          float amax = 0.f;
+#pragma unroll
+          for (int e = 0; e < 16; ++e) amax = fmaxf(amax, fabsf(v[e]));
+          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+          const bool finite_row = amax > 0.f && amax < INFINITY;
+          const float inv = finite_row ? 32512.f / amax : 0.f;
+          uint32_t hi_w[4] = {0, 0, 0, 0}, lo_w[4] = {0, 0, 0, 0};
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            int qi = __float2int_rn(v[e] * inv);
+            qi = max(-32512, min(32512, qi));
+            const int qh = (qi + 128) >> 8;
+            const int ql = qi - (qh << 8);
+            hi_w[e >> 2] |= (uint32_t)(qh & 0xff) << (8 * (e & 3));
+            lo_w[e >> 2] |= (uint32_t)(ql & 0xff) << (8 * (e & 3));
+          }
+          // image row of (digit, n) is digit * NPAD + n; 16-byte column block `part`
+          *reinterpret_cast<uint4*>(qimg + part * (2 * NPAD * 16) + n * 16) = make_uint4(hi_w[0], hi_w[1], hi_w[2], hi_w[3]);
+          *reinterpret_cast<uint4*>(qimg + part * (2 * NPAD * 16) + (NPAD + n) * 16) =
+              make_uint4(lo_w[0], lo_w[1], lo_w[2], lo_w[3]);
+          if (part == 0) sq[n] = finite_row ? amax / 32512.f : 0.f;
+        }
+      }
+      tc::fence_async_smem();
+      mbar_arrive(&bars[B::item_full + slot]);
+      ++pub;
+    }
+    // no more items for this CTA
+    {
+      const int slot = pub % kItemSlots;
+      if (pub >= kItemSlots && ok) ok &= wait_or_abort(&bars[B::item_empty + slot], ((pub / kItemSlots) - 1) & 1, abort_flag);
+      if (lane == 0) descs[slot].n_tiles = 0;
+      __syncwarp();
+      mbar_arrive(&bars[B::item_full + slot]);
+    }
+  } else if (warp == kLoadWarp) {
+    // =========================== loader =======================================
+    // The raw bytes of a tile arrive PAGE BY PAGE through TMA: one copy per KV page and head,
+    // issued by lane `page` of this warp, completing on the raw stage's mbarrier.
+    //   raw_mode 1 (slot stride a multiple of 16, e.g. NHD with several heads): a tiled
+    //     tensor-map copy of a [block_size slots] x [272 bytes] box whose inner start is the
+    //     cell address rounded down to 16 bytes;
+    //   raw_mode 2 (cells of a page contiguous and 16-byte aligned: HND, or one KV head): a
+    //     plain bulk copy of the page run.
+    // TMA writes shared memory directly (no L1 staging) and a handful of 4 KB copies per tile
+    // keeps tens of KB in flight per SM.  The block id of the next tile's page is fetched
+    // before waiting for the raw stage, so the block-table latency is off the refill path.
+    const int pages_per_tile = kKeys >> p.block_shift;
+    const int bs = p.block_size;
+    const uint32_t raw_s = tc::smem_u32(smem + L::raw);
+    int g0 = 0;  // running tile count at the start of the item
+#pragma unroll 1
+    for (int item = 0;; ++item) {
+      const int slot = item % kItemSlots;
+      ok &= wait_or_abort(&bars[B::item_full + slot], (item / kItemSlots) & 1, abort_flag);
+      if (!ok) break;
+      const int n_tiles = descs[slot].n_tiles;
+      if (n_tiles == 0) break;
+      if (lane < pages_per_tile) {
+        const int tile_begin = descs[slot].tile_begin, range_begin = descs[slot].range_begin,
+                  range_end = descs[slot].range_end;
+        const int32_t* bt = p.block_table + (int64_t)descs[slot].req * p.block_table_row_stride;
+        const uint8_t* kb = p.k.data + (int64_t)descs[slot].kvh * p.k.stride_head;
+        const uint32_t delta = (uint32_t)(reinterpret_cast<uintptr_t>(kb) & 15);
+        // inner coordinate (4-byte elements) of this head's box: the tensor map starts at the
+        // 16-byte boundary below head 0's first cell
+        const int tma_x = (int)((reinterpret_cast<uintptr_t>(kb) - delta -
+                                 (reinterpret_cast<uintptr_t>(p.k.data) & ~(uintptr_t)15)) >> 2);
+        // block id of this lane's page of a tile, -1 if no key of the page is in range
+        auto page_block = [&](int tile) -> int {
+          const int pos0 = (tile_begin + tile) * kKeys + lane * bs;
+          if (tile >= n_tiles || pos0 >= range_end || pos0 + bs <= range_begin) return -1;
+          return __ldg(bt + (pos0 >> p.block_shift));
+        };
+        int blk = page_block(0);
+#pragma unroll 1
+        for (int j = 0; j < n_tiles; ++j) {
+          const int blk_next = page_block(j + 1);
+          const int g = g0 + j, rs = g % kRawStages;
+          if (g >= kRawStages) ok &= wait_or_abort(&bars[B::raw_free + rs], ((g / kRawStages) - 1) & 1, abort_flag);
+          uint64_t* bar = &bars[B::raw_full + rs];
+          if (blk >= 0 && ok) {
+            const uint32_t dst = raw_s + rs * kRawStageBytes + lane * bs * kRawRow;
+            if (p.raw_mode == 1) {
+              mbar_arrive_expect_tx(bar, bs * kRawRow);
+              tma_load_3d(dst, &tmap, tma_x, 0, blk, bar);
+            } else {
+              const uint32_t bytes = bs * (2 * kHeadDimI8 + 8);  // a multiple of 16, like the run's address
+              mbar_arrive_expect_tx(bar, bytes);
+              bulk_copy_g2s(dst, kb + (int64_t)blk * p.k.stride_block, bytes, bar);
+            }
+          } else {
+            mbar_arrive(bar);
+          }
+          blk = blk_next;
+        }
+      }
+      g0 += n_tiles;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[B::item_empty + slot]);
+    }
+  } else if (warp >= 8 && warp < kMmaWarp) {
     // =========================== producers ====================================
     const int pgrp = (warp - 8) >> 2;                              // producer group
-    const int pt = (tid - kSoftmaxThreads) & (kProducerThreads - 1);  // key of the tile this thread resolves
-    // The raw bytes of a tile are brought in by the loader warp (below), page by page; when a
-    // raw tile has landed, producer thread t moves the words of key t into the operand
+    const int pt = (tid - kSoftmaxThreads) & (kProducerThreads - 1);  // row of the operand images this thread fills
+    // The raw bytes of a tile are brought in by the loader warp (above), page by page; when a
+    // raw tile has landed, producer thread t moves the words of its key into the operand
     // images: with delta = (cell address mod 16) in {0, 8}, word w of K block j is raw word
     // delta / 4 + 4 j + w, of V block j raw word delta / 4 + 33 + 4 j + w; the scales are raw
     // words delta / 4 + 32 and + 65.
-    STAT_DECL
     const int bs = p.block_size;
-    const uint8_t* kb = p.k.data + (int64_t)kvh * p.k.stride_head;
-    const uint32_t delta = (uint32_t)(reinterpret_cast<uintptr_t>(kb) & 15);
     const int row_pitch = p.raw_mode == 1 ? kRawRow : 2 * kHeadDimI8 + 8;
     // Row pt of the operand images holds key `key` of the tile.  With a 264-byte pitch
     // (raw_mode 2) consecutive cells alternate between the two 8-byte alignments: taking the
@@ -272,282 +508,184 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     // the keys inside a tile has no effect on the integer sums; the softmax masks by `key`.
     const int key = tile_key(p, pt);
     const int my_page = key >> p.block_shift, my_slot = key & (bs - 1);
-    const uint32_t cell_off = my_page * bs * kRawRow + my_slot * row_pitch + delta;  // inside a raw stage
-    const bool odd = (cell_off & 8u) != 0;
+    int g0 = 0;
 #pragma unroll 1
-    for (int j = pgrp; j < n_tiles; j += NP) {
-      const int rs = j % kRawStages;
-      const int pos = (tile_begin + j) * kKeys + key;
-      const bool valid = pos >= range_begin && pos < range_end;
-      if constexpr (NP > 1) {
-        // A raw stage is shared by the producer groups in turn (NR is not a multiple of NP).
-        // A parity wait only tells apart two consecutive phases, so this group must not look
-        // at raw_full[rs] while the stage's PREVIOUS tile (another group's) is still pending:
-        // first wait until that tile has been taken out of the stage.
-        if (j >= kRawStages) ok &= wait_or_abort(&bars[B::raw_free + rs], ((j / kRawStages) - 1) & 1, abort_flag);
-      }
-      if (pt == 0) { TL(j, 0) }
-      STAT_WAIT(2, ok &= wait_or_abort(&bars[B::raw_full + rs], (j / kRawStages) & 1, abort_flag))
-      if (pt == 0) { TL(j, 1) }
-      STAT_T(tP0_)
-      uint32_t w[kRawRow / 4];
-      if (valid) {
-        const uint4* row = reinterpret_cast<const uint4*>(smem + L::raw + rs * kRawStageBytes + (cell_off & ~15u));
-#pragma unroll
-        for (int c = 0; c < kRawRow / 16; ++c) {
-          const uint4 v = row[c];
-          w[4 * c] = v.x;
-          w[4 * c + 1] = v.y;
-          w[4 * c + 2] = v.z;
-          w[4 * c + 3] = v.w;
-        }
-      } else {
-#pragma unroll
-        for (int c = 0; c < kRawRow / 4; ++c) w[c] = 0u;
-      }
-      STAT_ADD(3, clock64() - tP0_)
-      // this thread's row is in registers (the arrive orders the loads before it): once all
-      // 128 producers have arrived the loader may refill the raw stage
-      mbar_arrive(&bars[B::raw_free + rs]);
-      const int st = j % NS;
-      if (j >= NS) STAT_WAIT(0, ok &= wait_or_abort(&bars[B::empty + st], ((j / NS) - 1) & 1, abort_flag))
-      // K image j % NK is free once QK(j - NK) has completed, which is what S^T of that tile
-      // being ready means: the producers wait on the s_ready barrier the softmax group waits
-      // on (one commit less per tile for the issuing thread).  That barrier completes next
-      // for a tile whose images this group writes after this wait, so the parity is unambiguous.
-      if (j >= NK) {
-        const int q = j - NK, qk = q >> 1;
-        STAT_WAIT(1, ok &= wait_or_abort(&bars[B::s_ready + 2 * (q & 1) + qk % SB], (qk / SB) & 1, abort_flag))
-      }
-      if (pt == 0) { TL(j, 2) }
-      STAT_T(tP4_)
-      uint8_t* stage = smem + L::vstages + st * kVStageBytes;  // V image, then the scales
-      uint8_t* krow = smem + L::kstages + (j % NK) * kImgBytes + pt * 16;
-      uint8_t* vrow = stage + pt * 16;
-      if (!odd) {
-#pragma unroll
-        for (int b = 0; b < 8; ++b) {
-          *reinterpret_cast<uint4*>(krow + b * kImgChunk) = make_uint4(w[4 * b], w[4 * b + 1], w[4 * b + 2], w[4 * b + 3]);
-          *reinterpret_cast<uint4*>(vrow + b * kImgChunk) =
-              make_uint4(w[33 + 4 * b], w[34 + 4 * b], w[35 + 4 * b], w[36 + 4 * b]);
-        }
-        *reinterpret_cast<uint32_t*>(stage + kImgBytes + pt * 4) = w[32];
-        *reinterpret_cast<uint32_t*>(stage + kImgBytes + kKeys * 4 + pt * 4) = w[65];
-      } else {
-#pragma unroll
-        for (int b = 0; b < 8; ++b) {
-          *reinterpret_cast<uint4*>(krow + b * kImgChunk) =
-              make_uint4(w[2 + 4 * b], w[3 + 4 * b], w[4 + 4 * b], w[5 + 4 * b]);
-          *reinterpret_cast<uint4*>(vrow + b * kImgChunk) =
-              make_uint4(w[35 + 4 * b], w[36 + 4 * b], w[37 + 4 * b], w[38 + 4 * b]);
-        }
-        *reinterpret_cast<uint32_t*>(stage + kImgBytes + pt * 4) = w[34];
-        *reinterpret_cast<uint32_t*>(stage + kImgBytes + kKeys * 4 + pt * 4) = w[67];
-      }
-      STAT_ADD(7, clock64() - tP4_)
-      STAT_T(tP5_)
-      tc::fence_async_smem();
-      mbar_arrive(&bars[B::full + st]);
-      if (pt == 0) { TL(j, 3) }
-      STAT_ADD(8, clock64() - tP5_)
-    }
-    if (pt == 0 && pgrp == 0) { STAT_FLUSH(0) }
-  } else if (warp == kLoadWarp) {
-    // =========================== loader =======================================
-    // The raw bytes of a tile arrive PAGE BY PAGE through TMA: one copy per KV page and head,
-    // issued by lane `page` of this warp, completing on the raw stage's mbarrier.
-    //   raw_mode 1 (slot stride a multiple of 16, e.g. NHD with several heads): a tiled
-    //     tensor-map copy of a [block_size slots] x [272 bytes] box whose inner start is the
-    //     cell address rounded down to 16 bytes;
-    //   raw_mode 2 (cells of a page contiguous: HND, or one KV head): a plain bulk copy of the
-    //     run, again from the 16-byte boundary below it.
-    // TMA writes shared memory directly (no L1 staging) and a handful of 4 KB copies per tile
-    // keeps tens of KB in flight per SM.  The block id of the next tile's page is fetched
-    // before waiting for the raw stage, so the block-table latency is off the refill path.
-    const int pages_per_tile = kKeys >> p.block_shift;
-    if (lane < pages_per_tile) {
-      const int bs = p.block_size;
-      const int32_t* bt = p.block_table + (int64_t)t.req * p.block_table_row_stride;
-      const uint8_t* kb = p.k.data + (int64_t)kvh * p.k.stride_head;
+    for (int item = 0;; ++item) {
+      const int slot = item % kItemSlots;
+      ok &= wait_or_abort(&bars[B::item_full + slot], (item / kItemSlots) & 1, abort_flag);
+      if (!ok) break;
+      const int n_tiles = descs[slot].n_tiles;
+      if (n_tiles == 0) break;
+      const int tile_begin = descs[slot].tile_begin, range_begin = descs[slot].range_begin,
+                range_end = descs[slot].range_end;
+      const uint8_t* kb = p.k.data + (int64_t)descs[slot].kvh * p.k.stride_head;
       const uint32_t delta = (uint32_t)(reinterpret_cast<uintptr_t>(kb) & 15);
-      // inner coordinate (4-byte elements) of this head's box: the tensor map starts at the
-      // 16-byte boundary below head 0's first cell
-      const int tma_x = (int)((reinterpret_cast<uintptr_t>(kb) - delta -
-                               (reinterpret_cast<uintptr_t>(p.k.data) & ~(uintptr_t)15)) >> 2);
-      const uint32_t raw_s = tc::smem_u32(smem + L::raw);
-      // block id of this lane's page of a tile, -1 if no key of the page is in range
-      auto page_block = [&](int tile) -> int {
-        const int pos0 = (tile_begin + tile) * kKeys + lane * bs;
-        if (tile >= n_tiles || pos0 >= range_end || pos0 + bs <= range_begin) return -1;
-        return __ldg(bt + (pos0 >> p.block_shift));
-      };
-      int blk = page_block(0);
+      const uint32_t cell_off = my_page * bs * kRawRow + my_slot * row_pitch + delta;  // inside a raw stage
+      const bool odd = (cell_off & 8u) != 0;
+      int j = pgrp - g0 % NP;  // first tile of the item whose running count is pgrp mod NP
+      if (j < 0) j += NP;
 #pragma unroll 1
-      for (int j = 0; j < n_tiles; ++j) {
-        const int blk_next = page_block(j + 1);
-        const int rs = j % kRawStages;
-        if (j >= kRawStages) ok &= wait_or_abort(&bars[B::raw_free + rs], ((j / kRawStages) - 1) & 1, abort_flag);
-        uint64_t* bar = &bars[B::raw_full + rs];
-        if (blk >= 0 && ok) {
-          const uint32_t dst = raw_s + rs * kRawStageBytes + lane * bs * kRawRow;
-          if (p.raw_mode == 1) {
-            mbar_arrive_expect_tx(bar, bs * kRawRow);
-            tma_load_3d(dst, &tmap, tma_x, 0, blk, bar);
-          } else {
-            const uint8_t* src = kb + (int64_t)blk * p.k.stride_block - delta;
-            const uint32_t bytes = (delta + bs * (2 * kHeadDimI8 + 8) + 15u) & ~15u;
-            mbar_arrive_expect_tx(bar, bytes);
-            bulk_copy_g2s(dst, src, bytes, bar);
+      for (; j < n_tiles; j += NP) {
+        const int g = g0 + j;  // running tile count: indexes every ring
+        const int rs = g % kRawStages;
+        const int pos = (tile_begin + j) * kKeys + key;
+        const bool valid = pos >= range_begin && pos < range_end;
+        if constexpr (NP > 1) {
+          // A raw stage is shared by the producer groups in turn (NR is not a multiple of NP).
+          // A parity wait only tells apart two consecutive phases, so this group must not look
+          // at raw_full[rs] while the stage's PREVIOUS tile (another group's) is still pending:
+          // first wait until that tile has been taken out of the stage.
+          if (g >= kRawStages) ok &= wait_or_abort(&bars[B::raw_free + rs], ((g / kRawStages) - 1) & 1, abort_flag);
+        }
+        ok &= wait_or_abort(&bars[B::raw_full + rs], (g / kRawStages) & 1, abort_flag);
+        uint32_t w[kRawRow / 4];
+        if (valid) {
+          const uint4* row = reinterpret_cast<const uint4*>(smem + L::raw + rs * kRawStageBytes + (cell_off & ~15u));
+#pragma unroll
+          for (int c = 0; c < kRawRow / 16; ++c) {
+            const uint4 v = row[c];
+            w[4 * c] = v.x;
+            w[4 * c + 1] = v.y;
+            w[4 * c + 2] = v.z;
+            w[4 * c + 3] = v.w;
           }
         } else {
-          mbar_arrive(bar);
+#pragma unroll
+          for (int c = 0; c < kRawRow / 4; ++c) w[c] = 0u;
         }
-        blk = blk_next;
+        // this thread's row is in registers (the arrive orders the loads before it): once all
+        // 128 producers have arrived the loader may refill the raw stage
+        mbar_arrive(&bars[B::raw_free + rs]);
+        const int st = g % NS;
+        if (g >= NS) ok &= wait_or_abort(&bars[B::empty + st], ((g / NS) - 1) & 1, abort_flag);
+        // K image g % NK is free once QK(g - NK) has completed, which is what S^T of that tile
+        // being ready means: the producers wait on the s_ready barrier the softmax group waits
+        // on (one commit less per tile for the issuing thread).  That barrier completes next
+        // for a tile whose images this group writes after this wait, so the parity is unambiguous.
+        if (g >= NK) {
+          const int q = g - NK, qk = q >> 1;
+          ok &= wait_or_abort(&bars[B::s_ready + 2 * (q & 1) + qk % SB], (qk / SB) & 1, abort_flag);
+        }
+        uint8_t* stage = smem + L::vstages + st * kVStageBytes;  // V image, then the scales
+        uint8_t* krow = smem + L::kstages + (g % NK) * kImgBytes + pt * 16;
+        uint8_t* vrow = stage + pt * 16;
+        if (!odd) {
+#pragma unroll
+          for (int b = 0; b < 8; ++b) {
+            *reinterpret_cast<uint4*>(krow + b * kImgChunk) = make_uint4(w[4 * b], w[4 * b + 1], w[4 * b + 2], w[4 * b + 3]);
+            *reinterpret_cast<uint4*>(vrow + b * kImgChunk) =
+                make_uint4(w[33 + 4 * b], w[34 + 4 * b], w[35 + 4 * b], w[36 + 4 * b]);
+          }
+          *reinterpret_cast<uint32_t*>(stage + kImgBytes + pt * 4) = w[32];
+          *reinterpret_cast<uint32_t*>(stage + kImgBytes + kKeys * 4 + pt * 4) = w[65];
+        } else {
+#pragma unroll
+          for (int b = 0; b < 8; ++b) {
+            *reinterpret_cast<uint4*>(krow + b * kImgChunk) =
+                make_uint4(w[2 + 4 * b], w[3 + 4 * b], w[4 + 4 * b], w[5 + 4 * b]);
+            *reinterpret_cast<uint4*>(vrow + b * kImgChunk) =
+                make_uint4(w[35 + 4 * b], w[36 + 4 * b], w[37 + 4 * b], w[38 + 4 * b]);
+          }
+          *reinterpret_cast<uint32_t*>(stage + kImgBytes + pt * 4) = w[34];
+          *reinterpret_cast<uint32_t*>(stage + kImgBytes + kKeys * 4 + pt * 4) = w[67];
+        }
+        tc::fence_async_smem();
+        mbar_arrive(&bars[B::full + st]);
       }
+      g0 += n_tiles;
+      mbar_arrive(&bars[B::item_empty + slot]);
     }
   } else if (warp == kMmaWarp) {
     // =========================== MMA issuer ===================================
-    // ONE thread (lane 0) issues every tcgen05.mma of the CTA, in a fixed order (two issuing
-    // threads, one for QK and one for PV, produced rare run-to-run differences):
+    // ONE thread (lane 0) issues every tcgen05.mma of the CTA, item after item, inside an item
+    // in a fixed order (two issuing threads, one for QK and one for PV, produced rare
+    // run-to-run differences):
     //   QK(0), QK(1), then for i = 0, 1, ...: QK(i + 2), PV(i).
-    //   QK(i): tile i is the k-th tile (k = i >> 1) of softmax group g = i & 1 and lands in
-    //          that group's S^T buffer k % SB; needs the tile's images (full) and that
+    // With g = running tile count of tile i:
+    //   QK(i): the tile belongs to softmax group g & 1, is that group's k-th tile (k = g >> 1)
+    //          and lands in its S^T buffer k % SB; needs the tile's images (full) and that
     //          buffer read by the softmax (s_free);
     //   PV(i): needs the group's P image (p_ready) and its O^T buffer folded (o_free); its
     //          completion frees the V stage.
     // Every condition of a step depends only on MMAs issued earlier in this order, so the
     // order cannot deadlock, and QK runs two tiles ahead of PV, which is as far as the S^T
-    // buffers allow.  The two barriers of a step are waited for by lanes 0 and 1 in the same
-    // instruction: a look at an mbarrier costs 100-200 cycles on the busy shared-memory pipe,
-    // and four looks in a row per tile made this thread the bottleneck of the CTA.
+    // buffers allow.  The next item's first QK follows the last PV of this item at once: its
+    // images have long been filled, so S^T of the next item is ready while the softmax groups
+    // still merge and write this one.  The two barriers of a step are waited for by lanes 0
+    // and 1 in the same instruction: a look at an mbarrier costs 100-200 cycles on the busy
+    // shared-memory pipe, and four looks in a row per tile made this thread the bottleneck.
     // This thread's own instruction stream is the narrowest part of the CTA (a few hundred
     // dependent instructions per tile took as long as the tile), so everything it needs is
     // kept in registers: barrier addresses as shared-memory offsets, operand descriptors as
     // word pairs that move by one addition per MMA.
-    named_barrier(5, kSoftmaxThreads + 32);  // wait for the Q image
-    {
-      STAT_DECL
-      const uint32_t bars_s = tc::smem_u32(bars);
-      const DescWords qd = desc_words(tc::smem_u32(qimg), 2 * NPAD * 16, 128);
-      const DescWords kd = desc_words(kstage0, kImgChunk, 128);
-      const DescWords vd = desc_words(vstage0, 128, kImgChunk);
-      const DescWords pd = desc_words(tc::smem_u32(pimg), 128, kDigitChunk);
-      // lane 0 waits for barrier i0 (parity par0); lane 1 for barrier i1 if need1; true when both are complete
-      auto wait_pair = [&](int i0, uint32_t par0, int i1, uint32_t par1, bool need1) -> bool {
-        const uint32_t mine = bars_s + 8u * (uint32_t)(lane == 0 ? i0 : i1);
-        const uint32_t par = lane == 0 ? par0 : par1;
-        const bool need = lane == 0 || (lane == 1 && need1);
-        const bool done = !need || wait_or_abort_s(mine, par, abort_flag);
-        return __all_sync(0xffffffffu, done);
-      };
-      auto qk_step = [&](int q) -> bool {
+    const uint32_t bars_s = tc::smem_u32(bars);
+    const DescWords kd = desc_words(kstage0, kImgChunk, 128);
+    const DescWords vd = desc_words(vstage0, 128, kImgChunk);
+    const DescWords pd = desc_words(tc::smem_u32(pimg), 128, kDigitChunk);
+    // lane 0 waits for barrier i0 (parity par0); lane 1 for barrier i1 if need1; true when both are complete
+    auto wait_pair = [&](int i0, uint32_t par0, int i1, uint32_t par1, bool need1) -> bool {
+      const uint32_t mine = bars_s + 8u * (uint32_t)(lane == 0 ? i0 : i1);
+      const uint32_t par = lane == 0 ? par0 : par1;
+      const bool need = lane == 0 || (lane == 1 && need1);
+      const bool done = !need || wait_or_abort_s(mine, par, abort_flag);
+      return __all_sync(0xffffffffu, done);
+    };
+    int g0 = 0;
+    bool go = true;
+#pragma unroll 1
+    for (int item = 0; go; ++item) {
+      const int slot = item % kItemSlots;
+      go = wait_or_abort(&bars[B::item_full + slot], (item / kItemSlots) & 1, abort_flag);
+      if (!go) break;
+      const int n_tiles = descs[slot].n_tiles;
+      if (n_tiles == 0) break;
+      tc::fence_after_sync();
+      const DescWords qd = desc_words(tc::smem_u32(smem + L::qimg + slot * L::qimg_bytes), 2 * NPAD * 16, 128);
+      auto qk_step = [&](int q) -> bool {  // q = running tile count
         const int g = q & 1, k = q >> 1, sb = k % SB;
-        const bool go = wait_pair(B::full + q % NS, (q / NS) & 1, B::s_free + 2 * g + sb, ((k / SB) - 1) & 1, k >= SB);
-        if (go && lane == 0) {
-          TL(q, 13)
+        const bool ready = wait_pair(B::full + q % NS, (q / NS) & 1, B::s_free + 2 * g + sb, ((k / SB) - 1) & 1, k >= SB);
+        if (ready && lane == 0) {
           tc::fence_after_sync();
-          TL(q, 4)
           DescWords kq = kd;
           kq.lo += (uint32_t)(q % NK) * (kImgBytes >> 4);
           issue_qk_i8_words<NPAD>(tmem_base + (g * SB + sb) * L::s_cols, kq, qd);
-          TL(q, 9)
           tc::mma_commit_s(bars_s + 8u * (B::s_ready + 2 * g + sb));
-          TL(q, 10)
         }
-        return go;
+        return ready;
       };
       auto pv_step = [&](int i) -> bool {
         const int g = i & 1;
-        const bool go = wait_pair(B::p_ready + g, (i >> 1) & 1, B::o_free + g, ((i >> 1) - 1) & 1, i >= 2);
-        if (go && lane == 0) {
-          TL(i, 14)
+        const bool ready = wait_pair(B::p_ready + g, (i >> 1) & 1, B::o_free + g, ((i >> 1) - 1) & 1, i >= 2);
+        if (ready && lane == 0) {
           tc::fence_after_sync();
-          TL(i, 8)
           DescWords vi = vd, pi = pd;
           vi.lo += (uint32_t)(i % NS) * (kVStageBytes >> 4);
           pi.lo += (uint32_t)g * ((PD * NPAD * kKeys) >> 4);
           issue_pv_i8_words<NPAD, PD>(tmem_base + L::s_total + g * L::o_cols, vi, pi);
-          TL(i, 11)
           tc::mma_commit_s(bars_s + 8u * (B::o_ready + g));
           tc::mma_commit_s(bars_s + 8u * (B::empty + i % NS));
-          TL(i, 12)
         }
-        return go;
+        return ready;
       };
-      bool go = qk_step(0);
-      if (go && n_tiles > 1) go = qk_step(1);
+      go = qk_step(g0);
+      if (go && n_tiles > 1) go = qk_step(g0 + 1);
 #pragma unroll 1
       for (int i = 0; i < n_tiles && go; ++i) {
-        if (i + 2 < n_tiles) go = qk_step(i + 2);
-        if (go) go = pv_step(i);
+        if (i + 2 < n_tiles) go = qk_step(g0 + i + 2);
+        if (go) go = pv_step(g0 + i);
       }
-      ok &= go;
+      g0 += n_tiles;
       __syncwarp();
-      if (lane == 0) { STAT_FLUSH(1) }
+      if (lane == 0) mbar_arrive(&bars[B::item_empty + slot]);
     }
+    ok &= go;
+    __syncwarp();
   } else if (warp < 2 * 4) {
     // =========================== softmax ======================================
-    // Two warpgroups: group g owns the tiles i with i & 1 == g and keeps its own running
-    // maximum, sum and accumulator (as if the KV range were split in two inside the CTA);
-    // the two states are merged in the epilogue.  Thread t of a group owns key t of S^T and
-    // output column d = t of O^T.
-    if (tid < NPAD) {
-      int lo = 0, hi = -1;
-      if (tid < rows) visible_range(p, t, t.first_idx + tid / p.group, &lo, &hi);
-      rlo[tid] = lo;
-      rhi[tid] = hi;
-    }
-    // Q digits: 8 threads per row, 16 elements each (32 rows per pass).  The page copies
-    // and the realignment of the first tiles run meanwhile.
-    {
-      for (int base = 0; base < NPAD; base += 32) {
-        const int n = base + (tid >> 3), part = tid & 7;
-        float v[16];
-        if (n < rows) {
-          int token, head;
-          row_target(p, t, kvh, n, &token, &head);
-          const uint4* src = reinterpret_cast<const uint4*>(p.q + (int64_t)token * p.q_stride_token +
-                                                            (int64_t)head * p.q_stride_head + part * 32);
-          const uint4 a = src[0], b = src[1];
-          const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-  #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            v[2 * e] = __uint_as_float(w[e] << 16);
-            v[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
-          }
-        } else {
-  #pragma unroll
-          for (int e = 0; e < 16; ++e) v[e] = 0.f;
-        }
-        float amax = 0.f;
-  #pragma unroll
-        for (int e = 0; e < 16; ++e) amax = fmaxf(amax, fabsf(v[e]));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-        const bool finite_row = amax > 0.f && amax < INFINITY;
-        const float inv = finite_row ? 32512.f / amax : 0.f;
-        uint32_t hi_w[4] = {0, 0, 0, 0}, lo_w[4] = {0, 0, 0, 0};
-  #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          int qi = __float2int_rn(v[e] * inv);
-          qi = max(-32512, min(32512, qi));
-          const int qh = (qi + 128) >> 8;
-          const int ql = qi - (qh << 8);
-          hi_w[e >> 2] |= (uint32_t)(qh & 0xff) << (8 * (e & 3));
-          lo_w[e >> 2] |= (uint32_t)(ql & 0xff) << (8 * (e & 3));
-        }
-        // image row of (digit, n) is digit * NPAD + n; 16-byte column block `part`
-        if (n < NPAD) {
-        *reinterpret_cast<uint4*>(qimg + part * (2 * NPAD * 16) + n * 16) = make_uint4(hi_w[0], hi_w[1], hi_w[2], hi_w[3]);
-        *reinterpret_cast<uint4*>(qimg + part * (2 * NPAD * 16) + (NPAD + n) * 16) =
-            make_uint4(lo_w[0], lo_w[1], lo_w[2], lo_w[3]);
-        if (part == 0) sq[n] = finite_row ? amax / 32512.f : 0.f;
-        }
-      }
-    }
-    tc::fence_async_smem();
-    named_barrier(5, kSoftmaxThreads + 32);  // Q image, row scales and masks complete; the QK issuer may start
+    // Two warpgroups: group g owns the tiles whose running count is g mod 2 and keeps its own
+    // running maximum, sum and accumulator (as if the KV range were split in two inside the
+    // CTA); the two states are merged at the end of every item.  Thread t of a group owns
+    // key t of S^T and output column d = t of O^T.
     const int g = warp >> 2;
     const int gt = tid & 127;          // thread index inside the group
     const int gw = warp & 3;           // warp inside the group = TMEM lane quadrant
@@ -555,41 +693,51 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     uint8_t* pimg_g = pimg + g * (PD * NPAD * kKeys);
     float* wred_g = wred + g * (2 * 4 * (NPAD + 1));   // [2][4][NPAD + 1]
     float* mrun_g = mrun + g * (2 * NPAD);             // [2][NPAD]
-    int mask_lo, mask_hi, tmp;  // key positions every live row sees: such tiles need no mask
-    visible_range(p, t, t.first_idx + t.ntok - 1, &mask_lo, &tmp);
-    visible_range(p, t, t.first_idx, &tmp, &mask_hi);
-
-    STAT_DECL
     constexpr int NROW = 4 * RQ;  // rows this instance computes (live rows rounded up to four)
-    float acc[NROW], l_part[NROW];
-#pragma unroll
-    for (int n = 0; n < NROW; ++n) {
-      acc[n] = 0.f;
-      l_part[n] = 0.f;
-    }
-    // Per-row softmax state lives in LANES, not in shared memory: lane l of every warp holds,
-    // for row l + 32 j, the running maximum and the factors of the latest tile (every warp
-    // computes the same values), and the row loops fetch them with warp shuffles.
     constexpr int RL = (NPAD + 31) / 32;
-    float m_run[RL], a_l[RL], unit_l[RL], muse_l[RL], invu_l[RL];
-#pragma unroll
-    for (int j = 0; j < RL; ++j) {
-      m_run[j] = -INFINITY;
-      a_l[j] = 0.f;
-      unit_l[j] = 0.f;
-      muse_l[j] = 0.f;
-      invu_l[j] = 0.f;
-    }
+    const int my_key = tile_key(p, gt);
 
-    // Folds O^T of tile j (this group's TMEM buffer) into the register accumulator, with the
-    // rescale factor and digit unit of that tile (still in a_l / unit_l).
-    auto fold_o = [&](int j) {
-      STAT_WAIT(1, ok &= wait_or_abort(&bars[B::o_ready + g], (j >> 1) & 1, abort_flag))
-      tc::fence_after_sync();
-      const uint32_t o_tmem = tmem_base + L::s_total + g * L::o_cols + lane_addr;
+    int g0 = 0, item = 0;
+    ok &= wait_or_abort(&bars[B::item_full + 0], 0, abort_flag);
+    bool stop = named_barrier_or(4, kSoftmaxThreads, !ok || descs[0].n_tiles == 0);
+#pragma unroll 1
+    while (!stop) {
+      const int slot = item % kItemSlots;
+      const int n_tiles = descs[slot].n_tiles, tile_begin = descs[slot].tile_begin;
+      const int kvh = descs[slot].kvh, split = descs[slot].split, tok0 = descs[slot].tok0;
+      const int rows = descs[slot].ntok * p.group;  // <= NROW by construction of bq
+      const int mask_lo = descs[slot].mask_lo, mask_hi = descs[slot].mask_hi;
+      const float* sq = reinterpret_cast<const float*>(smem + L::sq) + slot * NPAD;
+      const int* rlo = reinterpret_cast<const int*>(smem + L::rlo) + slot * NPAD;
+      const int* rhi = reinterpret_cast<const int*>(smem + L::rhi) + slot * NPAD;
+
+      float acc[NROW], l_part[NROW];
 #pragma unroll
-      for (int q4 = 0; q4 < RQ; ++q4) {
-        {
+      for (int n = 0; n < NROW; ++n) {
+        acc[n] = 0.f;
+        l_part[n] = 0.f;
+      }
+      // Per-row softmax state lives in LANES, not in shared memory: lane l of every warp holds,
+      // for row l + 32 j, the running maximum and the factors of the latest tile (every warp
+      // computes the same values), and the row loops fetch them with warp shuffles.
+      float m_run[RL], a_l[RL], unit_l[RL], muse_l[RL], invu_l[RL];
+#pragma unroll
+      for (int j = 0; j < RL; ++j) {
+        m_run[j] = -INFINITY;
+        a_l[j] = 0.f;
+        unit_l[j] = 0.f;
+        muse_l[j] = 0.f;
+        invu_l[j] = 0.f;
+      }
+
+      // Folds O^T of the tile with running count q (this group's TMEM buffer) into the register
+      // accumulator, with the rescale factor and digit unit of that tile (still in a_l / unit_l).
+      auto fold_o = [&](int q) {
+        ok &= wait_or_abort(&bars[B::o_ready + g], (q >> 1) & 1, abort_flag);
+        tc::fence_after_sync();
+        const uint32_t o_tmem = tmem_base + L::s_total + g * L::o_cols + lane_addr;
+#pragma unroll
+        for (int q4 = 0; q4 < RQ; ++q4) {
           uint32_t d[PD][4];
 #pragma unroll
           for (int k = 0; k < PD; ++k) tmem_ld4(o_tmem + k * NPAD + q4 * 4, d[k]);
@@ -605,36 +753,34 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
             acc[n] = fmaf(acc[n], alpha_n, o * unit_n);
           }
         }
-      }
-      tc::fence_before_sync();
-      mbar_arrive(&bars[B::o_free + g]);
-    };
+        tc::fence_before_sync();
+        mbar_arrive(&bars[B::o_free + g]);
+      };
 
-    int it = 0;  // iteration count of this group; buffers alternate with it & 1
+      int lit = 0;                // tiles of this item this group has started
+      int j = (g - g0) & 1;       // first tile of the item whose running count is g mod 2
 #pragma unroll 1
-    for (int i = g; i < n_tiles; i += 2, ++it) {
-      const int b = it & 1;
-      float* wred_i = wred_g + b * 4 * (NPAD + 1);
-      const uint8_t* scales = smem + L::vstages + (i % NS) * kVStageBytes + kImgBytes;
-      const int sb = it % SB;
-      if (gt == 0) { TL(i, 5) }
-      STAT_WAIT(0, ok &= wait_or_abort(&bars[B::s_ready + 2 * g + sb], (it / SB) & 1, abort_flag))
-      tc::fence_after_sync();
-      if (gt == 0) { TL(i, 6) }
-      STAT_T(tS0_)
-      const float ks_cur = reinterpret_cast<const float*>(scales)[gt];
-      const float vs_cur = reinterpret_cast<const float*>(scales)[kKeys + gt];
-      const uint32_t s_tmem = tmem_base + (g * SB + sb) * L::s_cols + lane_addr;
-      const int pos = (tile_begin + i) * kKeys + tile_key(p, gt);
-      const bool interior = (tile_begin + i) * kKeys >= mask_lo && (tile_begin + i) * kKeys + (kKeys - 1) <= mask_hi;
-      const float mult = ks_cur * p.scale_log2;
-      float s[NROW];
-      int mykey[RL];  // warp maximum of row lane + 32 j, as an ordered integer key
+      for (; j < n_tiles; j += 2, ++lit) {
+        const int q = g0 + j;     // running tile count
+        const int it = q >> 1;    // running count of this group's tiles; buffers alternate with it
+        const int b = it & 1;
+        float* wred_i = wred_g + b * 4 * (NPAD + 1);
+        const uint8_t* scales = smem + L::vstages + (q % NS) * kVStageBytes + kImgBytes;
+        const int sb = it % SB;
+        ok &= wait_or_abort(&bars[B::s_ready + 2 * g + sb], (it / SB) & 1, abort_flag);
+        tc::fence_after_sync();
+        const float ks_cur = reinterpret_cast<const float*>(scales)[gt];
+        const float vs_cur = reinterpret_cast<const float*>(scales)[kKeys + gt];
+        const uint32_t s_tmem = tmem_base + (g * SB + sb) * L::s_cols + lane_addr;
+        const int pos = (tile_begin + j) * kKeys + my_key;
+        const bool interior = (tile_begin + j) * kKeys >= mask_lo && (tile_begin + j) * kKeys + (kKeys - 1) <= mask_hi;
+        const float mult = ks_cur * p.scale_log2;
+        float s[NROW];
+        int mykey[RL];  // warp maximum of row lane + 32 j, as an ordered integer key
 #pragma unroll
-      for (int j = 0; j < RL; ++j) mykey[j] = float_key(-INFINITY);
+        for (int jj = 0; jj < RL; ++jj) mykey[jj] = float_key(-INFINITY);
 #pragma unroll
-      for (int q4 = 0; q4 < RQ; ++q4) {
-        {
+        for (int q4 = 0; q4 < RQ; ++q4) {
           uint32_t hi[4], lo[4];
           tmem_ld4(s_tmem + q4 * 4, hi);
           tmem_ld4(s_tmem + NPAD + q4 * 4, lo);
@@ -649,165 +795,156 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
             if (lane == (n & 31)) mykey[n >> 5] = key;
           }
         }
-      }
 #pragma unroll
-      for (int j = 0; j < RL; ++j)
-        if (lane + 32 * j < NPAD) wred_i[gw * (NPAD + 1) + lane + 32 * j] = key_float(mykey[j]);
-      STAT_ADD(3, clock64() - tS0_)
-      STAT_T(tS1_)
-      tc::fence_before_sync();
-      mbar_arrive(&bars[B::s_free + 2 * g + sb]);  // this S^T buffer may be overwritten by a later QK
-      {
-        const int key = __reduce_max_sync(0xffffffffu, float_key(vs_cur));
-        if (lane == 0) wred_i[gw * (NPAD + 1) + NPAD] = key_float(key);
-      }
-      // O^T of this group's previous tile; afterwards its P image is free.
-      STAT_ADD(4, clock64() - tS1_)
-      STAT_T(tS2_)
-      if (it > 0) fold_o(i - 2);
-      STAT_ADD(5, clock64() - tS2_)
-      STAT_WAIT(2, named_barrier(1 + g, kGroupThreads))
-      STAT_T(tS3_)  // per-warp maxima of the tile visible to the whole group
-      const float vs_max = fmaxf(fmaxf(wred_i[NPAD], wred_i[(NPAD + 1) + NPAD]),
-                                 fmaxf(wred_i[2 * (NPAD + 1) + NPAD], wred_i[3 * (NPAD + 1) + NPAD]));
+        for (int jj = 0; jj < RL; ++jj)
+          if (lane + 32 * jj < NPAD) wred_i[gw * (NPAD + 1) + lane + 32 * jj] = key_float(mykey[jj]);
+        tc::fence_before_sync();
+        mbar_arrive(&bars[B::s_free + 2 * g + sb]);  // this S^T buffer may be overwritten by a later QK
+        {
+          const int key = __reduce_max_sync(0xffffffffu, float_key(vs_cur));
+          if (lane == 0) wred_i[gw * (NPAD + 1) + NPAD] = key_float(key);
+        }
+        // O^T of this group's previous tile of the item; afterwards its P image is free.
+        if (lit > 0) fold_o(q - 2);
+        named_barrier(1 + g, kGroupThreads);  // per-warp maxima of the tile visible to the whole group
+        const float vs_max = fmaxf(fmaxf(wred_i[NPAD], wred_i[(NPAD + 1) + NPAD]),
+                                   fmaxf(wred_i[2 * (NPAD + 1) + NPAD], wred_i[3 * (NPAD + 1) + NPAD]));
 #pragma unroll
-      for (int j = 0; j < RL; ++j) {
-        const int r = (lane + 32 * j) & (NPAD - 1);
-        const float m_tile = fmaxf(fmaxf(wred_i[r], wred_i[(NPAD + 1) + r]),
-                                   fmaxf(wred_i[2 * (NPAD + 1) + r], wred_i[3 * (NPAD + 1) + r]));
-        const float m_old = m_run[j];
-        const float m_new = fmaxf(m_old, m_tile);
-        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-        a_l[j] = fast_exp2(m_old - m_use);
-        // largest p * v_scale of the tile bounds the fixed-point range of its digits
-        const float bound = vs_max * fast_exp2(m_tile - m_use);
-        invu_l[j] = bound > 0.f ? __fdividef((float)XMAX, bound) : 0.f;
-        unit_l[j] = bound * (1.0f / (float)XMAX);
-        muse_l[j] = m_use;
-        m_run[j] = m_new;
-      }
+        for (int jj = 0; jj < RL; ++jj) {
+          const int r = (lane + 32 * jj) & (NPAD - 1);
+          const float m_tile = fmaxf(fmaxf(wred_i[r], wred_i[(NPAD + 1) + r]),
+                                     fmaxf(wred_i[2 * (NPAD + 1) + r], wred_i[3 * (NPAD + 1) + r]));
+          const float m_old = m_run[jj];
+          const float m_new = fmaxf(m_old, m_tile);
+          const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+          a_l[jj] = fast_exp2(m_old - m_use);
+          // largest p * v_scale of the tile bounds the fixed-point range of its digits
+          const float bound = vs_max * fast_exp2(m_tile - m_use);
+          invu_l[jj] = bound > 0.f ? __fdividef((float)XMAX, bound) : 0.f;
+          unit_l[jj] = bound * (1.0f / (float)XMAX);
+          muse_l[jj] = m_use;
+          m_run[jj] = m_new;
+        }
 #pragma unroll
-      for (int q16 = 0; q16 < NPAD / 16; ++q16) {
-        if (q16 * 4 < RQ) {
-          uint32_t dig[PD][4] = {};
+        for (int q16 = 0; q16 < NPAD / 16; ++q16) {
+          if (q16 * 4 < RQ) {
+            uint32_t dig[PD][4] = {};
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            // Whole groups of four rows, padded rows included (their scores are finite
-            // and their columns of O^T are never read): no branch per row, so the four
-            // dependency chains overlap.
-            if (q16 * 4 + q4 < RQ) {
+            for (int q4 = 0; q4 < 4; ++q4) {
+              // Whole groups of four rows, padded rows included (their scores are finite
+              // and their columns of O^T are never read): no branch per row, so the four
+              // dependency chains overlap.
+              if (q16 * 4 + q4 < RQ) {
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int n = q16 * 16 + q4 * 4 + e;
-                const float m_use = __shfl_sync(0xffffffffu, muse_l[n >> 5], n & 31);
-                const float a = __shfl_sync(0xffffffffu, a_l[n >> 5], n & 31);
-                const float inv_u = __shfl_sync(0xffffffffu, invu_l[n >> 5], n & 31);
-                const float pr = fast_exp2(s[n] - m_use);
-                l_part[n] = fmaf(l_part[n], a, pr);
-                int x = __float2int_rn(pr * vs_cur * inv_u);
-                x = min(x, XMAX);
+                for (int e = 0; e < 4; ++e) {
+                  const int n = q16 * 16 + q4 * 4 + e;
+                  const float m_use = __shfl_sync(0xffffffffu, muse_l[n >> 5], n & 31);
+                  const float a = __shfl_sync(0xffffffffu, a_l[n >> 5], n & 31);
+                  const float inv_u = __shfl_sync(0xffffffffu, invu_l[n >> 5], n & 31);
+                  const float pr = fast_exp2(s[n] - m_use);
+                  l_part[n] = fmaf(l_part[n], a, pr);
+                  int x = __float2int_rn(pr * vs_cur * inv_u);
+                  x = min(x, XMAX);
 #pragma unroll
-                for (int k = 0; k < PD; ++k) dig[k][q4] |= (uint32_t)((x >> (7 * k)) & 127) << (8 * e);
+                  for (int k = 0; k < PD; ++k) dig[k][q4] |= (uint32_t)((x >> (7 * k)) & 127) << (8 * e);
+                }
               }
             }
+#pragma unroll
+            for (int k = 0; k < PD; ++k)
+              *reinterpret_cast<uint4*>(pimg_g + (k * (NPAD / 16) + q16) * kDigitChunk + gt * 16) =
+                  make_uint4(dig[k][0], dig[k][1], dig[k][2], dig[k][3]);
           }
-#pragma unroll
-          for (int k = 0; k < PD; ++k)
-            *reinterpret_cast<uint4*>(pimg_g + (k * (NPAD / 16) + q16) * kDigitChunk + gt * 16) =
-                make_uint4(dig[k][0], dig[k][1], dig[k][2], dig[k][3]);
         }
+        tc::fence_async_smem();
+        mbar_arrive(&bars[B::p_ready + g]);  // P image of the tile complete
       }
-      STAT_ADD(6, clock64() - tS3_)
-      STAT_T(tS4_)
-      tc::fence_async_smem();
-      mbar_arrive(&bars[B::p_ready + g]);  // P image of tile i complete
-      if (gt == 0) { TL(i, 7) }
-      STAT_ADD(7, clock64() - tS4_)
-    }
-    if (it > 0) fold_o(g + 2 * (it - 1));
-    if (gt == 0) { STAT_FLUSH(2) }
-    STAT_MARK(2)
+      if (lit > 0) fold_o(g0 + j - 2);  // the group's last tile of the item
 
-    // ---- epilogue: reduce the row sums inside the group, merge the two groups ----
-    named_barrier(1 + g, kGroupThreads);
-    float* wsum = wred_g;  // [4][NPAD + 1]
-    if (gw == 0) {
+      // ---- end of the item: reduce the row sums inside the group, merge the two groups ----
+      // Every PV of the item has been folded by now, so the P images of both groups are idle:
+      // group 1 parks its accumulator there ([row][d] fp32) for group 0 to pick up.
+      named_barrier(4, kSoftmaxThreads);  // both groups have left their last tile
+      float* wsum = wred_g;  // [4][NPAD + 1]
+      if (gw == 0) {
 #pragma unroll
-      for (int j = 0; j < RL; ++j)
-        if (lane + 32 * j < NPAD) mrun_g[lane + 32 * j] = m_run[j];
-    }
-#pragma unroll
-    for (int n = 0; n < NROW; ++n) {
-      if (n < rows) {
-        float v = l_part[n];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == (n & 31)) wsum[gw * (NPAD + 1) + n] = v;
+        for (int jj = 0; jj < RL; ++jj)
+          if (lane + 32 * jj < NPAD) mrun_g[lane + 32 * jj] = m_run[jj];
       }
-    }
-    // group 1 parks its accumulator in the raw ring ([row][d]) once the producers have
-    // finished with it, i.e. once the image of the last tile is complete
-    float* park = reinterpret_cast<float*>(smem + L::raw);
-    if (g == 1) {
-      ok &= wait_or_abort(&bars[B::full + (n_tiles - 1) % NS], ((n_tiles - 1) / NS) & 1, abort_flag);
-#pragma unroll
-      for (int n = 0; n < NROW; ++n)
-        if (n < rows) park[n * kKeys + gt] = acc[n];
-    }
-    named_barrier(4, 2 * kGroupThreads);  // both groups: sums, maxima and the parked accumulator visible
-    if (g == 0) {
-      const float* w0 = wred;
-      const float* w1 = wred + 2 * 4 * (NPAD + 1);
-      const float* m0p = mrun;             // running maxima published by the two groups
-      const float* m1p = mrun + 2 * NPAD;
 #pragma unroll
       for (int n = 0; n < NROW; ++n) {
         if (n < rows) {
-          const float l0 = w0[n] + w0[(NPAD + 1) + n] + w0[2 * (NPAD + 1) + n] + w0[3 * (NPAD + 1) + n];
-          const float l1 = w1[n] + w1[(NPAD + 1) + n] + w1[2 * (NPAD + 1) + n] + w1[3 * (NPAD + 1) + n];
-          const float m0 = m0p[n], m1 = m1p[n];
-          const float m = fmaxf(m0, m1);
-          const float c0 = m0 == -INFINITY ? 0.f : fast_exp2(m0 - m);
-          const float c1 = m1 == -INFINITY ? 0.f : fast_exp2(m1 - m);
-          const float l = l0 * c0 + l1 * c1;
-          const float o = acc[n] * c0 + (c1 > 0.f ? park[n * kKeys + gt] * c1 : 0.f);
-          const float val = l > 0.f ? o / l : 0.f;
-          int token, head;
-          row_target(p, t, kvh, n, &token, &head);
-          if (p.num_splits == 1) {
-            store_out_elem(p.out + (int64_t)token * p.out_stride_token + (int64_t)head * p.out_stride_head, gt,
-                           p.out_dtype, val);
-          } else {
-            reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.ws_o) + (int64_t)split * p.ws_o_stride_split +
-                                     (int64_t)token * p.ws_o_stride_token + (int64_t)head * p.ws_o_stride_head)[gt] = val;
-          }
-          if (gt == n) {
-            const float lse2 = l > 0.f ? m + log2f(l) : -INFINITY;
-            if (p.num_splits > 1) {
-              *reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.ws_lse) + (int64_t)split * p.ws_lse_stride_split +
-                                        (int64_t)token * p.ws_lse_stride_token + (int64_t)head * p.ws_lse_stride_head) = lse2;
-            } else if (p.lse_out != nullptr) {
-              *reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.lse_out) + (int64_t)token * p.lse_stride_token +
-                                        (int64_t)head * p.lse_stride_head) = lse2 * kLn2;
+          float v = l_part[n];
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+          if (lane == (n & 31)) wsum[gw * (NPAD + 1) + n] = v;
+        }
+      }
+      float* park = reinterpret_cast<float*>(pimg);
+      if (g == 1) {
+#pragma unroll
+        for (int n = 0; n < NROW; ++n)
+          if (n < rows) park[n * kKeys + gt] = acc[n];
+      }
+      named_barrier(4, kSoftmaxThreads);  // sums, maxima and the parked accumulator visible
+      if (g == 0) {
+        const float* w0 = wred;
+        const float* w1 = wred + 2 * 4 * (NPAD + 1);
+        const float* m0p = mrun;             // running maxima published by the two groups
+        const float* m1p = mrun + 2 * NPAD;
+#pragma unroll
+        for (int n = 0; n < NROW; ++n) {
+          if (n < rows) {
+            const float l0 = w0[n] + w0[(NPAD + 1) + n] + w0[2 * (NPAD + 1) + n] + w0[3 * (NPAD + 1) + n];
+            const float l1 = w1[n] + w1[(NPAD + 1) + n] + w1[2 * (NPAD + 1) + n] + w1[3 * (NPAD + 1) + n];
+            const float m0 = m0p[n], m1 = m1p[n];
+            const float m = fmaxf(m0, m1);
+            const float c0 = m0 == -INFINITY ? 0.f : fast_exp2(m0 - m);
+            const float c1 = m1 == -INFINITY ? 0.f : fast_exp2(m1 - m);
+            const float l = l0 * c0 + l1 * c1;
+            const float o = acc[n] * c0 + (c1 > 0.f ? park[n * kKeys + gt] * c1 : 0.f);
+            const float val = l > 0.f ? o / l : 0.f;
+            const int token = tok0 + n / p.group, head = kvh * p.group + n % p.group;
+            if (p.num_splits == 1) {
+              store_out_elem(p.out + (int64_t)token * p.out_stride_token + (int64_t)head * p.out_stride_head, gt,
+                             p.out_dtype, val);
+            } else {
+              reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.ws_o) + (int64_t)split * p.ws_o_stride_split +
+                                       (int64_t)token * p.ws_o_stride_token + (int64_t)head * p.ws_o_stride_head)[gt] = val;
+            }
+            if (gt == n) {
+              const float lse2 = l > 0.f ? m + log2f(l) : -INFINITY;
+              if (p.num_splits > 1) {
+                *reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.ws_lse) + (int64_t)split * p.ws_lse_stride_split +
+                                          (int64_t)token * p.ws_lse_stride_token + (int64_t)head * p.ws_lse_stride_head) = lse2;
+              } else if (p.lse_out != nullptr) {
+                *reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.lse_out) + (int64_t)token * p.lse_stride_token +
+                                          (int64_t)head * p.lse_stride_head) = lse2 * kLn2;
+              }
             }
           }
         }
       }
+      // ---- next item: the slot is released, and the barrier that protects the buffers of the
+      // merge also makes "no more items" one decision of all 256 threads ----
+      mbar_arrive(&bars[B::item_empty + slot]);
+      g0 += n_tiles;
+      ++item;
+      const int nslot = item % kItemSlots;
+      ok &= wait_or_abort(&bars[B::item_full + nslot], (item / kItemSlots) & 1, abort_flag);
+      stop = named_barrier_or(4, kSoftmaxThreads, !ok || descs[nslot].n_tiles == 0);
     }
   }
 
-  STAT_MARK(3)
   tc::fence_before_sync();
   __syncthreads();
-  STAT_MARK(4)
-  STAT_EXIT
   if (warp == 0) tc::tmem_dealloc(tmem_base, L::tmem_alloc);
   if (tid == 0 && *abort_flag) atomicOr(&g_i8_status, 4u);
   (void)ok;
 }
 
 template <int NPAD, int PD, int NS, int NK, int NR, int SB, int RQ, int NP>
-cudaError_t launch_cfg(const KernelParams& p, const CUtensorMap& map, cudaStream_t stream) {
+cudaError_t launch_cfg(const KernelParams& p, const CUtensorMap& map, int num_ctas, cudaStream_t stream) {
   constexpr int smem = Layout<NPAD, PD, NS, NK, NR, SB>::total;
   static_assert(smem <= 227 * 1024, "shared memory of one CTA");
   static_assert(Layout<NPAD, PD, NS, NK, NR, SB>::tmem_need <= 512, "TMEM columns");
@@ -820,9 +957,20 @@ cudaError_t launch_cfg(const KernelParams& p, const CUtensorMap& map, cudaStream
     if (err != cudaSuccess) return err;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  const dim3 grid(p.num_q_tiles, p.num_kv_heads, p.num_splits);
-  umma_i8_attention_kernel<NPAD, PD, NS, NK, NR, SB, RQ, NP><<<grid, threads_for(NP), smem, stream>>>(p, map);
+  umma_i8_attention_kernel<NPAD, PD, NS, NK, NR, SB, RQ, NP><<<num_ctas, threads_for(NP), smem, stream>>>(p, map);
   return cudaGetLastError();
+}
+
+// SMs of the current device (looked up once per device).
+int sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+  if (dev >= 0 && dev < 64) cached[dev] = n;
+  return n;
 }
 
 }  // namespace
@@ -831,9 +979,11 @@ cudaError_t launch_cfg(const KernelParams& p, const CUtensorMap& map, cudaStream
 // (K | k_scale | V | v_scale contiguous, 2 D + 8 bytes, 8-byte aligned), pages of 16 to 128
 // keys whose byte stride is a multiple of 16, and either a slot stride that is a multiple
 // of 16 or cells that are contiguous inside a page, on top of what the tcgen05 kernels
-// need in general.
+// need in general.  Queries may be bf16 or fp16 (they become int8 digits either way).
 bool umma_i8_supports(const KernelParams& p, const char** why) {
-  if (!umma_supports(p, why)) return false;
+  KernelParams pq = p;
+  if (pq.q_dtype == PTH_ATTN_F16) pq.q_dtype = PTH_ATTN_BF16;
+  if (!umma_supports(pq, why)) return false;
   const int D = p.head_size;
   if (p.ks.data != p.k.data + D || p.v.data != p.k.data + D + 4 || p.vs.data != p.k.data + 2 * D + 4 ||
       p.ks.stride_head != p.k.stride_head || p.v.stride_head != p.k.stride_head ||
@@ -852,39 +1002,52 @@ bool umma_i8_supports(const KernelParams& p, const char** why) {
   return true;
 }
 
+// Kernels this launch enqueues and the CTAs of the attention kernel (no device access).
+int umma_i8_num_ctas(const KernelParams& p_in, int sms) {
+  KernelParams p = p_in;
+  if (p.row_class == 1) {
+    p.bq = p.class_rows / p.group > 0 ? p.class_rows / p.group : 1;
+  } else {
+    const int cap = 64 / p.group;
+    if (p.bq > cap) p.bq = cap;
+  }
+  const long long items = ((long long)p.num_tokens / p.bq + p.num_reqs) * p.num_kv_heads * p.num_splits;
+  if (items > 0x7fffffffll) return -1;
+  return (int)(items < sms ? items : sms);
+}
+
 cudaError_t launch_umma_i8_attention(const KernelParams& p_in, cudaStream_t stream) {
   KernelParams p = p_in;
   if (p.row_class == 1) {
-    // Only requests of at most class_rows rows: each is one row tile, tile x is request x.
+    // Only requests of at most class_rows rows: each is one row tile.
     p.bq = p.class_rows / p.group > 0 ? p.class_rows / p.group : 1;
-    p.tile_map = 1;
-    p.num_q_tiles = p.num_reqs;
   } else {
     const int cap = 64 / p.group;
-    set_row_tile(p, p.bq > cap ? cap : p.bq);
+    if (p.bq > cap) p.bq = cap;
   }
   p.raw_mode = raw_mode_for(p);
-  CUtensorMap map{};
-  if (p.raw_mode == 1 && !make_page_map(p, p.num_blocks, &map)) return cudaErrorInvalidValue;
+  const CUtensorMap* map = nullptr;
+  static const CUtensorMap no_map{};
+  if (p.raw_mode == 1) {
+    map = cached_page_map(p);
+    if (map == nullptr) return cudaErrorInvalidValue;
+  } else {
+    map = &no_map;
+  }
+  const int sms = sm_count();
+  if (sms <= 0) return cudaErrorInvalidDevice;
+  const int ctas = umma_i8_num_ctas(p_in, sms);
+  if (ctas < 1) return cudaErrorInvalidValue;
   const int rows = p.bq * p.group;
   // Instances by live rows: the softmax code of each handles exactly ceil(rows / 4) row
   // groups, which keeps the decode loop small enough for the instruction cache.
   // The decode instance (rows <= 4) needs few registers and runs two producer groups.
-  if (rows <= 4) return launch_cfg<16, 3, 4, 2, 3, 2, 1, 2>(p, map, stream);
-  if (rows <= 8) return launch_cfg<16, 3, 4, 2, 3, 2, 2, 1>(p, map, stream);
-  if (rows <= 16) return launch_cfg<16, 3, 4, 2, 3, 2, 4, 1>(p, map, stream);
-  if (rows <= 32) return launch_cfg<32, 2, 3, 2, 3, 1, 8, 1>(p, map, stream);
-  return launch_cfg<64, 2, 3, 2, 2, 1, 16, 1>(p, map, stream);
+  if (rows <= 4) return launch_cfg<16, 3, 4, 2, 3, 2, 1, 2>(p, *map, ctas, stream);
+  if (rows <= 8) return launch_cfg<16, 3, 4, 2, 3, 2, 2, 1>(p, *map, ctas, stream);
+  if (rows <= 16) return launch_cfg<16, 3, 4, 2, 3, 2, 4, 1>(p, *map, ctas, stream);
+  if (rows <= 32) return launch_cfg<32, 2, 3, 2, 3, 1, 8, 1>(p, *map, ctas, stream);
+  return launch_cfg<64, 2, 3, 2, 2, 1, 16, 1>(p, *map, ctas, stream);
 }
-
-#ifdef PTHB200_WAIT_STATS
-extern "C" int pthb200_debug_timeline(long long* out) {
-  return cudaMemcpyFromSymbol(out, g_timeline, sizeof(long long) * 256) == cudaSuccess ? 0 : -1;
-}
-extern "C" int pthb200_debug_wait_stats(long long* out) {
-  return cudaMemcpyFromSymbol(out, g_wait_stats, sizeof(long long) * 48) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 // Reads and clears the integer kernel's status word (device must be idle).
 cudaError_t read_i8_status(unsigned int* v) {

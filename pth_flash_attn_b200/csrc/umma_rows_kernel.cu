@@ -34,17 +34,6 @@
 namespace pthb200 {
 
 __device__ unsigned int g_rows_status = 0;
-#ifdef PTHB200_ROWS_STATS
-// Debug build only: cycles one thread of each role of CTA (0,0,0) spent in each phase.
-__device__ long long g_rows_stats[4][12];
-#define RSTAT_DECL long long st_[12] = {0}; const long long st_begin_ = clock64();
-#define RSTAT(slot, expr) { const long long t0_ = clock64(); expr; st_[slot] += clock64() - t0_; }
-#define RSTAT_FLUSH(role) if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { st_[11] = clock64() - st_begin_; for (int q_ = 0; q_ < 12; ++q_) g_rows_stats[role][q_] = st_[q_]; }
-#else
-#define RSTAT_DECL
-#define RSTAT(slot, expr) { expr; }
-#define RSTAT_FLUSH(role)
-#endif
 
 namespace {
 
@@ -213,14 +202,20 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
     const int my_page = (pt & (kHalfKeys - 1)) >> p.block_shift, my_slot = pt & (bs - 1);
     const uint32_t cell_off = my_page * bs * kRawRow + my_slot * row_pitch + delta;  // inside a half stage
     const bool odd = (cell_off & 8u) != 0;
-    RSTAT_DECL
 #pragma unroll 1
     for (int j = 0; j < n_tiles; ++j) {
       const int u = 2 * j + half;
       const int rs = u % kRNR;
       const int pos = (tile_begin + j) * kTileKeys + pt;
       const bool valid = pos >= range_begin && pos < range_end;
-      RSTAT(0, ok &= wait_or_abort(&bars[B::raw_full + rs], (u / kRNR) & 1, abort_flag))
+      // A raw slot is used by the two halves in turn (kRNR is odd), and a parity wait only
+      // tells apart two consecutive phases: this thread must not look at raw_full[rs] while
+      // the slot's PREVIOUS half stage (the other half's) is still pending, or it would take
+      // the phase before that one for its own, read stale bytes and release the slot early.
+      // Page copies can complete out of order, so nothing else rules that out.  Wait first
+      // until the previous occupant has been taken out of the slot.
+      if (u >= kRNR) ok &= wait_or_abort(&bars[B::raw_free + rs], ((u / kRNR) - 1) & 1, abort_flag);
+      ok &= wait_or_abort(&bars[B::raw_full + rs], (u / kRNR) & 1, abort_flag);
       // nine 16-byte chunks: raw words 0..35 (K half, k_scale) or 32..67 (k_scale, V half, v_scale)
       uint32_t w[36];
       if (valid) {
@@ -242,11 +237,7 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
       const int st = j % kRNS;
       if (!v_part) {
         uint8_t* kdst = smem + L::kimg + (j % kRNK) * kWideBytes + pt * 16;
-#ifdef EXP_H
-        if (j >= 1) RSTAT(1, ok &= wait_or_abort(&bars[B::s_ready + ((j - 1) & 1)], ((j - 1) >> 1) & 1, abort_flag))
-#else
-        if (j >= kRNK) RSTAT(1, ok &= wait_or_abort(&bars[B::kempty + j % kRNK], ((j / kRNK) - 1) & 1, abort_flag))
-#endif
+        if (j >= kRNK) ok &= wait_or_abort(&bars[B::kempty + j % kRNK], ((j / kRNK) - 1) & 1, abort_flag);
         float* ksc = reinterpret_cast<float*>(smem + L::ksc) + (j % kRKsRing) * kTileKeys;
         if (!odd) {
 #pragma unroll
@@ -264,11 +255,7 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
       } else {
         uint8_t* vstage = smem + L::vst + st * kRVStage;
         uint8_t* vdst = vstage + pt * 16;
-#ifdef EXP_H
-        if (j >= 2) RSTAT(2, ok &= wait_or_abort(&bars[B::pv_done + (j & 1)], ((j >> 1) - 1) & 1, abort_flag))
-#else
-        if (j >= kRNS) RSTAT(2, ok &= wait_or_abort(&bars[B::vempty + st], ((j / kRNS) - 1) & 1, abort_flag))
-#endif
+        if (j >= kRNS) ok &= wait_or_abort(&bars[B::vempty + st], ((j / kRNS) - 1) & 1, abort_flag);
         if (!odd) {
 #pragma unroll
           for (int c = 0; c < kChunks; ++c)
@@ -284,7 +271,6 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
         mbar_arrive(&bars[B::vfull + st]);
       }
     }
-    if (pt == 0 && !v_part) { RSTAT_FLUSH(0) }
   } else if (warp == kRLoadWarp) {
     // =========================== loader =======================================
     // One TMA copy per KV page of a tile, issued by lane `page`: a tiled tensor-map box of
@@ -339,46 +325,31 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
     // columns S(g) shares.
     named_barrier(5, kRSoftmax + 32);  // wait for the Q image
     if (lane == 0) {
-      RSTAT_DECL
       const uint32_t qimg_s = tc::smem_u32(qimg);
       auto issue_qk = [&](int i) {
         const int g = i & 1;
-        RSTAT(0, ok &= wait_or_abort(&bars[B::kfull + i % kRNK], (i / kRNK) & 1, abort_flag))
+        ok &= wait_or_abort(&bars[B::kfull + i % kRNK], (i / kRNK) & 1, abort_flag);
         tc::fence_after_sync();
         issue_qk_rows(tmem_base + g * 128, qimg_s, kimg_s + (i % kRNK) * kWideBytes);
         tc::mma_commit(&bars[B::s_ready + g]);
-#ifndef EXP_H
         tc::mma_commit(&bars[B::kempty + i % kRNK]);
-#endif
-#ifdef EXP_E
-        ok &= wait_or_abort(&bars[B::s_ready + g], (i >> 1) & 1, abort_flag);
-#endif
       };
       issue_qk(0);
       if (n_tiles > 1) issue_qk(1);
 #pragma unroll 1
       for (int i = 0; i < n_tiles; ++i) {
         const int g = i & 1, k = i >> 1;
-        RSTAT(2, ok &= wait_or_abort(&bars[B::p_ready + g], k & 1, abort_flag))
-#ifdef EXP_G
-        ok &= wait_or_abort(&bars[B::vfull + i % kRNS], (i / kRNS) & 1, abort_flag);
-#endif
+        ok &= wait_or_abort(&bars[B::p_ready + g], k & 1, abort_flag);
         tc::fence_after_sync();
         issue_pv_rows(tmem_base + 256 + g * 128, tmem_base + g * 128, vst_s + (i % kRNS) * kRVStage, k > 0);
         tc::mma_commit(&bars[B::pv_done + g]);
-#ifndef EXP_H
         tc::mma_commit(&bars[B::vempty + i % kRNS]);
-#endif
-#ifdef EXP_E
-        ok &= wait_or_abort(&bars[B::pv_done + g], k & 1, abort_flag);
-#endif
         if (i + 2 < n_tiles) {
           // S(g) doubles as P(g): it is free once this PV has completed
-          RSTAT(1, ok &= wait_or_abort(&bars[B::pv_done + g], k & 1, abort_flag))
+          ok &= wait_or_abort(&bars[B::pv_done + g], k & 1, abort_flag);
           issue_qk(i + 2);
         }
       }
-      RSTAT_FLUSH(1)
     }
   } else if (warp < 8) {
     // =========================== softmax ======================================
@@ -410,8 +381,6 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
     int mask_lo, mask_hi, tmp;  // key positions every live row sees: such tiles need no mask
     visible_range(p, t, t.first_idx + t.ntok - 1, &mask_lo, &tmp);
     visible_range(p, t, t.first_idx, &tmp, &mask_hi);
-
-    RSTAT_DECL
     float m_ref = -INFINITY;  // reference maximum of the row's exponentials (log2 units)
     float l = 0.f;            // sum of exp2(score - m_ref)
     int it = 0;
@@ -421,14 +390,8 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
       const float* vsp = reinterpret_cast<const float*>(smem + L::vst + (i % kRNS) * kRVStage + kWideBytes);
       const int pos0 = (tile_begin + i) * kTileKeys;
       const bool interior = pos0 >= mask_lo && pos0 + (kTileKeys - 1) <= mask_hi;
-      RSTAT(0, ok &= wait_or_abort(&bars[B::s_ready + g], it & 1, abort_flag))
-#ifdef EXP_C
-      ok &= wait_or_abort(&bars[B::vfull + i % kRNS], (i / kRNS) & 1, abort_flag);
-#endif
+      ok &= wait_or_abort(&bars[B::s_ready + g], it & 1, abort_flag);
       tc::fence_after_sync();
-#ifdef PTHB200_ROWS_STATS
-      const long long tp1_ = clock64();
-#endif
 
       // ---- pass 1: maximum of the row's scores in this tile ----
       // (two instances: interior tiles, which every live row sees whole, skip the mask)
@@ -460,17 +423,9 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
         }
       };
       if (interior) pass1(std::false_type{}); else pass1(std::true_type{});
-#ifdef PTHB200_ROWS_STATS
-      st_[1] += clock64() - tp1_;
-      const long long tp2_ = clock64();
-#endif
       // ---- move the reference maximum if the row has outgrown it ----
       const float m_new = fmaxf(m_ref, m_t);
-#ifdef EXP_A
-      const bool need = true;
-#else
       const bool need = m_t > m_ref + kRescaleGap;  // also true when m_ref is still -inf
-#endif
       if (it == 0) {
         m_ref = m_new;  // nothing accumulated yet
       } else if (__any_sync(0xffffffffu, need)) {
@@ -492,13 +447,9 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
         if (need) m_ref = m_new;
       }
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-#ifdef PTHB200_ROWS_STATS
-      st_[2] += clock64() - tp2_;
-      const long long tp3_ = clock64();
-#endif
 
       // ---- pass 2: p * v_scale as packed bf16 over the columns of S already read ----
-      RSTAT(5, ok &= wait_or_abort(&bars[B::vfull + i % kRNS], (i / kRNS) & 1, abort_flag))  // v_scale (and V) of tile i
+      ok &= wait_or_abort(&bars[B::vfull + i % kRNS], (i / kRNS) & 1, abort_flag);  // v_scale (and V) of tile i
       auto pass2 = [&](auto masked) {
         constexpr bool kMask = decltype(masked)::value;
 #pragma unroll 1
@@ -534,21 +485,10 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
         }
       };
       if (interior) pass2(std::false_type{}); else pass2(std::true_type{});
-#ifdef PTHB200_ROWS_STATS
-      st_[3] += clock64() - tp3_;
-#endif
-#ifdef EXP_B
       tc::tmem_st_wait();
-      named_barrier(1 + g, kRGroup);
-#endif
-#ifdef EXP_D
-      tc::tmem_st_wait();
-      tc::fence_async_smem();
-      __threadfence_block();
-#endif
-      RSTAT(4, tc::tmem_st_wait(); tc::fence_before_sync(); mbar_arrive(&bars[B::p_ready + g]))  // P of tile i complete
+      tc::fence_before_sync();
+      mbar_arrive(&bars[B::p_ready + g]);  // P of tile i complete
     }
-    if (tid == 0) { RSTAT_FLUSH(3) }
 
     // ---- epilogue: merge the two groups' (m, l, O) and write the rows ----
     const int my_tiles = it;
@@ -702,10 +642,5 @@ cudaError_t read_rows_status(unsigned int* v) {
 
 }  // namespace pthb200
 
-#ifdef PTHB200_ROWS_STATS
-extern "C" int pthb200_debug_rows_stats(long long* out) {
-  return cudaMemcpyFromSymbol(out, pthb200::g_rows_stats, sizeof(long long) * 48) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 #include "umma_rows_tile_test.cuh"

@@ -1,50 +1,37 @@
 """Host-side launch planner of ``pth_flash_attn_fwd`` for B200 (sm_100a).
 
-Same public surface as the reference planner (python/pth_flash_attn/planner.py:
-``plan_launch``, ``LaunchPlan``, ``c_target``, ``s_alone``, ``max_tokens_per_tile``,
-``wm_for_rows``, ``split_tile_range``, ``workspace_token_splits``,
-``workspace_shapes``, ``workspace_bytes``, ``DESCRIPTOR_FIELDS``), same contract:
+The public names, keyword-only signatures, ``DESCRIPTOR_FIELDS`` and exception types are
+those of the reference planner (python/pth_flash_attn/planner.py:102-113, 147-381;
+docs/api.md:135-145), so callers and their tests can switch modules.  The contract is the
+reference's too: pure Python, no device query, every argument a host ``int`` / ``bool``
+taken from the padded batch descriptor (a 0-d tensor is refused because converting it
+would be a hidden device-to-host copy), and no argument that carries a sequence length,
+so one plan is valid for every replay of a CUDA graph captured for its descriptor.
 
-* pure Python, standard library only, no device query;
-* every input is a host ``int``/``bool`` of the padded batch descriptor (a 0-d
-  tensor is refused: converting it would be a hidden device-to-host sync);
-* there is no sequence-length parameter, so a plan is valid for every replay of
-  a CUDA graph captured for its descriptor.
+What is planned differs, because the kernels differ:
 
-What differs is the machine model.  A row tile of this library holds up to 64
-rows (query heads of one KV head x query tokens), as in the reference, but at
-head size 128 the kernel is one warp-specialised CTA per SM (it keeps about
-220 KB of cache bytes in flight in shared memory) on a 148-SM part and reads
-the cache in 128-key tiles.  The split count is chosen per launch from the
-descriptor:
+* The attention kernel for short row tiles is persistent: it is launched with one CTA per
+  SM, cuts every request into pieces of about equal length ON THE DEVICE (where the
+  lengths are) and deals the pieces out to its CTAs.  The host's ``num_splits`` is
+  therefore only a bound - the most pieces a request may be cut into, which is what sizes
+  the workspace - and the planner's job is to make that bound generous enough:
 
-    work items per split = Hkv * row tiles            (row tiles: see below)
-    S = max(1, C_target // items)
+      unsplit = Hkv * row tiles of the launch        work items without any split
+      S = ceil(ITEMS_PER_SM * SMs / unsplit)         pieces so that every SM gets a handful
+      S = min(S, s_alone)                            never more than a lone request needs
 
-that is: no split once the unsplit work items fill the GPU, otherwise the
-largest count that still fits ONE wave.  Every CTA pays a fixed cost (finding
-its row tile, quantising Q, filling the copy pipeline, merging its two softmax
-groups) worth some tens of KV tiles, and every split adds a partial for the
-combine kernel to read, so more, shorter CTAs than one wave lose more than a
-fuller last wave wins (measured on B200 at 8 K and 128 K keys per request).
-``wm`` keeps its meaning of "16 * wm rows per tile" because it is part of the
-op's frozen schema; the kernels pad rows to 16/32/64 accordingly.
+  ``s_alone`` = ``ceil(2 * SMs / Hkv)``: a single request is cut so that every SM gets two
+  pieces of it.  The kernel never uses more pieces than keep a piece above a few KV tiles,
+  so a generous bound costs workspace, not time.
+* ``wm`` keeps its meaning of "16 * wm rows per tile" because it is an argument of the
+  op's frozen schema; rows per tile are 16, 32 or 64 and the kernels pad to those.
+* A sliding window caps the pieces at the number of 128-key tiles a row tile can touch.
 """
 
 from __future__ import annotations
 
-from dataclasses import dataclass
-
-ROWS_PER_WM = 16
-WM_CHOICES = (1, 2, 4)
-MAX_ROWS_PER_CTA = ROWS_PER_WM * WM_CHOICES[-1]
-# Resident CTAs per SM of the attention kernels, by head size.
-CTAS_PER_SM = {64: 4, 128: 1, 256: 2}
-SUPPORTED_HEAD_SIZES = tuple(sorted(CTAS_PER_SM))
-WINDOWED_HEAD_SIZES = (128,)
-KV_TILE_TOKENS = 128
-PARTIAL_BYTES_PER_ELEMENT = 4
-B200_NUM_SMS = 148
+import dataclasses
+import numbers
 
 DESCRIPTOR_FIELDS = (
     "num_tokens",
@@ -59,70 +46,94 @@ DESCRIPTOR_FIELDS = (
     "window",
 )
 
+# machine and kernel model
+B200_NUM_SMS = 148
+KV_TILE_TOKENS = 128               # keys per KV tile of every kernel family
+ROWS_PER_WM = 16
+WM_CHOICES = (1, 2, 4)
+MAX_ROWS_PER_CTA = ROWS_PER_WM * max(WM_CHOICES)
+CTAS_PER_SM = {64: 4, 128: 1, 256: 2}   # resident CTAs per SM by head size
+SUPPORTED_HEAD_SIZES = tuple(sorted(CTAS_PER_SM))
+WINDOWED_HEAD_SIZES = (128,)
+ITEMS_PER_SM = 8                   # pieces of work per SM the split bound allows for
+ALONE_ITEMS_PER_SM = 2             # pieces per SM for a single request
+PARTIAL_BYTES_PER_ELEMENT = 4
 
-def _ceil_div(a: int, b: int) -> int:
-    return -(-a // b)
 
-
-def _require_int(name: str, value: object, minimum: int) -> int:
-    if not isinstance(value, int) or isinstance(value, bool):
+def _host_int(name: str, value: object, *, at_least: int) -> int:
+    """``value`` as an int, refusing bools, tensors and anything else that is not a plain int."""
+    if isinstance(value, bool) or not isinstance(value, numbers.Integral) or type(value).__module__ != "builtins":
         raise TypeError(f"{name} must be a host int, got {type(value).__name__}")
-    if value < minimum:
-        raise ValueError(f"{name} must be >= {minimum}, got {value}")
-    return value
+    if value < at_least:
+        raise ValueError(f"{name} must be >= {at_least}, got {value}")
+    return int(value)
 
 
-def _require_head_size(D: object) -> int:
-    d = _require_int("D", D, 1)
+def _head_size(D: object) -> int:
+    d = _host_int("D", D, at_least=1)
     if d not in CTAS_PER_SM:
         raise ValueError(f"D must be one of {SUPPORTED_HEAD_SIZES}, got {d}")
     return d
 
 
-def _require_group_size(G: object) -> int:
-    g = _require_int("G", G, 1)
+def _group_size(G: object) -> int:
+    g = _host_int("G", G, at_least=1)
     if g > MAX_ROWS_PER_CTA:
         raise ValueError(f"G must be <= {MAX_ROWS_PER_CTA}, got {g}")
     return g
 
 
+def _ceil_div(a: int, b: int) -> int:
+    return (a + b - 1) // b
+
+
 def c_target(*, D: int, num_sms: int) -> int:
-    """CTAs that fill the GPU in one wave: SMs x resident CTAs per SM at head size D."""
-    d = _require_head_size(D)
-    return _require_int("num_sms", num_sms, 1) * CTAS_PER_SM[d]
+    """CTAs resident at once: ``num_sms`` x the CTAs of head size ``D`` one SM holds."""
+    return CTAS_PER_SM[_head_size(D)] * _host_int("num_sms", num_sms, at_least=1)
 
 
 def max_tokens_per_tile(G: int) -> int:
-    """Query tokens of one request that fit one 64-row tile: ``64 // G``."""
-    return MAX_ROWS_PER_CTA // _require_group_size(G)
+    """Query tokens of one request in a 64-row tile."""
+    return MAX_ROWS_PER_CTA // _group_size(G)
 
 
 def wm_for_rows(rows: int) -> int:
-    """Smallest wm in {1, 2, 4} with ``16 * wm >= rows``."""
-    r = _require_int("rows", rows, 1)
-    for wm in WM_CHOICES:
-        if r <= ROWS_PER_WM * wm:
-            return wm
-    raise ValueError(f"{r} rows exceed one {MAX_ROWS_PER_CTA}-row tile")
+    """The smallest ``wm`` whose ``16 * wm`` rows hold ``rows``."""
+    need = _host_int("rows", rows, at_least=1)
+    fitting = [wm for wm in WM_CHOICES if ROWS_PER_WM * wm >= need]
+    if not fitting:
+        raise ValueError(f"{need} rows exceed one {MAX_ROWS_PER_CTA}-row tile")
+    return fitting[0]
 
 
 def split_tile_range(*, split: int, num_splits: int, num_tiles: int) -> tuple[int, int]:
-    """KV tiles ``[floor(s T / S), floor((s + 1) T / S))`` of split ``s`` (the device rule)."""
-    s_count = _require_int("num_splits", num_splits, 1)
-    s = _require_int("split", split, 0)
-    tiles = _require_int("num_tiles", num_tiles, 0)
-    if s >= s_count:
-        raise ValueError(f"split {s} out of range for num_splits={s_count}")
-    return s * tiles // s_count, (s + 1) * tiles // s_count
+    """KV tiles of piece ``split`` when ``num_tiles`` tiles are cut into ``num_splits`` pieces.
 
-
-@dataclass(frozen=True)
-class LaunchPlan:
-    """What one ``pth_flash_attn_fwd`` call needs from the host.
-
-    ``wm`` and ``num_splits`` are arguments of the op; the other fields record
-    the descriptor and the shapes derived from it.
+    The device's rule (csrc/sched.cuh ``split_tile_span``): piece s is
+    ``[s * n // S, (s + 1) * n // S)`` - whole tiles, disjoint, covering, sizes within one.
     """
+    pieces = _host_int("num_splits", num_splits, at_least=1)
+    which = _host_int("split", split, at_least=0)
+    tiles = _host_int("num_tiles", num_tiles, at_least=0)
+    if which >= pieces:
+        raise ValueError(f"split {which} out of range for num_splits={pieces}")
+    return which * tiles // pieces, (which + 1) * tiles // pieces
+
+
+def s_alone(*, Hkv: int, D: int, num_sms: int) -> int:
+    """Pieces a lone row tile per KV head is cut into: every SM gets two of them."""
+    heads = _host_int("Hkv", Hkv, at_least=1)
+    return max(1, _ceil_div(ALONE_ITEMS_PER_SM * c_target(D=D, num_sms=num_sms), heads))
+
+
+def _split_bound(unsplit_items: int, *, Hkv: int, D: int, num_sms: int) -> int:
+    wanted = _ceil_div(ITEMS_PER_SM * c_target(D=D, num_sms=num_sms), unsplit_items)
+    return max(1, min(wanted, s_alone(Hkv=Hkv, D=D, num_sms=num_sms)))
+
+
+@dataclasses.dataclass(frozen=True)
+class LaunchPlan:
+    """The host's part of one op call: ``wm`` and ``num_splits`` go to the op as they are."""
 
     wm: int
     bq: int
@@ -136,34 +147,30 @@ class LaunchPlan:
 
     @property
     def Hq(self) -> int:
-        return self.G * self.Hkv
+        return self.Hkv * self.G
 
     @property
     def rows_per_cta(self) -> int:
-        return self.bq * self.G
+        return self.G * self.bq
 
     @property
     def grid(self) -> tuple[int, int, int]:
-        return (self.q_tiles_upper, self.Hkv, self.num_splits)
+        return self.q_tiles_upper, self.Hkv, self.num_splits
+
+    def _partial_splits(self) -> int:
+        return 0 if self.num_splits == 1 else self.num_splits
 
     @property
     def ws_token_splits_used(self) -> int:
-        return self.num_splits * self.num_tokens if self.num_splits > 1 else 0
+        return self._partial_splits() * self.num_tokens
 
     @property
     def ws_o_shape(self) -> tuple[int, int, int, int]:
-        s = self.num_splits if self.num_splits > 1 else 0
-        return (s, self.num_tokens, self.Hq, self.D)
+        return self._partial_splits(), self.num_tokens, self.Hq, self.D
 
     @property
     def ws_lse_shape(self) -> tuple[int, int, int]:
-        s = self.num_splits if self.num_splits > 1 else 0
-        return (s, self.num_tokens, self.Hq)
-
-
-def _pick_splits(items: int, target: int) -> int:
-    """Largest split count whose CTAs still fit one wave (1 if the items alone fill it)."""
-    return max(1, target // items)
+        return self._partial_splits(), self.num_tokens, self.Hq
 
 
 def plan_launch(
@@ -179,86 +186,67 @@ def plan_launch(
     ws_token_splits: int,
     window: int = 0,
 ) -> LaunchPlan:
-    """Plan one launch from the padded batch descriptor of its slice."""
-    t = _require_int("num_tokens", num_tokens, 1)
-    reqs = _require_int("num_reqs", num_reqs, 1)
-    q_max = _require_int("max_query_len", max_query_len, 1)
-    g = _require_group_size(G)
-    hkv = _require_int("Hkv", Hkv, 1)
-    d = _require_head_size(D)
-    sms = _require_int("num_sms", num_sms, 1)
-    w_ts = _require_int("ws_token_splits", ws_token_splits, 0)
-    w = _require_int("window", window, 0)
-    if not isinstance(is_prefill, bool):
+    """Plan one op call from the padded batch descriptor of its slice of the batch."""
+    tokens = _host_int("num_tokens", num_tokens, at_least=1)
+    requests = _host_int("num_reqs", num_reqs, at_least=1)
+    longest = _host_int("max_query_len", max_query_len, at_least=1)
+    group = _group_size(G)
+    heads = _host_int("Hkv", Hkv, at_least=1)
+    head_size = _head_size(D)
+    sms = _host_int("num_sms", num_sms, at_least=1)
+    reserved = _host_int("ws_token_splits", ws_token_splits, at_least=0)
+    win = _host_int("window", window, at_least=0)
+    if type(is_prefill) is not bool:
         raise TypeError(f"is_prefill must be a bool, got {type(is_prefill).__name__}")
-    if q_max > t:
-        raise ValueError(f"max_query_len={q_max} > num_tokens={t}")
-    if t > reqs * q_max:
-        raise ValueError(f"num_tokens={t} cannot come from {reqs} requests of at most {q_max} tokens")
+    if longest > tokens:
+        raise ValueError(f"max_query_len={longest} > num_tokens={tokens}")
+    if tokens > requests * longest:
+        raise ValueError(f"num_tokens={tokens} cannot come from {requests} requests of at most {longest} tokens")
 
-    b_max = max_tokens_per_tile(g)
+    tile_tokens = max_tokens_per_tile(group)
     if is_prefill:
-        wm = WM_CHOICES[-1]
-        row_tiles = _ceil_div(t, b_max)
+        # chunks of any length: full 64-row tiles over all tokens
+        wm = max(WM_CHOICES)
+        row_tiles = _ceil_div(tokens, tile_tokens)
     else:
-        rt = _ceil_div(q_max, b_max)
-        wm = wm_for_rows(_ceil_div(q_max, rt) * g)
-        # every request is assumed to bring its full rt tiles (lengths are not visible here)
-        row_tiles = rt * reqs
-    bq = ROWS_PER_WM * wm // g
+        # every request may be as long as the longest: the fewest tiles that hold it,
+        # then the lowest tile that holds its share
+        tiles_per_request = _ceil_div(longest, tile_tokens)
+        wm = wm_for_rows(group * _ceil_div(longest, tiles_per_request))
+        row_tiles = requests * tiles_per_request
+    bq = (ROWS_PER_WM * wm) // group
 
-    s_want = _pick_splits(hkv * row_tiles, c_target(D=d, num_sms=sms))
-    s_cap = w_ts // t
-    num_splits = max(1, min(s_want, s_cap))
-    if w > 0:
-        # The most KV tiles one row tile can touch at the worst alignment.
-        num_splits = min(num_splits, _ceil_div(w + q_max - 2, KV_TILE_TOKENS) + 1)
-
-    return LaunchPlan(
-        wm=wm,
-        bq=bq,
-        q_tiles_upper=t // bq + reqs,
-        num_splits=num_splits,
-        num_tokens=t,
-        G=g,
-        Hkv=hkv,
-        D=d,
-        is_prefill=is_prefill,
-    )
-
-
-def s_alone(*, Hkv: int, D: int, num_sms: int) -> int:
-    """Splits that let ONE row tile per KV head fill one wave of the GPU."""
-    hkv = _require_int("Hkv", Hkv, 1)
-    return _pick_splits(hkv, c_target(D=D, num_sms=num_sms))
+    pieces = _split_bound(heads * row_tiles, Hkv=heads, D=head_size, num_sms=sms)
+    pieces = min(pieces, reserved // tokens)   # S > 1 only if S * T fits the reservation
+    if win:
+        # a row tile sees at most win + longest - 1 keys; at the worst alignment they touch
+        touched = _ceil_div(win + longest - 2, KV_TILE_TOKENS) + 1
+        pieces = min(pieces, touched)
+    return LaunchPlan(wm=wm, bq=bq, q_tiles_upper=tokens // bq + requests, num_splits=max(1, pieces),
+                      num_tokens=tokens, G=group, Hkv=heads, D=head_size, is_prefill=is_prefill)
 
 
 def workspace_token_splits(*, max_num_seqs: int, q_dec_max: int, Hkv: int, D: int, num_sms: int) -> int:
-    """Token-splits to reserve so that every plan this module makes fits.
+    """The reservation ``W_ts`` under which no decode-like plan of this module is clamped.
 
-    A launch of R requests of up to ``q_dec_max`` tokens needs ``S * T`` with
-    ``T <= R * q_dec_max`` and ``S <= max(1, C_target // (Hkv * R))``.
+    A launch of ``r <= max_num_seqs`` requests of up to ``q_dec_max`` tokens asks for
+    ``S(r) * T`` token-splits with ``T <= r * q_dec_max``; the bound below takes the worst
+    ``r``, with the fewest row tiles such a launch can have (one per request).
     """
-    seqs = _require_int("max_num_seqs", max_num_seqs, 1)
-    q_dec = _require_int("q_dec_max", q_dec_max, 1)
-    alone = s_alone(Hkv=Hkv, D=D, num_sms=num_sms)
-    target = c_target(D=D, num_sms=num_sms)
-    hkv = _require_int("Hkv", Hkv, 1)
-    worst = 0
-    for r in range(1, seqs + 1):
-        worst = max(worst, min(_pick_splits(hkv * r, target), alone) * r * q_dec)
-    return worst
+    most = _host_int("max_num_seqs", max_num_seqs, at_least=1)
+    longest = _host_int("q_dec_max", q_dec_max, at_least=1)
+    heads = _host_int("Hkv", Hkv, at_least=1)
+    return max(_split_bound(heads * r, Hkv=heads, D=D, num_sms=num_sms) * r * longest for r in range(1, most + 1))
 
 
 def workspace_shapes(*, ws_token_splits: int, Hq: int, D: int) -> tuple[tuple[int, int, int], tuple[int, int]]:
-    """fp32 shapes to reserve: O partials ``[W_ts, Hq, D]`` and log2-LSE ``[W_ts, Hq]``."""
-    w_ts = _require_int("ws_token_splits", ws_token_splits, 0)
-    hq = _require_int("Hq", Hq, 1)
-    d = _require_head_size(D)
-    return (w_ts, hq, d), (w_ts, hq)
+    """Shapes of the two fp32 buffers to reserve: partial outputs and their log2-sum-exp."""
+    rows = _host_int("ws_token_splits", ws_token_splits, at_least=0)
+    heads = _host_int("Hq", Hq, at_least=1)
+    return (rows, heads, _head_size(D)), (rows, heads)
 
 
 def workspace_bytes(*, ws_token_splits: int, Hq: int, D: int) -> int:
-    """``W_ts * Hq * (D + 1) * 4``: both fp32 partial buffers."""
-    o_shape, lse_shape = workspace_shapes(ws_token_splits=ws_token_splits, Hq=Hq, D=D)
-    return (o_shape[0] * o_shape[1] * o_shape[2] + lse_shape[0] * lse_shape[1]) * PARTIAL_BYTES_PER_ELEMENT
+    """Bytes of both buffers together: ``W_ts * Hq * (D + 1) * 4``."""
+    (rows, heads, head_size), _ = workspace_shapes(ws_token_splits=ws_token_splits, Hq=Hq, D=D)
+    return rows * heads * (head_size + 1) * PARTIAL_BYTES_PER_ELEMENT

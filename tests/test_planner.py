@@ -31,6 +31,8 @@ def test_rejects_non_host_ints():
         _plan(G=True)
     with pytest.raises(TypeError):
         _plan(is_prefill=1)
+    with pytest.raises(TypeError):
+        _plan(num_reqs=__import__("numpy").int64(64))
     with pytest.raises(ValueError):
         _plan(D=96)
     with pytest.raises(ValueError):
@@ -60,22 +62,29 @@ def test_plan_is_a_pure_function_of_the_descriptor():
 
 
 def test_baseline_shapes():
-    # one request at any length must still spread over the machine
+    # one request at any length must still spread over the machine: two pieces per SM
     one = _plan(num_tokens=1, num_reqs=1)
-    assert one.wm == 1 and one.bq == 4 and one.num_splits == planner.c_target(D=128, num_sms=148) // 8 == 18
-    # a full batch needs few splits
+    assert one.wm == 1 and one.bq == 4 and one.num_splits == planner.s_alone(Hkv=8, D=128, num_sms=148) == 37
+    # a full batch needs only a small bound (the device cuts 8,192-key requests in two)
     full = _plan()
-    assert 1 <= full.num_splits <= 16
+    assert full.num_splits == 3
+    # monotone in the machine size, never below one
+    assert [_plan(num_sms=n).num_splits for n in (1, 32, 148, 1000)] == sorted(
+        _plan(num_sms=n).num_splits for n in (1, 32, 148, 1000))
     # verify: 4 draft tokens x G = 4 -> 16 rows
     v = _plan(num_tokens=128, num_reqs=32, max_query_len=4)
-    assert v.wm == 1 and v.bq == 4
+    assert v.wm == 1 and v.bq == 4 and v.num_splits == 5
     # drafter: 16 tokens x 4 heads = 64 rows, window caps the splits
     d = _plan(num_tokens=512, num_reqs=32, max_query_len=16, window=4096)
     assert d.wm == 4 and d.bq == 16
     assert d.num_splits <= -(-(4096 + 16 - 2) // planner.KV_TILE_TOKENS) + 1
+    tight = _plan(num_tokens=1, num_reqs=1, window=200)
+    assert tight.num_splits == -(-(200 + 1 - 2) // planner.KV_TILE_TOKENS) + 1 == 3
     # prefill
     pf = _plan(num_tokens=8192, num_reqs=4, max_query_len=2048, G=8, is_prefill=True)
-    assert pf.wm == 4 and pf.bq == 8
+    assert pf.wm == 4 and pf.bq == 8 and pf.num_splits == 1
+    # no reservation, no split
+    assert _plan(num_tokens=1, num_reqs=1, ws_token_splits=0).num_splits == 1
 
 
 def test_workspace_reservation_covers_every_plan():
