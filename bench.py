@@ -286,7 +286,7 @@ class Workload:
     the attention kernels alone (one graph per cache set; sets rotate so that a pass never
     finds its cache in L2)."""
 
-    def __init__(self, torch, name, rank, world, device, num_sms, l2_bytes, seed=1234):
+    def __init__(self, torch, name, rank, world, device, num_sms, l2_bytes, seed=1234, graphs=True):
         self.torch, self.name, self.world = torch, name, world
         self.launches = workload_launches(name)
         hkv_total = self.launches[0]["Hkv"]
@@ -304,8 +304,9 @@ class Workload:
         for d in self.dls:  # one eager pass: sets kernel attributes, builds the page maps
             d.launch(0)
         torch.cuda.synchronize()
-        self.graphs = self._capture(lambda d, s: d.launch(s))
-        self.attn_graphs = self._capture(lambda d, s: d.launch_attention_only(s))
+        if graphs:
+            self.graphs = self._capture(lambda d, s: d.launch(s))
+            self.attn_graphs = self._capture(lambda d, s: d.launch_attention_only(s))
 
     def _capture(self, fn):
         torch = self.torch
@@ -643,7 +644,7 @@ def main():
     else:
         hbm_peak, tc_peak, tc_sustained, peak_src = 6650.0, 1590.0, 1400.0, "fallback"
 
-    wl = Workload(torch, args.config, rank, world, device, num_sms, l2_bytes)
+    wl = Workload(torch, args.config, rank, world, device, num_sms, l2_bytes, graphs=not args.profile)
     if args.profile:
         for i in range(2):
             for d in wl.dls:

@@ -75,6 +75,34 @@ __device__ __forceinline__ bool wait_or_abort_s(uint32_t bar_s, uint32_t parity,
   return false;
 }
 
+// The same wait for a thread that others wait for (the MMA-issuing thread): it polls without
+// a suspend hint, so it sees the phase complete as early as possible.
+__device__ __forceinline__ bool wait_or_abort_spin_s(uint32_t bar_s, uint32_t parity, volatile int* abort_flag) {
+  if (tc::mbar_try_wait_s(bar_s, parity)) return true;
+  const long long deadline = clock64() + (1ll << 32);
+  for (;;) {
+    if (tc::mbar_try_wait_s(bar_s, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() > deadline) break;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+// True in exactly one lane of a converged warp (elect.sync): the form in which the compiler
+// knows that a single thread issues what follows.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 __device__ __forceinline__ void row_target(const KernelParams& p, const RowTile& t, int kvh, int n, int* token, int* head) {
   *token = t.tok0 + n / p.group;
   *head = kvh * p.group + n % p.group;
@@ -155,6 +183,18 @@ const CUtensorMap* cached_page_map(const KernelParams& p) {
   }
   thread_local CUtensorMap scratch;
   return make_page_map(p, p.num_blocks, &scratch) ? &scratch : nullptr;
+}
+
+// SMs of the current device (looked up once per device).
+int sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+  if (dev >= 0 && dev < 64) cached[dev] = n;
+  return n;
 }
 
 // 1 = tiled TMA per page, 2 = bulk copy per contiguous page run, 0 = neither applies.

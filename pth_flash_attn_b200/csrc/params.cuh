@@ -56,6 +56,7 @@ struct KernelParams {
   // How grid index x maps to a row tile, and which requests this launch serves.
   int32_t tile_map;    // 0 = padded tile grid (bisection over query_start_loc); 1 = row tile x is request x
                        //     (valid when no request has more than bq query tokens): num_q_tiles = num_reqs
+  int32_t num_sms;     // SMs of the device (set by the launchers whose kernels choose splits on the device)
   int32_t row_class;   // 0 = every request; 1 = only requests with q_len * group <= class_rows; 2 = only the others
   int32_t class_rows;
 };
@@ -139,8 +140,9 @@ __device__ __forceinline__ void visible_range(const KernelParams& p, const RowTi
 
 // KV tiles [tile_begin, tile_end) that split `split` of this row tile reads:
 // the tiles touched by the union of the rows' visible ranges, divided into
-// num_splits runs whose sizes differ by at most one.
-__device__ __forceinline__ void split_tiles(const KernelParams& p, const RowTile& t, int split,
+// num_splits runs whose sizes differ by at most one (num_splits: the launch's, or the number
+// of pieces the kernel has chosen for this request).
+__device__ __forceinline__ void split_tiles(const KernelParams& p, const RowTile& t, int split, int num_splits,
                                             int* tile_begin, int* tile_end, int* range_begin,
                                             int* range_end) {
   int lo_first, hi_first, lo_last, hi_last;
@@ -157,8 +159,13 @@ __device__ __forceinline__ void split_tiles(const KernelParams& p, const RowTile
   const int t0 = rb / kKvTile;
   const int t1 = (re + kKvTile - 1) / kKvTile;
   const int64_t n = t1 - t0;
-  *tile_begin = t0 + (int)((int64_t)split * n / p.num_splits);
-  *tile_end = t0 + (int)((int64_t)(split + 1) * n / p.num_splits);
+  *tile_begin = t0 + (int)((int64_t)split * n / num_splits);
+  *tile_end = t0 + (int)((int64_t)(split + 1) * n / num_splits);
+}
+__device__ __forceinline__ void split_tiles(const KernelParams& p, const RowTile& t, int split,
+                                            int* tile_begin, int* tile_end, int* range_begin,
+                                            int* range_end) {
+  split_tiles(p, t, split, p.num_splits, tile_begin, tile_end, range_begin, range_end);
 }
 
 __device__ __forceinline__ float load_q_elem(const uint8_t* q_row, int d, int dtype) {

@@ -87,6 +87,12 @@ __device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t* r) {
                : "memory");
 }
 
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
+               "r"(r[2]), "r"(r[3])
+               : "memory");
+}
+
 // Instruction descriptor of tcgen05.mma.kind::i8: signed 8-bit operands, int32 accumulator.
 __host__ __device__ constexpr uint32_t idesc_i8(uint32_t m, uint32_t n, uint32_t a_mn, uint32_t b_mn) {
   return (2u << 4) | (1u << 7) | (1u << 10) | (a_mn << 15) | (b_mn << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);

@@ -597,7 +597,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     }
   } else if (warp == kMmaWarp) {
     // =========================== MMA issuer ===================================
-    // ONE thread (lane 0) issues every tcgen05.mma of the CTA, item after item, inside an item
+    // ONE thread (the lane elect.sync picks) issues every tcgen05.mma of the CTA, item after item, inside an item
     // in a fixed order (two issuing threads, one for QK and one for PV, produced rare
     // run-to-run differences):
     //   QK(0), QK(1), then for i = 0, 1, ...: QK(i + 2), PV(i).
@@ -644,7 +644,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       auto qk_step = [&](int q) -> bool {  // q = running tile count
         const int g = q & 1, k = q >> 1, sb = k % SB;
         const bool ready = wait_pair(B::full + q % NS, (q / NS) & 1, B::s_free + 2 * g + sb, ((k / SB) - 1) & 1, k >= SB);
-        if (ready && lane == 0) {
+        if (ready && elect_one()) {
           tc::fence_after_sync();
           DescWords kq = kd;
           kq.lo += (uint32_t)(q % NK) * (kImgBytes >> 4);
@@ -656,7 +656,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       auto pv_step = [&](int i) -> bool {
         const int g = i & 1;
         const bool ready = wait_pair(B::p_ready + g, (i >> 1) & 1, B::o_free + g, ((i >> 1) - 1) & 1, i >= 2);
-        if (ready && lane == 0) {
+        if (ready && elect_one()) {
           tc::fence_after_sync();
           DescWords vi = vd, pi = pd;
           vi.lo += (uint32_t)(i % NS) * (kVStageBytes >> 4);
@@ -736,21 +736,27 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
         ok &= wait_or_abort(&bars[B::o_ready + g], (q >> 1) & 1, abort_flag);
         tc::fence_after_sync();
         const uint32_t o_tmem = tmem_base + L::s_total + g * L::o_cols + lane_addr;
+        constexpr int FB = RQ < 2 ? RQ : 2;  // eight rows per round trip to TMEM
 #pragma unroll
-        for (int q4 = 0; q4 < RQ; ++q4) {
-          uint32_t d[PD][4];
+        for (int qb = 0; qb < RQ; qb += FB) {
+          uint32_t d[FB][PD][4];
 #pragma unroll
-          for (int k = 0; k < PD; ++k) tmem_ld4(o_tmem + k * NPAD + q4 * 4, d[k]);
+          for (int c = 0; c < FB; ++c)
+#pragma unroll
+            for (int k = 0; k < PD; ++k) tmem_ld4(o_tmem + k * NPAD + (qb + c) * 4, d[c][k]);
           tc::tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int n = q4 * 4 + e;
-            const float alpha_n = __shfl_sync(0xffffffffu, a_l[n >> 5], n & 31);
-            const float unit_n = __shfl_sync(0xffffffffu, unit_l[n >> 5], n & 31);
-            float o = int_to_float(d[PD - 1][e]);
+          for (int c = 0; c < FB; ++c) {
 #pragma unroll
-            for (int k = PD - 2; k >= 0; --k) o = fmaf(o, 128.f, int_to_float(d[k][e]));
-            acc[n] = fmaf(acc[n], alpha_n, o * unit_n);
+            for (int e = 0; e < 4; ++e) {
+              const int n = (qb + c) * 4 + e;
+              const float alpha_n = __shfl_sync(0xffffffffu, a_l[n >> 5], n & 31);
+              const float unit_n = __shfl_sync(0xffffffffu, unit_l[n >> 5], n & 31);
+              float o = int_to_float(d[c][PD - 1][e]);
+#pragma unroll
+              for (int k = PD - 2; k >= 0; --k) o = fmaf(o, 128.f, int_to_float(d[c][k][e]));
+              acc[n] = fmaf(acc[n], alpha_n, o * unit_n);
+            }
           }
         }
         tc::fence_before_sync();
@@ -779,20 +785,28 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
         int mykey[RL];  // warp maximum of row lane + 32 j, as an ordered integer key
 #pragma unroll
         for (int jj = 0; jj < RL; ++jj) mykey[jj] = float_key(-INFINITY);
+        // up to sixteen rows per round trip to TMEM (one wait for the batch)
+        constexpr int QB = RQ < 4 ? RQ : 4;
 #pragma unroll
-        for (int q4 = 0; q4 < RQ; ++q4) {
-          uint32_t hi[4], lo[4];
-          tmem_ld4(s_tmem + q4 * 4, hi);
-          tmem_ld4(s_tmem + NPAD + q4 * 4, lo);
+        for (int qb = 0; qb < RQ; qb += QB) {
+          uint32_t hi[QB][4], lo[QB][4];
+#pragma unroll
+          for (int c = 0; c < QB; ++c) {
+            tmem_ld4(s_tmem + (qb + c) * 4, hi[c]);
+            tmem_ld4(s_tmem + NPAD + (qb + c) * 4, lo[c]);
+          }
           tc::tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int n = q4 * 4 + e;
-            const float sv = fmaf(int_to_float(hi[e]), 256.f, int_to_float(lo[e])) * (sq[n] * mult);
-            const bool vis = interior || (pos >= rlo[n] && pos <= rhi[n]);
-            s[n] = vis ? sv : -INFINITY;
-            const int key = __reduce_max_sync(0xffffffffu, float_key(s[n]));
-            if (lane == (n & 31)) mykey[n >> 5] = key;
+          for (int c = 0; c < QB; ++c) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int n = (qb + c) * 4 + e;
+              const float sv = fmaf(int_to_float(hi[c][e]), 256.f, int_to_float(lo[c][e])) * (sq[n] * mult);
+              const bool vis = interior || (pos >= rlo[n] && pos <= rhi[n]);
+              s[n] = vis ? sv : -INFINITY;
+              const int key = __reduce_max_sync(0xffffffffu, float_key(s[n]));
+              if (lane == (n & 31)) mykey[n >> 5] = key;
+            }
           }
         }
 #pragma unroll
@@ -959,18 +973,6 @@ cudaError_t launch_cfg(const KernelParams& p, const CUtensorMap& map, int num_ct
   }
   umma_i8_attention_kernel<NPAD, PD, NS, NK, NR, SB, RQ, NP><<<num_ctas, threads_for(NP), smem, stream>>>(p, map);
   return cudaGetLastError();
-}
-
-// SMs of the current device (looked up once per device).
-int sm_count() {
-  static int cached[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
-  if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
-  int n = 0;
-  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
-  if (dev >= 0 && dev < 64) cached[dev] = n;
-  return n;
 }
 
 }  // namespace

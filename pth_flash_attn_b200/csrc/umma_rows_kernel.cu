@@ -28,6 +28,7 @@
 #include <type_traits>
 
 #include "params.cuh"
+#include "sched.cuh"
 #include "umma_rows.cuh"
 #include "page_copy.cuh"
 
@@ -61,7 +62,7 @@ struct RLayout {
   static constexpr int bars = park_l + kRGroup * 4;            // uint64 [...]
   static constexpr int n_bars = kRNS * 2 + 2 * kRNK + 6 + 2 * kRNR;
   static constexpr int misc = bars + n_bars * 8;
-  static constexpr int total = misc + 16;
+  static constexpr int total = misc + 32;
 };
 
 template <int kRNK, int kRNR>
@@ -123,8 +124,49 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
   }
   if (t.req < 0) return;
   const int rows = t.ntok * p.group;  // <= 128 by construction of bq
+  // num_splits is a bound: the pieces a request is cut into are chosen here, from the lengths,
+  // by the rule of the integer kernel (sched.cuh) - pieces of about equal length over the
+  // whole launch, so a prefill chunk among long decode requests is not cut at all.  CTAs of
+  // unused pieces leave at once; the CTA of piece 0 marks them as holding no keys.
+  int nsplits = p.num_splits;
+  if (p.num_splits > 1) {
+    unsigned long long* total_s = reinterpret_cast<unsigned long long*>(smem + L::misc + 16);
+    if (tid == 0) *total_s = 0ull;
+    __syncthreads();
+    SchedShape shape;
+    shape.group = p.group;
+    shape.num_kv_heads = p.num_kv_heads;
+    shape.bq = p.bq;
+    shape.num_splits = p.num_splits;
+    shape.window = p.window;
+    shape.causal = p.causal;
+    shape.row_class = p.row_class;
+    shape.class_rows = p.class_rows;
+    unsigned long long w = 0;
+    for (int r = tid; r < p.num_reqs; r += kRThreads) {
+      const int q0 = __ldg(p.query_start_loc + r), q1 = __ldg(p.query_start_loc + r + 1);
+      w += (unsigned long long)req_row_tiles(shape, q1 - q0) *
+           (unsigned long long)req_kv_tiles(shape, q1 - q0, __ldg(p.seq_lens + r));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) w += __shfl_xor_sync(0xffffffffu, w, o);
+    if (lane == 0 && w != 0) atomicAdd(total_s, w);
+    __syncthreads();
+    const int t_star = item_tiles(*total_s * (unsigned long long)p.num_kv_heads, p.num_sms);
+    nsplits = req_splits(req_kv_tiles(shape, t.q_len, t.seq_len), t_star, p.num_splits);
+    if (split >= nsplits) return;
+    if (split == 0) {
+      for (int i = tid; i < rows * (p.num_splits - nsplits); i += kRThreads) {
+        int token, head;
+        row_target(p, t, kvh, i % rows, &token, &head);
+        *reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.ws_lse) + (int64_t)(nsplits + i / rows) * p.ws_lse_stride_split +
+                                  (int64_t)token * p.ws_lse_stride_token + (int64_t)head * p.ws_lse_stride_head) = -INFINITY;
+      }
+    }
+    __syncthreads();  // the scratch word is part of a region the barriers are initialised in next
+  }
   int tile_begin, tile_end, range_begin, range_end;
-  split_tiles(p, t, split, &tile_begin, &tile_end, &range_begin, &range_end);
+  split_tiles(p, t, split, nsplits, &tile_begin, &tile_end, &range_begin, &range_end);
 
   if (tile_begin >= tile_end) {
     // No keys for this work item: zero output, log-sum-exp -inf.
@@ -305,10 +347,9 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
             mbar_arrive_expect_tx(bar, bs * kRawRow);
             tma_load_3d(dst, &tmap, tma_x, 0, blk, bar);
           } else {
-            const uint8_t* src = kb + (int64_t)blk * p.k.stride_block - delta;
-            const uint32_t bytes = (delta + bs * (2 * kHeadDim + 8) + 15u) & ~15u;
+            const uint32_t bytes = bs * (2 * kHeadDim + 8);  // a multiple of 16, like the run's address
             mbar_arrive_expect_tx(bar, bytes);
-            bulk_copy_g2s(dst, src, bytes, bar);
+            bulk_copy_g2s(dst, kb + (int64_t)blk * p.k.stride_block, bytes, bar);
           }
         } else {
           mbar_arrive(bar);
@@ -622,8 +663,15 @@ cudaError_t launch_umma_rows_attention(const KernelParams& p_in, cudaStream_t st
   // the query tokens into row tiles is internal to a launch.
   set_row_tile(p, 128 / p.group > 0 ? 128 / p.group : 1);
   p.raw_mode = raw_mode_for(p);
-  CUtensorMap map{};
-  if (p.raw_mode == 1 && !make_page_map(p, p.num_blocks, &map)) return cudaErrorInvalidValue;
+  p.num_sms = sm_count();
+  if (p.num_sms <= 0) return cudaErrorInvalidDevice;
+  static const CUtensorMap no_map{};
+  const CUtensorMap* mapp = &no_map;
+  if (p.raw_mode == 1) {
+    mapp = cached_page_map(p);
+    if (mapp == nullptr) return cudaErrorInvalidValue;
+  }
+  const CUtensorMap& map = *mapp;
   // Two K images and three raw half stages (64 keys each).  Consecutive QK MMAs must not read
   // their K operand from the same shared-memory addresses: with a single K image that the
   // producers rewrote between two QKs, results varied from run to run although every

@@ -147,7 +147,8 @@ def test_one_tile_per_request_flag_gives_the_same_bytes(qlens, bq, S, kernel):
 def test_mixed_launch_runs_each_request_on_its_kernel(G, S):
     """Decode, verification and prefill requests in one launch: the automatic choice serves
     the requests of at most 16 rows with the integer kernel and the others with the row-major
-    kernel, so each request's rows equal the bytes of the launch forced to that kernel."""
+    kernel, so each request's rows equal the bytes of the launch forced to that kernel (when
+    the key range is not split; pieces are chosen per launch)."""
     from tests.gpu_util import run_case
 
     qlens = [1, 40, 16 // G, 1, 300, 16 // G + 1, 1]
@@ -167,4 +168,9 @@ def test_mixed_launch_runs_each_request_on_its_kernel(G, S):
     for r, ql in enumerate(qlens):
         sl = slice(int(qsl[r]), int(qsl[r + 1]))
         want = i8 if ql * G <= 16 else rows
-        assert (auto["out_bytes"][sl] == want["out_bytes"][sl]).all(), (r, ql)
+        if S == 1:
+            assert (auto["out_bytes"][sl] == want["out_bytes"][sl]).all(), (r, ql)
+        else:
+            # the kernels cut a request into pieces by the total work of the requests THEY serve,
+            # which differs between the mixed launch and a launch forced to one kernel
+            check_out(auto["out"][sl], want["out"][sl], max_tol=1e-2, mean_tol=1e-3, what=f"request {r}")
