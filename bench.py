@@ -127,7 +127,14 @@ class DeviceLaunch:
         need, width = sum(nblk), max(nblk)
         q_max = max(qlens)
         is_prefill = bool(launch.get("prefill", False))
-        w_ts = planner.workspace_token_splits(max_num_seqs=R, q_dec_max=q_max, Hkv=hkv, D=D, num_sms=num_sms)
+        if not is_prefill:
+            w_ts = planner.workspace_token_splits(max_num_seqs=R, q_dec_max=q_max, Hkv=hkv, D=D, num_sms=num_sms)
+        elif min(qlens) < max(qlens):
+            # a mixed batch in ONE launch: its decode requests only balance if they may be cut, so
+            # this caller reserves partials for the whole launch (8 pieces x T tokens)
+            w_ts = 8 * T
+        else:
+            w_ts = 0  # prefill chunks alone are never cut
         plan = planner.plan_launch(num_tokens=T, num_reqs=R, max_query_len=q_max, G=self.G, Hkv=hkv, D=D,
                                    num_sms=num_sms, is_prefill=is_prefill, ws_token_splits=w_ts,
                                    window=self.window)

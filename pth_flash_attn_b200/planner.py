@@ -205,9 +205,13 @@ def plan_launch(
 
     tile_tokens = max_tokens_per_tile(group)
     if is_prefill:
-        # chunks of any length: full 64-row tiles over all tokens
+        # Chunks of any length: full 64-row tiles over all tokens.  The bound on the pieces
+        # counts REQUESTS, not row tiles: a prefill launch may hold long decode requests of
+        # very different lengths (a mixed batch in one launch), which only balance when they
+        # may be cut.  The kernels cut on the device and leave the prefill chunks whole, and
+        # the bound only matters to a caller that reserved S * T token-splits for such launches.
         wm = max(WM_CHOICES)
-        row_tiles = _ceil_div(tokens, tile_tokens)
+        row_tiles = _ceil_div(requests, 2)
     else:
         # every request may be as long as the longest: the fewest tiles that hold it,
         # then the lowest tile that holds its share

@@ -81,8 +81,12 @@ def test_baseline_shapes():
     tight = _plan(num_tokens=1, num_reqs=1, window=200)
     assert tight.num_splits == -(-(200 + 1 - 2) // planner.KV_TILE_TOKENS) + 1 == 3
     # prefill
-    pf = _plan(num_tokens=8192, num_reqs=4, max_query_len=2048, G=8, is_prefill=True)
+    # prefill: full tiles; cut only if the caller reserved partials for the whole launch (the
+    # bound then counts requests, which may be long decode requests inside a mixed launch)
+    pf = _plan(num_tokens=8192, num_reqs=4, max_query_len=2048, G=8, is_prefill=True, ws_token_splits=4096)
     assert pf.wm == 4 and pf.bq == 8 and pf.num_splits == 1
+    mixed = _plan(num_tokens=2128, num_reqs=58, max_query_len=1024, G=8, is_prefill=True, ws_token_splits=8 * 2128)
+    assert mixed.num_splits == 6 and mixed.num_splits * mixed.num_tokens <= 8 * 2128
     # no reservation, no split
     assert _plan(num_tokens=1, num_reqs=1, ws_token_splits=0).num_splits == 1
 
