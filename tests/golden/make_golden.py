@@ -30,7 +30,8 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
-REFERENCE = Path(os.environ.get("REFERENCE", "/root/reference"))
+# the reference checkout: $REFERENCE, else a directory `reference` next to this repository
+REFERENCE = Path(os.environ.get("REFERENCE", Path(__file__).resolve().parents[3] / "reference"))
 sys.path.insert(0, str(REFERENCE / "python"))
 
 from pth_testing import ref_capi  # noqa: E402

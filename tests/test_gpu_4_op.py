@@ -137,3 +137,47 @@ def test_graph_replay_with_lengths_rewritten_in_place():
         if first is None:
             first = replayed
     assert not torch.equal(first.view(torch.int16), replayed.view(torch.int16)), "stale lengths would pass"
+
+
+def test_op_does_not_synchronise_or_allocate():
+    """The op reads no device data on the host and allocates nothing (the reference pins both:
+    tests/gpu/test_backend_impl.py:149-190): with the sync debug mode set to "error" a hidden
+    synchronisation raises, and the allocator's counters do not move across the calls."""
+    for qlens, S in (([1, 1, 1], 3), ([4, 4, 4], 1), ([40, 3, 1], 2)):
+        t = _setup([3000, 700, 129], qlens)
+        wm, S, ws_o, ws_lse = _plan(t, S)
+        out = torch.zeros((t["T"], t["Hq"], t["D"]), dtype=torch.bfloat16, device="cuda")
+        _call(t, out, wm, S, ws_o, ws_lse)   # first call: kernel attributes, page map
+        torch.cuda.synchronize()
+        before = torch.cuda.memory_stats()
+        torch.cuda.set_sync_debug_mode("error")
+        try:
+            for _ in range(3):
+                _call(t, out, wm, S, ws_o, ws_lse)
+        finally:
+            torch.cuda.set_sync_debug_mode("default")
+        torch.cuda.synchronize()
+        after = torch.cuda.memory_stats()
+        for key in ("allocation.all.allocated", "allocated_bytes.all.allocated", "segment.all.allocated",
+                    "reserved_bytes.all.allocated"):
+            assert after[key] == before[key], key
+        ref = orc.ref_attention_paged(t["q_f32"], t["c"], t["qsl_np"], t["scale"])
+        check_out(out.float().cpu().numpy(), ref.out, what=f"q {qlens} S {S}")
+
+
+@pytest.mark.parametrize("qlens,S", [([1, 1, 1], 1), ([4, 4, 2], 3), ([16, 9], 2)])
+def test_fp16_queries_and_output(qlens, S):
+    """fp16 q / out through the op: the integer kernel turns the queries into int8 digits
+    whatever their 16-bit format is."""
+    lens = [2500, 300, 77][:len(qlens)]
+    t = _setup(lens, qlens)
+    q16 = torch.from_numpy(t["q_f32"]).cuda().to(torch.float16)
+    t["q"] = q16
+    wm, S, ws_o, ws_lse = _plan(t, S)
+    out = torch.full((t["T"], t["Hq"], t["D"]), float("nan"), dtype=torch.float16, device="cuda")
+    _call(t, out, wm, S, ws_o, ws_lse)
+    torch.cuda.synchronize()
+    ref = orc.ref_attention_paged(q16.float().cpu().numpy(), t["c"], t["qsl_np"], t["scale"])
+    check_out(out.float().cpu().numpy(), ref.out, what=f"fp16 q {qlens} S {S}")
+    from pth_flash_attn_b200 import capi
+    assert capi.load_library().device_status() == 0

@@ -45,7 +45,7 @@ def test_schema_is_frozen():
     want = ("pth_flash_attn::" + ops.OP_SCHEMA).replace("Tensor! ", "Tensor(a!) ")
     norm = lambda s: re.sub(r"Tensor\([^)]*![^)]*\)", "Tensor!", str(s)).replace(" ", "")  # noqa: E731
     assert norm(schema) == norm("pth_flash_attn::" + ops.OP_SCHEMA)
-    assert want  # the textual schema is also what INTEGRATION.md documents
+    assert want  # the textual schema is part of the documented integration contract
 
 
 def test_valid_cpu_call_refuses_to_compute():
