@@ -229,6 +229,43 @@ int32_t pthb200_combine_ex(const PthAttnCombineArgs* args, const PthB200Options*
  * Results are those of pthb200_attention + pthb200_combine with a dense workspace. */
 int32_t pthb200_attention_noalloc(const PthAttnArgs* args, void* stream);
 
+/* ---- quantising cache writer --------------------------------------------------
+ * The step in front of the attention path: stores the K and V rows of new tokens in the
+ * cache's int8_per_token_head form.  It stands where vLLM's own per-token-head writer stands
+ * for the reference (the reference calls it at python/pth_testing/reference.py:301-307 and
+ * 461-473, and inherits it in production, python/pth_flash_attn/vllm_backend.py:10-14); the
+ * arithmetic is the one the reference documents and mirrors (docs/integration.md:73-117,
+ * python/pth_testing/reference.py:76-103), bit for bit:
+ *   scale = max(absmax / 127, 1e-6);  q = clamp(trunc(x * (1 / scale) +- 0.5), -128, 127).
+ * key / value: [num_tokens, num_kv_heads, head_size] of src_dtype (F32, F16 or BF16), byte
+ * strides given, rows contiguous.  The four streams are the ones PthAttnArgs describes (the
+ * data pointers are written through).  slot_mapping [num_tokens] int64: slot = block *
+ * block_size + position; a negative value skips the token. */
+typedef struct PthB200WriteArgs {
+  int32_t abi_version;  /* PTH_ATTN_ABI_VERSION */
+  int32_t struct_bytes; /* sizeof(PthB200WriteArgs) of the caller */
+  const void* key;
+  const void* value;
+  int32_t src_dtype;
+  int64_t key_stride_token;
+  int64_t key_stride_head;
+  int64_t value_stride_token;
+  int64_t value_stride_head;
+  PthAttnStream k_cache;
+  PthAttnStream v_cache;
+  PthAttnStream k_scale;
+  PthAttnStream v_scale;
+  int32_t num_blocks;
+  int32_t block_size;
+  int32_t num_kv_heads;
+  int32_t head_size; /* 64, 128 or 256 */
+  int32_t num_tokens;
+  const int64_t* slot_mapping;
+} PthB200WriteArgs;
+int32_t pthb200_write_args_bytes(void);
+/* Enqueue the writer on `stream`.  No allocation, no synchronisation. */
+int32_t pthb200_write_kv(const PthB200WriteArgs* args, void* stream);
+
 /* Host-only helpers of the op layer (no device access).
  * pthb200_tile_tokens: query tokens per row tile for a launch planned with `wm`
  * (1, 2 or 4), group size G and host bound max_query_len; returns -1 if wm is

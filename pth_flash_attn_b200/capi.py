@@ -102,6 +102,30 @@ class PthAttnCombineArgs(ctypes.Structure):
     ]
 
 
+class PthB200WriteArgs(ctypes.Structure):
+    _fields_ = [
+        ("abi_version", ctypes.c_int32),
+        ("struct_bytes", ctypes.c_int32),
+        ("key", ctypes.c_void_p),
+        ("value", ctypes.c_void_p),
+        ("src_dtype", ctypes.c_int32),
+        ("key_stride_token", ctypes.c_int64),
+        ("key_stride_head", ctypes.c_int64),
+        ("value_stride_token", ctypes.c_int64),
+        ("value_stride_head", ctypes.c_int64),
+        ("k_cache", PthAttnStream),
+        ("v_cache", PthAttnStream),
+        ("k_scale", PthAttnStream),
+        ("v_scale", PthAttnStream),
+        ("num_blocks", ctypes.c_int32),
+        ("block_size", ctypes.c_int32),
+        ("num_kv_heads", ctypes.c_int32),
+        ("head_size", ctypes.c_int32),
+        ("num_tokens", ctypes.c_int32),
+        ("slot_mapping", ctypes.c_void_p),
+    ]
+
+
 class PthB200Options(ctypes.Structure):
     _fields_ = [
         ("abi_version", ctypes.c_int32),
@@ -127,6 +151,8 @@ EXPORTED_SYMBOLS = (
     "pthb200_combine",
     "pthb200_combine_ex",
     "pthb200_attention_noalloc",
+    "pthb200_write_args_bytes",
+    "pthb200_write_kv",
     "pthb200_tile_tokens",
     "pthb200_check_call",
     "pthb200_launch_count",
@@ -180,6 +206,10 @@ class B200Lib:
         lib.pthb200_launch_count.restype = ctypes.c_int32
         lib.pthb200_launch_count.argtypes = [ap, ctypes.POINTER(ctypes.c_int32),
                                              ctypes.POINTER(ctypes.c_int32)]
+        lib.pthb200_write_args_bytes.restype = ctypes.c_int32
+        lib.pthb200_write_args_bytes.argtypes = []
+        lib.pthb200_write_kv.restype = ctypes.c_int32
+        lib.pthb200_write_kv.argtypes = [ctypes.POINTER(PthB200WriteArgs), ctypes.c_void_p]
         lib.pthb200_test_schedule.restype = ctypes.c_int32
         lib.pthb200_test_schedule.argtypes = ([ctypes.c_void_p] * 2 + [ctypes.c_int32] * 10
                                               + [ctypes.c_void_p, ctypes.c_int32])
@@ -197,6 +227,8 @@ class B200Lib:
             raise RuntimeError(f"{path}: PthAttnArgs size differs from the ctypes mirror")
         if lib.pthb200_combine_args_bytes() != ctypes.sizeof(PthAttnCombineArgs):
             raise RuntimeError(f"{path}: PthAttnCombineArgs size differs from the ctypes mirror")
+        if lib.pthb200_write_args_bytes() != ctypes.sizeof(PthB200WriteArgs):
+            raise RuntimeError(f"{path}: PthB200WriteArgs size differs from the ctypes mirror")
         if lib.pthb200_options_bytes() != ctypes.sizeof(PthB200Options):
             raise RuntimeError(f"{path}: PthB200Options size differs from the ctypes mirror")
 
@@ -223,6 +255,10 @@ class B200Lib:
             return int(self.lib.pthb200_combine(ctypes.byref(args), stream or None))
         return int(self.lib.pthb200_combine_ex(ctypes.byref(args), ctypes.byref(options),
                                                stream or None))
+
+    def write_kv(self, args: "PthB200WriteArgs", *, stream: int = 0) -> int:
+        """Quantise and store the K / V rows of new tokens (the cache writer)."""
+        return int(self.lib.pthb200_write_kv(ctypes.byref(args), stream or None))
 
     def tile_tokens(self, wm: int, group: int, max_query_len: int) -> int:
         return int(self.lib.pthb200_tile_tokens(wm, group, max_query_len))
@@ -291,6 +327,13 @@ def new_attn_args() -> PthAttnArgs:
     a = PthAttnArgs()
     a.abi_version = ABI_VERSION
     a.struct_bytes = ctypes.sizeof(PthAttnArgs)
+    return a
+
+
+def new_write_args() -> PthB200WriteArgs:
+    a = PthB200WriteArgs()
+    a.abi_version = ABI_VERSION
+    a.struct_bytes = ctypes.sizeof(PthB200WriteArgs)
     return a
 
 

@@ -349,6 +349,37 @@ int32_t pthb200_launch_count(const PthAttnArgs* args, int32_t* attention_kernels
   return PTH_ATTN_OK;
 }
 
+int32_t pthb200_write_args_bytes(void) { return (int32_t)sizeof(PthB200WriteArgs); }
+
+int32_t pthb200_write_kv(const PthB200WriteArgs* a, void* stream) {
+  using namespace pthb200;
+  g_last_error.clear();
+  PTHB_REQUIRE(a != nullptr, "args is NULL");
+  PTHB_REQUIRE(a->abi_version == PTH_ATTN_ABI_VERSION, "args.abi_version does not match the library");
+  PTHB_REQUIRE(a->struct_bytes == (int32_t)sizeof(PthB200WriteArgs), "args.struct_bytes != sizeof(PthB200WriteArgs)");
+  PTHB_REQUIRE(is_head_size(a->head_size), "head_size must be 64, 128 or 256");
+  PTHB_REQUIRE(a->num_kv_heads >= 1 && a->block_size >= 1 && a->num_blocks >= 1, "num_kv_heads, block_size and num_blocks must be >= 1");
+  PTHB_REQUIRE(a->num_tokens >= 0, "num_tokens must be >= 0");
+  PTHB_REQUIRE(a->src_dtype == PTH_ATTN_F32 || a->src_dtype == PTH_ATTN_F16 || a->src_dtype == PTH_ATTN_BF16,
+               "src_dtype must be F32, F16 or BF16");
+  if (a->num_tokens == 0) return PTH_ATTN_OK;
+  PTHB_REQUIRE(a->key != nullptr && a->value != nullptr && a->slot_mapping != nullptr,
+               "key, value and slot_mapping must not be NULL");
+  const int64_t elem = a->src_dtype == PTH_ATTN_F32 ? 4 : 2;
+  PTHB_REQUIRE(aligned(a->key, elem) && aligned(a->value, elem) && a->key_stride_token % elem == 0 &&
+                   a->key_stride_head % elem == 0 && a->value_stride_token % elem == 0 &&
+                   a->value_stride_head % elem == 0,
+               "key / value must be aligned to their element size");
+  PTHB_REQUIRE(aligned(a->slot_mapping, 8), "slot_mapping must be 8-byte aligned");
+  if (int32_t rc = check_stream(a->k_cache, "k_cache")) return rc;
+  if (int32_t rc = check_stream(a->v_cache, "v_cache")) return rc;
+  if (int32_t rc = check_stream(a->k_scale, "k_scale")) return rc;
+  if (int32_t rc = check_stream(a->v_scale, "v_scale")) return rc;
+  const cudaError_t err = launch_kv_writer(*a, static_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) return fail(PTH_ATTN_ECUDA, std::string("writer launch failed: ") + cudaGetErrorString(err));
+  return PTH_ATTN_OK;
+}
+
 // Host restatement of the persistent kernel's work-item schedule, built from the same
 // functions the device runs (sched.cuh): the items each of `num_ctas` CTAs would run, in
 // the order it would run them.

@@ -115,3 +115,26 @@ def attention_forward(q, out, cache: CacheViews, block_table, seq_lens, query_st
             rc = lib.combine(fill_combine_args(a), options=opt, stream=stream)
             if rc != capi.OK:
                 raise RuntimeError(f"pthb200_combine: {lib.last_error()} (code {rc})")
+
+
+def write_kv(key, value, cache: CacheViews, slot_mapping, *, lib: capi.B200Lib | None = None) -> None:
+    """Quantise ``key`` / ``value`` ``[T, Hkv, D]`` into the cache at ``slot_mapping`` (int64 ``[T]``;
+    negative = skip) on the current stream, exactly as the cache format's own writer does."""
+    lib = lib or capi.load_library()
+    a = capi.new_write_args()
+    es = key.element_size()
+    a.key, a.value, a.src_dtype = key.data_ptr(), value.data_ptr(), _DTYPE_CODE[key.dtype]
+    a.key_stride_token, a.key_stride_head = key.stride(0) * es, key.stride(1) * es
+    a.value_stride_token, a.value_stride_head = value.stride(0) * es, value.stride(1) * es
+    _set_stream(a.k_cache, cache.k)
+    _set_stream(a.v_cache, cache.v)
+    _set_stream(a.k_scale, cache.ks)
+    _set_stream(a.v_scale, cache.vs)
+    a.num_blocks, a.block_size = cache.num_blocks, cache.block_size
+    a.num_kv_heads, a.head_size = cache.num_kv_heads, cache.head_size
+    a.num_tokens = key.shape[0]
+    a.slot_mapping = slot_mapping.data_ptr()
+    with torch.cuda.device(key.device):
+        rc = lib.write_kv(a, stream=torch.cuda.current_stream(key.device).cuda_stream)
+    if rc != capi.OK:
+        raise RuntimeError(f"pthb200_write_kv: {lib.last_error()} (code {rc})")
