@@ -240,6 +240,15 @@ class DeviceLaunch:
         if rc != 0:
             raise RuntimeError(lib.last_error())
 
+    def launch_copy_ceiling(self, which=0):
+        """The paged-copy ceiling of this launch (same bytes, same copies, no compute)."""
+        from pth_flash_attn_b200 import capi
+
+        lib = capi.load_library()
+        rc = lib.copy_ceiling(self._args(which), stream=self.torch.cuda.current_stream().cuda_stream)
+        if rc != 0:
+            raise RuntimeError(lib.last_error())
+
     def e2e_pass(self, which=0):
         """Host buffers in, host buffer out: ONE pinned H2D copy of the call's inputs (queries,
         block table, lengths), the launch, D2H of out."""
@@ -311,9 +320,16 @@ class Workload:
         for d in self.dls:  # one eager pass: sets kernel attributes, builds the page maps
             d.launch(0)
         torch.cuda.synchronize()
+        # the copy ceiling follows the integer kernel: only where that kernel serves the whole launch
+        self.has_copy_ceiling = all(d.attention_kernels == 1 and d.bq * d.G <= 16 for d in self.dls)
         if graphs:
             self.graphs = self._capture(lambda d, s: d.launch(s))
             self.attn_graphs = self._capture(lambda d, s: d.launch_attention_only(s))
+            if self.has_copy_ceiling:
+                for d in self.dls:
+                    d.launch_copy_ceiling(0)
+                torch.cuda.synchronize()
+                self.copy_graphs = self._capture(lambda d, s: d.launch_copy_ceiling(s))
 
     def _capture(self, fn):
         torch = self.torch
@@ -333,6 +349,9 @@ class Workload:
 
     def run_attention(self, i):
         self.attn_graphs[i % self.num_sets].replay()
+
+    def run_copy_ceiling(self, i):
+        self.copy_graphs[i % self.num_sets].replay()
 
     def run_e2e(self, i):
         for d in self.dls:
@@ -569,6 +588,16 @@ class Timer:
                     spread={"min": per[0], "median": per[len(per) // 2], "max": per[-1]})
 
 
+def copy_ceiling_of(wl, timer, attn_ms):
+    """Time of the paged-copy ceiling of the workload and eta_mem = T_copy / T_attention."""
+    if not wl.has_copy_ceiling:
+        return None
+    pps = timer.passes_per_step(wl.run_copy_ceiling, 5, 0.2)
+    ms = timer.timed(wl.run_copy_ceiling, 5, 3, pps)["ms_per_pass"]
+    return {"ms_per_pass": ms, "gbs": wl.bytes_local / (ms * 1e-3) / 1e9, "eta_mem": ms / attn_ms,
+            "what": "same bytes, same persistent CTAs, schedule and TMA page copies as the attention kernel, no compute"}
+
+
 def roofline_of(wl, world, attn_ms, pass_ms, hbm_peak, tc_peak, tc_sustained, peak_src):
     """The roofline block of a workload on this rank: achieved = algorithmic bytes (flops) of
     the rank's shard over the time of its attention kernels alone."""
@@ -589,7 +618,9 @@ def roofline_of(wl, world, attn_ms, pass_ms, hbm_peak, tc_peak, tc_sustained, pe
                 "frac": bound_ms / attn_ms, "tflops": tfs, "bound_ms": bound_ms, "traffic": None,
                 "kernel": "umma_i8_attention_kernel + umma_rows_attention_kernel"}
     else:
-        rows_kernel = all(d.attention_kernels == 1 and d.bq * d.G > 16 for d in wl.dls)
+        # tall row tiles whose requests are all tall run on the row-major kernel (the integer
+        # kernel of the pair finds nothing to do)
+        rows_kernel = all(d.bq * d.G > 16 and min(d.launch_spec["q_lens"]) * d.G > 16 for d in wl.dls)
         roof = {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
                 "traffic": None if rows_kernel else DRAM_BYTES_PER_ALGORITHMIC_BYTE * wl.bytes_local,
                 "kernel": "umma_rows_attention_kernel" if rows_kernel else "umma_i8_attention_kernel"}
@@ -690,6 +721,7 @@ def main():
     lat_ms = timer.max_over_ranks(float(np.median(lat[5:])))
 
     roof = roofline_of(wl, world, attn_ms, ms_pass, hbm_peak, tc_peak, tc_sustained, peak_src)
+    roof["copy_ceiling"] = copy_ceiling_of(wl, timer, attn_ms)
     parity = wl.parity()
     tensor_headline = args.config in TENSOR_BOUND
     line = {
@@ -739,12 +771,15 @@ def main():
             p2 = timer.passes_per_step(w.run_attention, 5, 0.2)
             a_ms = min(timer.timed(w.run_attention, 5, 3, p2)["ms_per_pass"], t["ms_per_pass"])
             r = roofline_of(w, world, a_ms, t["ms_per_pass"], hbm_peak, tc_peak, tc_sustained, peak_src)
+            ceiling = copy_ceiling_of(w, timer, a_ms)
             par = w.parity()
             per[name] = {"ms_per_pass": t["ms_per_pass"], "us_per_layer": t["ms_per_pass"] * 1e3,
                          "kv_gbs": w.bytes_total / (t["ms_per_pass"] * 1e-3) / 1e9,
                          "tflops": w.flops_total / (t["ms_per_pass"] * 1e-3) / 1e12,
                          "roofline_frac": r["frac"], "bound": r["bound"], "unit": r["unit"], "achieved": r["achieved"],
                          "peak": r["peak"], "kernel": r["kernel"], "kernel_ms_per_pass": a_ms,
+                         "eta_mem": ceiling["eta_mem"] if ceiling else None,
+                         "copy_ceiling_gbs": ceiling["gbs"] if ceiling else None,
                          "launches": w.describe(), "l2_sets": w.num_sets, "gpu_launches_per_pass": w.kernels_per_pass,
                          "parity_checked": par["within_tolerance"], "parity": par}
             del w

@@ -229,6 +229,16 @@ int32_t pthb200_combine_ex(const PthAttnCombineArgs* args, const PthB200Options*
  * Results are those of pthb200_attention + pthb200_combine with a dense workspace. */
 int32_t pthb200_attention_noalloc(const PthAttnArgs* args, void* stream);
 
+/* ---- paged-copy ceiling ---------------------------------------------------------
+ * Enqueues a kernel that fetches exactly the cache bytes pthb200_attention would fetch for
+ * these arguments on the integer kernel - same persistent CTAs, same work-item schedule,
+ * same TMA page copies into the same three-stage ring - and discards them.  Its time is the
+ * memory-side floor of the attention launch: eta_mem = T_copy / T_attention, the measure the
+ * reference reports against its own copy-ceiling program (bench/sol_copy.cu:424-512,
+ * docs/benchmark-methodology.md:60-63).  Writes nothing.  PTH_ATTN_EINVAL where the integer
+ * kernel does not apply. */
+int32_t pthb200_copy_ceiling(const PthAttnArgs* args, void* stream);
+
 /* ---- quantising cache writer --------------------------------------------------
  * The step in front of the attention path: stores the K and V rows of new tokens in the
  * cache's int8_per_token_head form.  It stands where vLLM's own per-token-head writer stands

@@ -151,6 +151,7 @@ EXPORTED_SYMBOLS = (
     "pthb200_combine",
     "pthb200_combine_ex",
     "pthb200_attention_noalloc",
+    "pthb200_copy_ceiling",
     "pthb200_write_args_bytes",
     "pthb200_write_kv",
     "pthb200_tile_tokens",
@@ -206,6 +207,8 @@ class B200Lib:
         lib.pthb200_launch_count.restype = ctypes.c_int32
         lib.pthb200_launch_count.argtypes = [ap, ctypes.POINTER(ctypes.c_int32),
                                              ctypes.POINTER(ctypes.c_int32)]
+        lib.pthb200_copy_ceiling.restype = ctypes.c_int32
+        lib.pthb200_copy_ceiling.argtypes = [ap, ctypes.c_void_p]
         lib.pthb200_write_args_bytes.restype = ctypes.c_int32
         lib.pthb200_write_args_bytes.argtypes = []
         lib.pthb200_write_kv.restype = ctypes.c_int32
@@ -255,6 +258,10 @@ class B200Lib:
             return int(self.lib.pthb200_combine(ctypes.byref(args), stream or None))
         return int(self.lib.pthb200_combine_ex(ctypes.byref(args), ctypes.byref(options),
                                                stream or None))
+
+    def copy_ceiling(self, args: PthAttnArgs, *, stream: int = 0) -> int:
+        """The paged-copy ceiling of an attention launch: same bytes, same copies, no compute."""
+        return int(self.lib.pthb200_copy_ceiling(ctypes.byref(args), stream or None))
 
     def write_kv(self, args: "PthB200WriteArgs", *, stream: int = 0) -> int:
         """Quantise and store the K / V rows of new tokens (the cache writer)."""

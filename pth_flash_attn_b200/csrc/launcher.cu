@@ -349,6 +349,18 @@ int32_t pthb200_launch_count(const PthAttnArgs* args, int32_t* attention_kernels
   return PTH_ATTN_OK;
 }
 
+int32_t pthb200_copy_ceiling(const PthAttnArgs* args, void* stream) {
+  using namespace pthb200;
+  g_last_error.clear();
+  KernelParams p;
+  if (int32_t rc = build_attention(args, nullptr, &p)) return rc;
+  const char* why = "";
+  PTHB_REQUIRE(umma_i8_supports(p, &why), std::string("the paged-copy ceiling follows the integer kernel, which does not apply: ") + why);
+  const cudaError_t err = launch_copy_ceiling(p, static_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) return fail(PTH_ATTN_ECUDA, std::string("copy launch failed: ") + cudaGetErrorString(err));
+  return PTH_ATTN_OK;
+}
+
 int32_t pthb200_write_args_bytes(void) { return (int32_t)sizeof(PthB200WriteArgs); }
 
 int32_t pthb200_write_kv(const PthB200WriteArgs* a, void* stream) {
