@@ -7,10 +7,11 @@
 //
 // The order of the sums depends on the number of splits S alone, never on the
 // number of rows or on timing.  Up to kWideSplits splits, one warp owns a row
-// and sums s = 0..S-1.  Above, one CTA owns a row: its four warps sum the four
-// contiguous quarters of the splits (each in ascending order) and warp 0 adds
-// the quarter sums in the order 0, 1, 2, 3 -- a launch with many splits has few
-// rows, and one warp walking 100+ dependent rows of partials is pure latency.
+// and sums s = 0..S-1.  Above, one CTA owns a row: its warps (4, or 16 beyond
+// kVeryWideSplits) sum contiguous runs of the splits (each in ascending order)
+// and warp 0 adds the run sums in ascending order -- a launch with many splits
+// has few rows, and one warp walking 100+ dependent rows of partials is pure
+// latency.
 //
 // A split with lse = -inf is skipped BEFORE its ws_o row is read, so garbage
 // (NaN included) in the partial of an empty split never reaches the output.
@@ -26,7 +27,8 @@ namespace {
 
 constexpr int kThreads = 128;
 constexpr int kWarps = kThreads / 32;
-constexpr int kWideSplits = 16;  // more splits than this: one CTA per row
+constexpr int kWideSplits = 16;      // more splits than this: one CTA of 4 warps per row
+constexpr int kVeryWideSplits = 64;  // more than this: one CTA of 16 warps per row
 constexpr int kBatch = 8;        // partial rows loaded before their sums start
 
 template <int D>
@@ -82,9 +84,11 @@ __device__ __forceinline__ void sum_splits(const CombineParams& p, const uint8_t
   }
 }
 
-// kWide: one CTA per row (four warps, a quarter of the splits each); else one warp per row.
-template <int D, bool kWide>
-__global__ void __launch_bounds__(kThreads) combine_kernel(const __grid_constant__ CombineParams p) {
+// kWideWarps > 0: one CTA of kWideWarps warps per row (a run of the splits each); else one warp per row.
+template <int D, int kWideWarps>
+__global__ void __launch_bounds__(kWideWarps > 0 ? kWideWarps * 32 : kThreads)
+combine_kernel(const __grid_constant__ CombineParams p) {
+  constexpr bool kWide = kWideWarps > 0;
   constexpr int kCols = RowSum<D>::kCols;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row = kWide ? (int64_t)blockIdx.x : (int64_t)blockIdx.x * kWarps + warp;
@@ -117,8 +121,9 @@ __global__ void __launch_bounds__(kThreads) combine_kernel(const __grid_constant
 
   // Pass 2: every lane walks the same sequence of splits, so the sums are identical across lanes.
   if (kWide) {
-    __shared__ float part[kWarps - 1][kCols * 4 + 1][32];
-    const int quarter = (S + kWarps - 1) / kWarps;
+    constexpr int kRunWarps = kWide ? kWideWarps : 1;
+    __shared__ float part[kRunWarps > 1 ? kRunWarps - 1 : 1][kCols * 4 + 1][32];
+    const int quarter = (S + kRunWarps - 1) / kRunWarps;
     if (mx > -INFINITY) sum_splits<D>(p, lse_base, o_base, mx, min(S, warp * quarter), min(S, (warp + 1) * quarter), lane, r);
     if (warp > 0) {
 #pragma unroll
@@ -130,7 +135,7 @@ __global__ void __launch_bounds__(kThreads) combine_kernel(const __grid_constant
     __syncthreads();
     if (warp > 0) return;
 #pragma unroll
-    for (int w = 0; w < kWarps - 1; ++w) {
+    for (int w = 0; w < kRunWarps - 1; ++w) {
 #pragma unroll
       for (int c = 0; c < kCols; ++c)
 #pragma unroll
@@ -178,13 +183,15 @@ __global__ void __launch_bounds__(kThreads) combine_kernel(const __grid_constant
 
 cudaError_t launch_combine_kernel(const CombineParams& p, cudaStream_t stream) {
   const int64_t rows = (int64_t)p.num_tokens * p.num_q_heads;
-  const bool wide = p.num_splits > kWideSplits;
-  const unsigned grid = wide ? (unsigned)rows : (unsigned)((rows + kWarps - 1) / kWarps);
-#define PTHB200_COMBINE(D_)                                          \
-  if (wide)                                                          \
-    combine_kernel<D_, true><<<grid, kThreads, 0, stream>>>(p);      \
-  else                                                               \
-    combine_kernel<D_, false><<<grid, kThreads, 0, stream>>>(p)
+  const int wide_warps = p.num_splits > kVeryWideSplits ? 16 : p.num_splits > kWideSplits ? 4 : 0;
+  const unsigned grid = wide_warps > 0 ? (unsigned)rows : (unsigned)((rows + kWarps - 1) / kWarps);
+#define PTHB200_COMBINE(D_)                                                  \
+  if (wide_warps == 16)                                                      \
+    combine_kernel<D_, 16><<<grid, 16 * 32, 0, stream>>>(p);                 \
+  else if (wide_warps == 4)                                                  \
+    combine_kernel<D_, 4><<<grid, 4 * 32, 0, stream>>>(p);                   \
+  else                                                                       \
+    combine_kernel<D_, 0><<<grid, kThreads, 0, stream>>>(p)
   switch (p.head_size) {
     case 64:
       PTHB200_COMBINE(64);
