@@ -187,6 +187,14 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
   shape.class_rows = p.class_rows;
 
   // ---- set-up by all threads -------------------------------------------------
+  // (the loads of the total-work pass below are issued first: their latency hides behind the
+  // barrier initialisation and the TMEM allocation)
+  unsigned long long work = 0;
+  for (int r = tid; r < p.num_reqs; r += kThreads) {
+    const int q0 = __ldg(p.query_start_loc + r), q1 = __ldg(p.query_start_loc + r + 1);
+    const int len = __ldg(p.seq_lens + r);
+    work += (unsigned long long)req_row_tiles(shape, q1 - q0) * (unsigned long long)req_kv_tiles(shape, q1 - q0, len);
+  }
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
       tc::mbar_init(&bars[B::full + s], kProducerThreads);
@@ -220,12 +228,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
   __syncthreads();
   {
     // total work of the launch in KV tiles (every CTA computes the same number)
-    unsigned long long w = 0;
-    for (int r = tid; r < p.num_reqs; r += kThreads) {
-      const int q0 = __ldg(p.query_start_loc + r), q1 = __ldg(p.query_start_loc + r + 1);
-      const int len = __ldg(p.seq_lens + r);
-      w += (unsigned long long)req_row_tiles(shape, q1 - q0) * (unsigned long long)req_kv_tiles(shape, q1 - q0, len);
-    }
+    unsigned long long w = work;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) w += __shfl_xor_sync(0xffffffffu, w, o);
     if (lane == 0 && w != 0) atomicAdd(total_s, w);
@@ -305,11 +308,15 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
         return reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.ws_lse) + (int64_t)s * p.ws_lse_stride_split +
                                         (int64_t)token * p.ws_lse_stride_token + (int64_t)head * p.ws_lse_stride_head);
       };
-      if (c.split == 0 && S > splits) {
-        // splits this request does not use: no keys
-        for (int i = lane; i < rows * (S - splits); i += 32) *lse_slot(splits + i / rows, i % rows) = -INFINITY;
-      }
+      // splits this request does not use hold no keys: marked by the CTA of split 0, once its
+      // item has been handed to the other roles (the marks are off their critical path)
+      auto mark_unused_splits = [&]() {
+        if (c.split == 0 && S > splits) {
+          for (int i = lane; i < rows * (S - splits); i += 32) *lse_slot(splits + i / rows, i % rows) = -INFINITY;
+        }
+      };
       if (tile_begin >= tile_end) {
+        mark_unused_splits();
         // No keys for this item: zero output, log-sum-exp -inf.
         if (S == 1) {
           for (int i = lane; i < rows * kHeadDimI8; i += 32) {
@@ -415,6 +422,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       tc::fence_async_smem();
       mbar_arrive(&bars[B::item_full + slot]);
       ++pub;
+      mark_unused_splits();
     }
     // no more items for this CTA
     {

@@ -174,3 +174,27 @@ def test_mixed_launch_runs_each_request_on_its_kernel(G, S):
             # the kernels cut a request into pieces by the total work of the requests THEY serve,
             # which differs between the mixed launch and a launch forced to one kernel
             check_out(auto["out"][sl], want["out"][sl], max_tol=1e-2, mean_tol=1e-3, what=f"request {r}")
+
+
+@pytest.mark.parametrize("bs,kernel", [(32, capi.KERNEL_UMMA), (64, capi.KERNEL_UMMA), (128, capi.KERNEL_UMMA),
+                                       (32, capi.KERNEL_UMMA_ROWS), (64, capi.KERNEL_UMMA_ROWS),
+                                       (48, capi.KERNEL_AUTO), (528, capi.KERNEL_AUTO), (256, capi.KERNEL_AUTO)])
+def test_other_page_sizes(bs, kernel):
+    """Pages of 32, 64 and 128 slots run on the TMA page copies; other sizes (the reference's
+    grid also has 528, 816 and 864, tests/gpu/grid_cases.py:225-245) are served by the kernels
+    that gather key by key, chosen automatically."""
+    from tests.gpu_util import run_case
+
+    lens, qlens = [1500, 257, 40], [4, 4, 4]
+    c = orc.make_paged_cache(lens, 2, 128, bs, seed=60 + bs)
+    rng = np.random.default_rng(61)
+    q = orc.round_to_bf16(rng.standard_normal((sum(qlens), 8, 128), dtype=np.float32))
+    qsl = np.concatenate([[0], np.cumsum(qlens)]).astype(np.int64)
+    scale = 128 ** -0.5
+    ref = orc.ref_attention_paged(q, c, qsl, scale)
+    for S in (1, 3):
+        res = run_case(c, q, qsl, scale, bq=4, num_splits=S, kernel=kernel)
+        assert capi.load_library().device_status() == 0
+        check_out(res["out"], ref.out, what=f"block size {bs} S{S}")
+        check_lse(res["lse"], ref.lse, what=f"block size {bs} S{S}")
+        assert res["tail_intact"]
