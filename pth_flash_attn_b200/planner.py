@@ -17,7 +17,7 @@ What is planned differs, because the kernels differ:
   the workspace - and the planner's job is to make that bound generous enough:
 
       unsplit = Hkv * row tiles of the launch        work items without any split
-      S = ceil(ITEMS_PER_SM * SMs / unsplit)         pieces so that every SM gets a handful
+      S = ceil(ITEMS_PER_SM * SMs / unsplit)         room for the device's choice (it aims at 8 items per SM)
       S = min(S, s_alone)                            never more than a lone request needs
 
   ``s_alone`` = ``ceil(2 * SMs / Hkv)``: a single request is cut so that every SM gets two
@@ -55,7 +55,7 @@ MAX_ROWS_PER_CTA = ROWS_PER_WM * max(WM_CHOICES)
 CTAS_PER_SM = {64: 4, 128: 1, 256: 2}   # resident CTAs per SM by head size
 SUPPORTED_HEAD_SIZES = tuple(sorted(CTAS_PER_SM))
 WINDOWED_HEAD_SIZES = (128,)
-ITEMS_PER_SM = 8                   # pieces of work per SM the split bound allows for
+ITEMS_PER_SM = 16                  # pieces of work per SM the split bound allows for (the device aims at 8 and rounds)
 ALONE_ITEMS_PER_SM = 2             # pieces per SM for a single request
 PARTIAL_BYTES_PER_ELEMENT = 4
 

@@ -67,13 +67,13 @@ def test_baseline_shapes():
     assert one.wm == 1 and one.bq == 4 and one.num_splits == planner.s_alone(Hkv=8, D=128, num_sms=148) == 37
     # a full batch needs only a small bound (the device cuts 8,192-key requests in two)
     full = _plan()
-    assert full.num_splits == 3
+    assert full.num_splits == 5
     # monotone in the machine size, never below one
     assert [_plan(num_sms=n).num_splits for n in (1, 32, 148, 1000)] == sorted(
         _plan(num_sms=n).num_splits for n in (1, 32, 148, 1000))
     # verify: 4 draft tokens x G = 4 -> 16 rows
     v = _plan(num_tokens=128, num_reqs=32, max_query_len=4)
-    assert v.wm == 1 and v.bq == 4 and v.num_splits == 5
+    assert v.wm == 1 and v.bq == 4 and v.num_splits == 10
     # drafter: 16 tokens x 4 heads = 64 rows, window caps the splits
     d = _plan(num_tokens=512, num_reqs=32, max_query_len=16, window=4096)
     assert d.wm == 4 and d.bq == 16
@@ -86,7 +86,7 @@ def test_baseline_shapes():
     pf = _plan(num_tokens=8192, num_reqs=4, max_query_len=2048, G=8, is_prefill=True, ws_token_splits=4096)
     assert pf.wm == 4 and pf.bq == 8 and pf.num_splits == 1
     mixed = _plan(num_tokens=2128, num_reqs=58, max_query_len=1024, G=8, is_prefill=True, ws_token_splits=8 * 2128)
-    assert mixed.num_splits == 6 and mixed.num_splits * mixed.num_tokens <= 8 * 2128
+    assert mixed.num_splits == 8 and mixed.num_splits * mixed.num_tokens <= 8 * 2128
     # no reservation, no split
     assert _plan(num_tokens=1, num_reqs=1, ws_token_splits=0).num_splits == 1
 
