@@ -80,4 +80,58 @@ __device__ __forceinline__ void issue_pv_rows(uint32_t o_tmem, uint32_t p_tmem, 
   }
 }
 
+// ---- the same chains for an issuing thread that keeps its descriptors in registers ----
+// (low word = start address in 16-byte units: moving an operand by `bytes` adds bytes / 16)
+struct RowsDesc {
+  uint32_t lo, hi;
+};
+__device__ __forceinline__ RowsDesc rows_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  const uint64_t d = tc::smem_desc(saddr, lbo_bytes, sbo_bytes);
+  return RowsDesc{(uint32_t)d, (uint32_t)(d >> 32)};
+}
+template <bool kAccumulate>
+__device__ __forceinline__ void mma_ss_words(uint32_t d_tmem, uint32_t alo, uint32_t ahi, uint32_t blo, uint32_t bhi,
+                                             uint32_t idesc) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "r"(alo), "r"(ahi), "r"(blo), "r"(bhi), "r"(idesc), "n"(kAccumulate ? 1 : 0)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_words(uint32_t d_tmem, uint32_t a_tmem, uint32_t blo, uint32_t bhi, uint32_t idesc,
+                                             bool accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(blo), "r"(bhi), "r"(idesc), "r"((uint32_t)accumulate)
+      : "memory");
+}
+// q = rows_desc(Q image, kChunkStride, 128), k = rows_desc(K image, kChunkStride, 128)
+__device__ __forceinline__ void issue_qk_rows_words(uint32_t s_tmem, RowsDesc q, RowsDesc k) {
+  constexpr uint32_t idesc = tc::instr_desc(kRowsPerTile, kTileKeys, tc::kFmtBF16, tc::kFmtBF16, 0, 0);
+  constexpr uint32_t step = (2 * kChunkStride) >> 4;
+  mma_ss_words<false>(s_tmem, q.lo, q.hi, k.lo, k.hi, idesc);
+#pragma unroll
+  for (int kk = 1; kk < kHeadDim / 16; ++kk)
+    mma_ss_words<true>(s_tmem, q.lo + kk * step, q.hi, k.lo + kk * step, k.hi, idesc);
+}
+// v = rows_desc(V image, 128, kChunkStride)
+__device__ __forceinline__ void issue_pv_rows_words(uint32_t o_tmem, uint32_t p_tmem, RowsDesc v, bool accumulate) {
+  constexpr uint32_t idesc = tc::instr_desc(kRowsPerTile, kHeadDim, tc::kFmtBF16, tc::kFmtBF16, 0, 1);
+#pragma unroll
+  for (int kk = 0; kk < kTileKeys / 16; ++kk)
+    mma_ts_words(o_tmem, p_tmem + kk * 8, v.lo + kk * (256 >> 4), v.hi, idesc, accumulate || kk > 0);
+}
+
 }  // namespace pthb200

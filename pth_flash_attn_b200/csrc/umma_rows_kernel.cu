@@ -359,35 +359,49 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
     }
   } else if (warp == kRMmaWarp) {
     // =========================== MMA issuer ===================================
-    // ONE thread issues every tcgen05.mma of the CTA.  (A version with one issuing thread
-    // for QK and another for PV produced results that varied from run to run; with a single
-    // issuing thread they do not.)  Order: QK(0), QK(1), then for each tile i: PV(i) as soon
-    // as its P is complete, and QK(i + 2) once PV(i) has finished reading P(g), whose
-    // columns S(g) shares.
+    // ONE thread (the lane elect.sync picks) issues every tcgen05.mma of the CTA, in one fixed
+    // order: QK(0), QK(1), then PV(i), QK(i + 2) for i = 0, 1, ...  (A version with one issuing
+    // thread for QK and another for PV produced results that varied from run to run; a version
+    // that polled the barriers of both groups and issued whatever was ready first was slower:
+    // in steady state the other group's P is never ready while this one's PV runs, and the
+    // polling takes issue slots from the softmax warps of the same scheduler.)  QK(i + 2)
+    // overwrites S(g), which shares its columns with P(g): it waits for PV(i) to have finished
+    // reading them.  Operand descriptors are kept as register word pairs.
     named_barrier(5, kRSoftmax + 32);  // wait for the Q image
-    if (lane == 0) {
-      const uint32_t qimg_s = tc::smem_u32(qimg);
-      auto issue_qk = [&](int i) {
-        const int g = i & 1;
-        ok &= wait_or_abort(&bars[B::kfull + i % kRNK], (i / kRNK) & 1, abort_flag);
-        tc::fence_after_sync();
-        issue_qk_rows(tmem_base + g * 128, qimg_s, kimg_s + (i % kRNK) * kWideBytes);
-        tc::mma_commit(&bars[B::s_ready + g]);
-        tc::mma_commit(&bars[B::kempty + i % kRNK]);
+    {
+      const RowsDesc qd = rows_desc(tc::smem_u32(qimg), kChunkStride, 128);
+      const RowsDesc kd = rows_desc(kimg_s, kChunkStride, 128);
+      const RowsDesc vd = rows_desc(vst_s, 128, kChunkStride);
+      auto issue_qk = [&](int q) {
+        const int g = q & 1;
+        ok &= wait_or_abort(&bars[B::kfull + q % kRNK], (q / kRNK) & 1, abort_flag);
+        if (ok && elect_one()) {
+          tc::fence_after_sync();
+          RowsDesc k = kd;
+          k.lo += (uint32_t)(q % kRNK) * (kWideBytes >> 4);
+          issue_qk_rows_words(tmem_base + g * 128, qd, k);
+          tc::mma_commit(&bars[B::s_ready + g]);
+          tc::mma_commit(&bars[B::kempty + q % kRNK]);
+        }
+        __syncwarp();
       };
       issue_qk(0);
       if (n_tiles > 1) issue_qk(1);
 #pragma unroll 1
-      for (int i = 0; i < n_tiles; ++i) {
-        const int g = i & 1, k = i >> 1;
-        ok &= wait_or_abort(&bars[B::p_ready + g], k & 1, abort_flag);
-        tc::fence_after_sync();
-        issue_pv_rows(tmem_base + 256 + g * 128, tmem_base + g * 128, vst_s + (i % kRNS) * kRVStage, k > 0);
-        tc::mma_commit(&bars[B::pv_done + g]);
-        tc::mma_commit(&bars[B::vempty + i % kRNS]);
+      for (int i = 0; i < n_tiles && ok; ++i) {
+        const int g = i & 1;
+        ok &= wait_or_abort(&bars[B::p_ready + g], (i >> 1) & 1, abort_flag);
+        if (ok && elect_one()) {
+          tc::fence_after_sync();
+          RowsDesc v = vd;
+          v.lo += (uint32_t)(i % kRNS) * (kRVStage >> 4);
+          issue_pv_rows_words(tmem_base + 256 + g * 128, tmem_base + g * 128, v, (i >> 1) > 0);
+          tc::mma_commit(&bars[B::pv_done + g]);
+          tc::mma_commit(&bars[B::vempty + i % kRNS]);
+        }
+        __syncwarp();
         if (i + 2 < n_tiles) {
-          // S(g) doubles as P(g): it is free once this PV has completed
-          ok &= wait_or_abort(&bars[B::pv_done + g], k & 1, abort_flag);
+          ok &= wait_or_abort(&bars[B::pv_done + g], (i >> 1) & 1, abort_flag);
           issue_qk(i + 2);
         }
       }
