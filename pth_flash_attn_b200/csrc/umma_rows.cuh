@@ -134,4 +134,16 @@ __device__ __forceinline__ void issue_pv_rows_words(uint32_t o_tmem, uint32_t p_
     mma_ts_words(o_tmem, p_tmem + kk * 8, v.lo + kk * (256 >> 4), v.hi, idesc, accumulate || kk > 0);
 }
 
+// PV of one tile as two chains: keys 0-63 (P columns 0-31 of the S buffer, V rows 0-63) into the
+// accumulator at o_tmem, keys 64-127 (P columns 64-95, V rows 64-127) into the one at o_tmem + 128.
+__device__ __forceinline__ void issue_pv_halves_words(uint32_t o_tmem, uint32_t s_tmem, RowsDesc v, bool accumulate) {
+  constexpr uint32_t idesc = tc::instr_desc(kRowsPerTile, kHeadDim, tc::kFmtBF16, tc::kFmtBF16, 0, 1);
+#pragma unroll
+  for (int h = 0; h < 2; ++h)
+#pragma unroll
+    for (int kk = 0; kk < kTileKeys / 32; ++kk)
+      mma_ts_words(o_tmem + h * 128, s_tmem + h * 64 + kk * 8, v.lo + (h * 4 + kk) * (256 >> 4), v.hi, idesc,
+                   accumulate || kk > 0);
+}
+
 }  // namespace pthb200

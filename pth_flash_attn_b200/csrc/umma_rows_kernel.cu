@@ -48,6 +48,11 @@ constexpr int kHalfKeys = 64;            // keys of one raw half stage
 constexpr int kRawHalfBytes = kHalfKeys * kRawRow;   // 17,408 B
 constexpr int kRVStage = kWideBytes + kTileKeys * 4;  // V image + v_scale[128]
 constexpr int kRKsRing = 4;                          // tiles of scaled k_scale vectors kept
+// Registers: the CTA starts with 96 per thread (18 warps: five on two of the SM's four schedulers, whose
+// 16,384 registers that fills).  The two producer warpgroups hand 16 per thread to the two softmax
+// warpgroups, which keep the 64 scores of a row and half tile in registers between the two passes;
+// every scheduler has two warps of either kind.
+constexpr int kRProducerRegs = 72, kRSoftmaxRegs = 120;
 constexpr float kRescaleGap = 8.0f;      // log2 units a row maximum may outgrow its reference
 
 template <int kRNK, int kRNR>  // K images, raw HALF stages (64 keys each)
@@ -207,7 +212,7 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
     }
     for (int g = 0; g < 2; ++g) {
       tc::mbar_init(&bars[B::s_ready + g], 1);
-      tc::mbar_init(&bars[B::p_ready + g], kRGroup);
+      tc::mbar_init(&bars[B::p_ready + g], kRSoftmax);
       tc::mbar_init(&bars[B::pv_done + g], 1);
     }
     for (int s = 0; s < kRNR; ++s) {
@@ -230,6 +235,7 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
 
   if (warp >= 8 && warp < kRMmaWarp) {
     // =========================== producers ====================================
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRProducerRegs));
     // Warps 8-11 widen the K half of the raw cells into the K image, warps 12-15 the V half
     // (and both scales) into the V stage; thread pt of either set owns key pt of the tile.
     const int pt = tid & 127;
@@ -360,27 +366,29 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
   } else if (warp == kRMmaWarp) {
     // =========================== MMA issuer ===================================
     // ONE thread (the lane elect.sync picks) issues every tcgen05.mma of the CTA, in one fixed
-    // order: QK(0), QK(1), then PV(i), QK(i + 2) for i = 0, 1, ...  (A version with one issuing
-    // thread for QK and another for PV produced results that varied from run to run; a version
-    // that polled the barriers of both groups and issued whatever was ready first was slower:
-    // in steady state the other group's P is never ready while this one's PV runs, and the
-    // polling takes issue slots from the softmax warps of the same scheduler.)  QK(i + 2)
-    // overwrites S(g), which shares its columns with P(g): it waits for PV(i) to have finished
-    // reading them.  Operand descriptors are kept as register word pairs.
+    // order: QK(0), QK(1), then PV(i), QK(i + 2) for i = 0, 1, ...  S has two buffers in TMEM
+    // (tile i uses buffer i % 2), so QK(i + 1) runs while the softmax warps work on tile i.
+    // P(i) is written over the columns of S(i) it was computed from: QK(i + 2), which
+    // overwrites that buffer, waits for PV(i) to have finished reading them - one whole tile
+    // of softmax later than it is issued, so the wait is not on the critical path.  PV(i) is
+    // two chains: keys 0-63 of the tile into O(0), keys 64-127 into O(1), the accumulators of
+    // the two softmax groups.  (A version with one issuing thread for QK and another for PV
+    // produced results that varied from run to run; a version that polled the barriers and
+    // issued whatever was ready first was slower.)  Operand descriptors are kept as register
+    // word pairs.
     named_barrier(5, kRSoftmax + 32);  // wait for the Q image
     {
       const RowsDesc qd = rows_desc(tc::smem_u32(qimg), kChunkStride, 128);
       const RowsDesc kd = rows_desc(kimg_s, kChunkStride, 128);
       const RowsDesc vd = rows_desc(vst_s, 128, kChunkStride);
       auto issue_qk = [&](int q) {
-        const int g = q & 1;
         ok &= wait_or_abort(&bars[B::kfull + q % kRNK], (q / kRNK) & 1, abort_flag);
         if (ok && elect_one()) {
           tc::fence_after_sync();
           RowsDesc k = kd;
           k.lo += (uint32_t)(q % kRNK) * (kWideBytes >> 4);
-          issue_qk_rows_words(tmem_base + g * 128, qd, k);
-          tc::mma_commit(&bars[B::s_ready + g]);
+          issue_qk_rows_words(tmem_base + (q & 1) * 128, qd, k);
+          tc::mma_commit(&bars[B::s_ready + (q & 1)]);
           tc::mma_commit(&bars[B::kempty + q % kRNK]);
         }
         __syncwarp();
@@ -389,29 +397,34 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
       if (n_tiles > 1) issue_qk(1);
 #pragma unroll 1
       for (int i = 0; i < n_tiles && ok; ++i) {
-        const int g = i & 1;
-        ok &= wait_or_abort(&bars[B::p_ready + g], (i >> 1) & 1, abort_flag);
+        const int sb = i & 1;
+        ok &= wait_or_abort(&bars[B::p_ready + sb], (i >> 1) & 1, abort_flag);
         if (ok && elect_one()) {
           tc::fence_after_sync();
           RowsDesc v = vd;
           v.lo += (uint32_t)(i % kRNS) * (kRVStage >> 4);
-          issue_pv_rows_words(tmem_base + 256 + g * 128, tmem_base + g * 128, v, (i >> 1) > 0);
-          tc::mma_commit(&bars[B::pv_done + g]);
+          issue_pv_halves_words(tmem_base + 256, tmem_base + sb * 128, v, i > 0);
+          tc::mma_commit(&bars[B::pv_done + sb]);
           tc::mma_commit(&bars[B::vempty + i % kRNS]);
         }
         __syncwarp();
         if (i + 2 < n_tiles) {
-          ok &= wait_or_abort(&bars[B::pv_done + g], (i >> 1) & 1, abort_flag);
+          ok &= wait_or_abort(&bars[B::pv_done + sb], (i >> 1) & 1, abort_flag);
           issue_qk(i + 2);
         }
       }
     }
   } else if (warp < 8) {
     // =========================== softmax ======================================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRSoftmaxRegs));
+    // Softmax group h (warps 4 h .. 4 h + 3) owns keys 64 h .. 64 h + 63 of EVERY tile: its thread
+    // `row` keeps the running reference maximum and sum of that row over those keys and the
+    // accumulator O(h) in TMEM; the two groups' results are merged at the end.  Both groups work
+    // on tile i at the same time while the tensor core computes S(i + 1) into the other buffer.
     const int g = warp >> 2;
     const int row = tid & 127;   // row of the tile = TMEM lane
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t s_tmem = tmem_base + g * 128 + lane_addr;        // S(g), later P(g)
+    const uint32_t s_half = tmem_base + g * 64 + lane_addr;         // this group's columns of S buffer 0
     const uint32_t o_tmem = tmem_base + 256 + g * 128 + lane_addr;  // O(g)
 
     // ---- Q image: thread (row, half) copies 8 of the 16 d-chunks of its row ----
@@ -438,64 +451,65 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
     visible_range(p, t, t.first_idx, &tmp, &mask_hi);
     float m_ref = -INFINITY;  // reference maximum of the row's exponentials (log2 units)
     float l = 0.f;            // sum of exp2(score - m_ref)
-    int it = 0;
 #pragma unroll 1
-    for (int i = g; i < n_tiles; i += 2, ++it) {
-      const float* ksp = reinterpret_cast<const float*>(smem + L::ksc) + (i % kRKsRing) * kTileKeys;
-      const float* vsp = reinterpret_cast<const float*>(smem + L::vst + (i % kRNS) * kRVStage + kWideBytes);
+    for (int i = 0; i < n_tiles; ++i) {
+      const float* ksp = reinterpret_cast<const float*>(smem + L::ksc) + (i % kRKsRing) * kTileKeys + g * 64;
+      const float* vsp = reinterpret_cast<const float*>(smem + L::vst + (i % kRNS) * kRVStage + kWideBytes) + g * 64;
+      const uint32_t s_tmem = s_half + (i & 1) * 128;
       const int pos0 = (tile_begin + i) * kTileKeys;
       const bool interior = pos0 >= mask_lo && pos0 + (kTileKeys - 1) <= mask_hi;
-      ok &= wait_or_abort(&bars[B::s_ready + g], it & 1, abort_flag);
+      const int c0 = pos0 + g * 64;  // first key position of this group's half
+      ok &= wait_or_abort(&bars[B::s_ready + (i & 1)], (i >> 1) & 1, abort_flag);
       tc::fence_after_sync();
+      // the 64 scores of this row and half, read once
+      uint32_t r[64];
+      tc::tmem_ld32(s_tmem, r);
+      tc::tmem_ld32(s_tmem + 32, r + 32);
+      tc::tmem_ld_wait();
 
-      // ---- pass 1: maximum of the row's scores in this tile ----
+      // ---- pass 1: scores in log2 units (kept in the registers) and their maximum ----
       // (two instances: interior tiles, which every live row sees whole, skip the mask)
-      float m_t = -INFINITY;
+      float m_t;
       auto pass1 = [&](auto masked) {
         constexpr bool kMask = decltype(masked)::value;
-#pragma unroll 1
-        for (int j = 0; j < 4; ++j) {
-          uint32_t r[32];
-          tc::tmem_ld32(s_tmem + j * 32, r);
-          tc::tmem_ld_wait();
-          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-          for (int n4 = 0; n4 < 8; ++n4) {
-            const float4 ks4 = reinterpret_cast<const float4*>(ksp)[j * 8 + n4];  // k_scale * scale * log2 e
-            const float kk[4] = {ks4.x, ks4.y, ks4.z, ks4.w};
+        for (int n4 = 0; n4 < 16; ++n4) {
+          const float4 ks4 = reinterpret_cast<const float4*>(ksp)[n4];  // k_scale * scale * log2 e
+          const float kk[4] = {ks4.x, ks4.y, ks4.z, ks4.w};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int n = n4 * 4 + e;
-              float s = __uint_as_float(r[n]) * kk[e];
-              if constexpr (kMask) {
-                const int pos = pos0 + j * 32 + n;
-                s = (pos >= rlo && pos <= rhi) ? s : -INFINITY;
-              }
-              mx[e] = fmaxf(mx[e], s);
+          for (int e = 0; e < 4; ++e) {
+            const int n = n4 * 4 + e;
+            float sc = __uint_as_float(r[n]) * kk[e];
+            if constexpr (kMask) {
+              const int pos = c0 + n;
+              sc = (pos >= rlo && pos <= rhi) ? sc : -INFINITY;
             }
+            r[n] = __float_as_uint(sc);
+            mx[e] = fmaxf(mx[e], sc);
           }
-          m_t = fmaxf(m_t, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])));
         }
+        m_t = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       };
       if (interior) pass1(std::false_type{}); else pass1(std::true_type{});
       // ---- move the reference maximum if the row has outgrown it ----
       const float m_new = fmaxf(m_ref, m_t);
       const bool need = m_t > m_ref + kRescaleGap;  // also true when m_ref is still -inf
-      if (it == 0) {
+      if (i == 0) {
         m_ref = m_new;  // nothing accumulated yet
       } else if (__any_sync(0xffffffffu, need)) {
-        // O(g) must be at rest: the PV of this group's previous tile has completed
-        ok &= wait_or_abort(&bars[B::pv_done + g], (it - 1) & 1, abort_flag);
+        // O(g) must be at rest: the PV of the previous tile has completed
+        ok &= wait_or_abort(&bars[B::pv_done + ((i - 1) & 1)], ((i - 1) >> 1) & 1, abort_flag);
         tc::fence_after_sync();
         const float alpha = need ? ex2f(m_ref - m_new) : 1.0f;  // 0 when m_ref was -inf
 #pragma unroll 1
-        for (int j = 0; j < 4; ++j) {
-          uint32_t r[32];
-          tc::tmem_ld32(o_tmem + j * 32, r);
+        for (int j = 0; j < 8; ++j) {
+          uint32_t o[16];
+          tc::tmem_ld16(o_tmem + j * 16, o);
           tc::tmem_ld_wait();
 #pragma unroll
-          for (int n = 0; n < 32; ++n) r[n] = __float_as_uint(__uint_as_float(r[n]) * alpha);
-          tc::tmem_st32(o_tmem + j * 32, r);
+          for (int n = 0; n < 16; ++n) o[n] = __float_as_uint(__uint_as_float(o[n]) * alpha);
+          tc::tmem_st16(o_tmem + j * 16, o);
         }
         tc::tmem_st_wait();
         l *= alpha;
@@ -503,54 +517,39 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
       }
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
 
-      // ---- pass 2: p * v_scale as packed bf16 over the columns of S already read ----
+      // ---- pass 2: p * v_scale as packed bf16 over the first columns of this half of S ----
+      // (a masked score is -inf: its p is exp2(-inf) = 0)
       ok &= wait_or_abort(&bars[B::vfull + i % kRNS], (i / kRNS) & 1, abort_flag);  // v_scale (and V) of tile i
-      auto pass2 = [&](auto masked) {
-        constexpr bool kMask = decltype(masked)::value;
-#pragma unroll 1
-        for (int j = 0; j < 4; ++j) {
-          uint32_t r[32];
-          tc::tmem_ld32(s_tmem + j * 32, r);
-          tc::tmem_ld_wait();
-          uint32_t pk[16];
-          float ls[4] = {0.f, 0.f, 0.f, 0.f};
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int n4 = 0; n4 < 8; ++n4) {
-            const float4 ks4 = reinterpret_cast<const float4*>(ksp)[j * 8 + n4];
-            const float4 vs4 = reinterpret_cast<const float4*>(vsp)[j * 8 + n4];
-            const float kk[4] = {ks4.x, ks4.y, ks4.z, ks4.w};
-            const float vv[4] = {vs4.x, vs4.y, vs4.z, vs4.w};
-            float pv[4];
+      for (int j = 0; j < 2; ++j) {
+        uint32_t pk[16];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int n = n4 * 4 + e;
-              float pr = ex2f(fmaf(__uint_as_float(r[n]), kk[e], -m_use));
-              if constexpr (kMask) {
-                const int pos = pos0 + j * 32 + n;
-                pr = (pos >= rlo && pos <= rhi) ? pr : 0.f;
-              }
-              ls[e] += pr;
-              pv[e] = pr * vv[e];
-            }
-            pk[n4 * 2] = pack_bf16(pv[0], pv[1]);
-            pk[n4 * 2 + 1] = pack_bf16(pv[2], pv[3]);
+        for (int n4 = 0; n4 < 8; ++n4) {
+          const float4 vs4 = reinterpret_cast<const float4*>(vsp)[j * 8 + n4];
+          const float vv[4] = {vs4.x, vs4.y, vs4.z, vs4.w};
+          float pv[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float pr = ex2f(__uint_as_float(r[j * 32 + n4 * 4 + e]) - m_use);
+            ls[e] += pr;
+            pv[e] = pr * vv[e];
           }
-          l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-          tc::tmem_st16(s_tmem + j * 16, pk);
+          pk[n4 * 2] = pack_bf16(pv[0], pv[1]);
+          pk[n4 * 2 + 1] = pack_bf16(pv[2], pv[3]);
         }
-      };
-      if (interior) pass2(std::false_type{}); else pass2(std::true_type{});
+        tc::tmem_st16(s_tmem + j * 16, pk);
+      }
+      l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       tc::tmem_st_wait();
       tc::fence_before_sync();
-      mbar_arrive(&bars[B::p_ready + g]);  // P of tile i complete
+      mbar_arrive(&bars[B::p_ready + (i & 1)]);  // this group's half of P(i) is complete
     }
 
     // ---- epilogue: merge the two groups' (m, l, O) and write the rows ----
-    const int my_tiles = it;
-    if (my_tiles > 0) {
-      ok &= wait_or_abort(&bars[B::pv_done + g], (my_tiles - 1) & 1, abort_flag);
-      tc::fence_after_sync();
-    }
+    // (the commit after the last PV covers every MMA issued before it)
+    ok &= wait_or_abort(&bars[B::pv_done + ((n_tiles - 1) & 1)], ((n_tiles - 1) >> 1) & 1, abort_flag);
+    tc::fence_after_sync();
     // Group 1 hands its state to group 0 through 64 KB of shared memory that is idle by
     // now: the K images if they are large enough (every QK has completed once the last
     // tile's K image has been released), else the raw ring (every producer has read it
@@ -568,15 +567,13 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
       }
       park_m[row] = m_ref;
       park_l[row] = l;
-      if (my_tiles > 0) {
 #pragma unroll 1
-        for (int j = 0; j < 4; ++j) {
-          uint32_t r[32];
-          tc::tmem_ld32(o_tmem + j * 32, r);
-          tc::tmem_ld_wait();
+      for (int j = 0; j < 4; ++j) {
+        uint32_t r[32];
+        tc::tmem_ld32(o_tmem + j * 32, r);
+        tc::tmem_ld_wait();
 #pragma unroll
-          for (int n = 0; n < 32; ++n) park[(j * 32 + n) * kRGroup + row] = __uint_as_float(r[n]);
-        }
+        for (int n = 0; n < 32; ++n) park[(j * 32 + n) * kRGroup + row] = __uint_as_float(r[n]);
       }
     }
     named_barrier(4, kRSoftmax);
@@ -595,7 +592,7 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
 #pragma unroll 1
       for (int j = 0; j < 4; ++j) {
         uint32_t r[32];
-        tc::tmem_ld32(o_tmem + j * 32, r);  // group 0 always has a tile
+        tc::tmem_ld32(o_tmem + j * 32, r);
         tc::tmem_ld_wait();
         float o[32];
 #pragma unroll
