@@ -11,18 +11,23 @@
 //                         exactly to bf16 into the K image / the V stage (canonical
 //                         no-swizzle layout), with k_scale * softmax_scale * log2 e and
 //                         v_scale of the key;
-//   MMA issuer (1 thread) S = Q K^T (M = 128 rows, N = 128 keys, fp32 in TMEM, one buffer
-//                         per softmax group) and O += P V with P read from TMEM (the A
-//                         operand), V from the V stage as an MN-major B operand;
-//   softmax    (2 groups of 4 warps; group g owns the tiles i with i % 2 == g) thread r:
-//                         pass 1 finds the tile maximum of row r (score = S * k_scale *
-//                         softmax_scale * log2 e), pass 2 writes p * v_scale as packed bf16
-//                         into TMEM over the columns of S it has already read.  The
-//                         reference maximum of a row moves only when the running maximum
-//                         outgrows it by 2^8; then the thread rescales its row of O in
-//                         TMEM.  In steady state O is never touched by the softmax;
+//   MMA issuer (1 warp, one elected lane) S = Q K^T (M = 128 rows, N = 128 keys, fp32 in
+//                         TMEM, two buffers: tile i uses buffer i % 2, so S(i + 1) is computed
+//                         while the softmax warps work on tile i) and O(g) += P V for each
+//                         softmax group g, with P read from TMEM (the A operand) and V from
+//                         the V stage as an MN-major B operand;
+//   softmax    (2 groups of 4 warps; group g owns keys 64 g .. 64 g + 63 of EVERY tile)
+//                         thread r reads the 64 scores of row r and its half once, pass 1
+//                         turns them into log2 units (score = S * k_scale * softmax_scale *
+//                         log2 e) and finds their maximum, pass 2 writes p * v_scale as
+//                         packed bf16 into TMEM over the columns of S it has read.  The
+//                         reference maximum of a (row, half) moves only when the running
+//                         maximum outgrows it by 2^8; then the thread rescales its row of
+//                         O(g) in TMEM.  In steady state O is never touched by the softmax.
 // The two groups' (m, l, O) are merged in the epilogue.  TMEM: S0 S1 O0 O1, 128 columns
-// each.  Every mbarrier wait is bounded (see page_copy.cuh).
+// each.  The CTA starts with 96 registers per thread; the producer warpgroups hand part of
+// theirs to the softmax warpgroups (setmaxnreg).  Every mbarrier wait is bounded (see
+// page_copy.cuh).
 #include <cuda.h>
 
 #include <type_traits>
