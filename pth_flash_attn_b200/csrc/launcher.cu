@@ -356,6 +356,7 @@ int32_t pthb200_copy_ceiling(const PthAttnArgs* args, void* stream) {
   if (int32_t rc = build_attention(args, nullptr, &p)) return rc;
   const char* why = "";
   PTHB_REQUIRE(umma_i8_supports(p, &why), std::string("the paged-copy ceiling follows the integer kernel, which does not apply: ") + why);
+  PTHB_REQUIRE(p.head_size == 128, "the paged-copy ceiling is built for head size 128");
   const cudaError_t err = launch_copy_ceiling(p, static_cast<cudaStream_t>(stream));
   if (err != cudaSuccess) return fail(PTH_ATTN_ECUDA, std::string("copy launch failed: ") + cudaGetErrorString(err));
   return PTH_ATTN_OK;

@@ -21,6 +21,9 @@ namespace {
 constexpr int kRawKeys = 128;                               // keys of one KV tile
 constexpr int kRawRow = 272;                                // aligned bytes that cover a 264-byte cell
 constexpr int kRawStageBytes = kRawKeys * kRawRow;          // 34,816 B
+// The same for any head size: 144 bytes for 64, 272 for 128, 528 for 256.
+__host__ __device__ constexpr int raw_row_for(int head_size) { return (2 * head_size + 8 + 8 + 15) / 16 * 16; }
+static_assert(raw_row_for(128) == kRawRow, "raw row of head size 128");
 
 __device__ __forceinline__ void named_barrier(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
@@ -132,9 +135,12 @@ bool make_page_map(const KernelParams& p, int num_blocks, CUtensorMap* map) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return false;
   const uintptr_t base = reinterpret_cast<uintptr_t>(p.k.data) & ~(uintptr_t)15;
-  const cuuint64_t dims[3] = {(cuuint64_t)(p.k.stride_slot / 4), (cuuint64_t)p.block_size, (cuuint64_t)num_blocks};
+  // a slot's cells end (k.data - base) bytes after one slot stride from the row's start: the row
+  // is that much longer, so the last head's cell is inside it (and no byte after the slot is)
+  const uintptr_t lead = reinterpret_cast<uintptr_t>(p.k.data) - base;
+  const cuuint64_t dims[3] = {(cuuint64_t)((p.k.stride_slot + lead) / 4), (cuuint64_t)p.block_size, (cuuint64_t)num_blocks};
   const cuuint64_t strides[2] = {(cuuint64_t)p.k.stride_slot, (cuuint64_t)p.k.stride_block};
-  const cuuint32_t box[3] = {(cuuint32_t)(kRawRow / 4), (cuuint32_t)p.block_size, 1u};
+  const cuuint32_t box[3] = {(cuuint32_t)(raw_row_for(p.head_size) / 4), (cuuint32_t)p.block_size, 1u};
   const cuuint32_t elem[3] = {1u, 1u, 1u};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, reinterpret_cast<void*>(base), dims, strides, box, elem,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -152,20 +158,20 @@ const CUtensorMap* cached_page_map(const KernelParams& p) {
   struct Entry {
     uintptr_t base;
     int64_t stride_slot, stride_block;
-    int32_t block_size, num_blocks;
+    int32_t block_size, num_blocks, head_size;
     CUtensorMap map;
   };
   constexpr int kEntries = 64;
   static Entry entries[kEntries];
   static int used = 0;
   static std::mutex mu;
-  const uintptr_t base = reinterpret_cast<uintptr_t>(p.k.data) & ~(uintptr_t)15;
+  const uintptr_t base = reinterpret_cast<uintptr_t>(p.k.data);
   {
     std::lock_guard<std::mutex> lock(mu);
     for (int i = 0; i < used; ++i) {
       const Entry& e = entries[i];
       if (e.base == base && e.stride_slot == p.k.stride_slot && e.stride_block == p.k.stride_block &&
-          e.block_size == p.block_size && e.num_blocks == p.num_blocks) {
+          e.block_size == p.block_size && e.num_blocks == p.num_blocks && e.head_size == p.head_size) {
         return &e.map;
       }
     }
@@ -177,6 +183,7 @@ const CUtensorMap* cached_page_map(const KernelParams& p) {
       e.stride_block = p.k.stride_block;
       e.block_size = p.block_size;
       e.num_blocks = p.num_blocks;
+      e.head_size = p.head_size;
       ++used;
       return &e.map;
     }
@@ -209,7 +216,7 @@ int raw_mode_for(const KernelParams& p) {
                               ((int64_t)p.block_size * p.k.stride_slot) % 16 == 0;
     return aligned_runs ? 2 : 0;
   }
-  if (p.k.stride_slot % 16 == 0 && p.k.stride_slot >= kRawRow) return 1;
+  if (p.k.stride_slot % 16 == 0 && p.k.stride_slot >= raw_row_for(p.head_size)) return 1;
   return 0;
 }
 

@@ -205,6 +205,7 @@ cudaError_t launch_umma_attention(const KernelParams& p, cudaStream_t stream);
 cudaError_t launch_umma_i8_attention(const KernelParams& p, cudaStream_t stream);
 cudaError_t launch_umma_rows_attention(const KernelParams& p, cudaStream_t stream);
 // CTAs the persistent integer kernel is launched with on a device of `sms` SMs (-1: too many items).
+int umma_i8_max_rows(int head_size);
 int umma_i8_num_ctas(const KernelParams& p, int sms);
 cudaError_t read_i8_status(unsigned int* v);
 cudaError_t read_rows_status(unsigned int* v);

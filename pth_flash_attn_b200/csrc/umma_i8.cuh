@@ -27,7 +27,20 @@ constexpr int kHeadDimI8 = 128;
 constexpr int kKeys = 128;
 constexpr int kDigitChunk = kKeys * 16;      // 2,048 B
 constexpr int kImgChunk = kKeys * 16 + 16;   // 2,064 B
-constexpr int kImgBytes = 8 * kImgChunk;     // 16,512 B
+constexpr int kImgBytes = 8 * kImgChunk;     // 16,512 B (head size 128)
+
+// Geometry of the raw cells and operand images for head size HD (64, 128 or 256).
+template <int HD>
+struct I8Geom {
+  static_assert(HD == 64 || HD == 128 || HD == 256, "head size");
+  static constexpr int chunks = HD / 16;                       // 16-byte column blocks of one key's K (or V) row
+  static constexpr int img_bytes = chunks * kImgChunk;         // one K or V image of a tile
+  static constexpr int cell = 2 * HD + 8;                      // K | k_scale | V | v_scale
+  static constexpr int raw_row = (cell + 8 + 15) / 16 * 16;    // 16-byte aligned bytes that cover an 8-byte aligned cell
+  static constexpr int raw_stage = kKeys * raw_row;            // raw cells of one tile
+  static constexpr int part_words = HD / 4 + 4;                // words of the 16-byte pieces that cover K + k_scale (or V + v_scale)
+  static constexpr int halves = HD > 128 ? 2 : 1;              // O^T accumulators of 128 dims (MMA M = 128)
+};
 
 // Order-preserving map float -> int, so an integer warp reduction finds a float maximum.
 __device__ __forceinline__ int float_key(float f) {
@@ -160,25 +173,32 @@ __device__ __forceinline__ void mma_i8_words(uint32_t d_tmem, uint32_t alo, uint
       : "memory");
 }
 // k = descriptor words of the K image (desc_words(kimg, kImgChunk, 128)), q = of the Q image
-// (desc_words(qimg, 2 NPAD 16, 128)).
-template <int NPAD>
+// (desc_words(qimg, 2 NPAD 16, 128)).  HD / 32 MMAs: one per 32 dims.
+template <int NPAD, int HD = 128>
 __device__ __forceinline__ void issue_qk_i8_words(uint32_t s_tmem, DescWords k, DescWords q) {
   constexpr uint32_t idesc = idesc_i8(128, 2 * NPAD, 0, 0);
   constexpr uint32_t ka = (2 * kImgChunk) >> 4, qa = (2 * (2 * NPAD * 16)) >> 4;
   mma_i8_words<false>(s_tmem, k.lo, k.hi, q.lo, q.hi, idesc);
-  mma_i8_words<true>(s_tmem, k.lo + ka, k.hi, q.lo + qa, q.hi, idesc);
-  mma_i8_words<true>(s_tmem, k.lo + 2 * ka, k.hi, q.lo + 2 * qa, q.hi, idesc);
-  mma_i8_words<true>(s_tmem, k.lo + 3 * ka, k.hi, q.lo + 3 * qa, q.hi, idesc);
+#pragma unroll
+  for (int kk = 1; kk < HD / 32; ++kk) mma_i8_words<true>(s_tmem, k.lo + kk * ka, k.hi, q.lo + kk * qa, q.hi, idesc);
 }
-// v = desc_words(vimg, 128, kImgChunk), pd = desc_words(pimg, 128, kDigitChunk).
-template <int NPAD, int PD>
+// v = desc_words(vimg, 128, kImgChunk), pd = desc_words(pimg, 128, kDigitChunk).  One chain of four
+// MMAs (32 keys each) per 128 dims of the head: dims 128 h ... land in the accumulator at
+// o_tmem + h PD NPAD.  For a head of 64 dims the M = 128 instruction also reads the 64 "rows"
+// after the V image (whatever bytes follow it in shared memory): integer garbage in TMEM lanes
+// 64-127, which nothing reads.
+template <int NPAD, int PD, int HD = 128>
 __device__ __forceinline__ void issue_pv_i8_words(uint32_t o_tmem, DescWords v, DescWords pd) {
   constexpr uint32_t idesc = idesc_i8(128, PD * NPAD, 1, 1);
   constexpr uint32_t step = (4 * 128) >> 4;
-  mma_i8_words<false>(o_tmem, v.lo, v.hi, pd.lo, pd.hi, idesc);
-  mma_i8_words<true>(o_tmem, v.lo + step, v.hi, pd.lo + step, pd.hi, idesc);
-  mma_i8_words<true>(o_tmem, v.lo + 2 * step, v.hi, pd.lo + 2 * step, pd.hi, idesc);
-  mma_i8_words<true>(o_tmem, v.lo + 3 * step, v.hi, pd.lo + 3 * step, pd.hi, idesc);
+#pragma unroll
+  for (int h = 0; h < I8Geom<HD>::halves; ++h) {
+    const uint32_t vlo = v.lo + h * ((8 * kImgChunk) >> 4), o = o_tmem + h * (PD * NPAD);
+    mma_i8_words<false>(o, vlo, v.hi, pd.lo, pd.hi, idesc);
+    mma_i8_words<true>(o, vlo + step, v.hi, pd.lo + step, pd.hi, idesc);
+    mma_i8_words<true>(o, vlo + 2 * step, v.hi, pd.lo + 2 * step, pd.hi, idesc);
+    mma_i8_words<true>(o, vlo + 3 * step, v.hi, pd.lo + 3 * step, pd.hi, idesc);
+  }
 }
 
 }  // namespace pthb200

@@ -1,4 +1,4 @@
-// Integer tcgen05 attention kernel, head size 128, token-major orientation, persistent CTAs.
+// Integer tcgen05 attention kernel, head sizes 64 / 128 / 256, token-major orientation, persistent CTAs.
 //
 // The cache holds int8 K and V, so both contractions run on the int8 tensor path
 // (tcgen05.mma.kind::i8, int32 accumulators in TMEM) with the cache bytes used AS
@@ -71,7 +71,6 @@ constexpr int kItemSlots = 2;                           // item descriptors (and
 // the loader and the scheduler.
 __host__ __device__ constexpr int threads_for(int np) { return kSoftmaxThreads + np * kProducerThreads + 96; }
 constexpr int kStageScales = 2 * kKeys * 4;                 // k_scale[128], v_scale[128]
-constexpr int kVStageBytes = kImgBytes + kStageScales;      // V image and both scale vectors of one tile
 
 // What the scheduler publishes for one item (shared memory, one per slot).
 struct ItemDesc {
@@ -84,16 +83,19 @@ struct ItemDesc {
   int32_t pad;
 };
 
-template <int NPAD, int PD, int NS, int NK, int NR, int SB>
+template <int HD, int NPAD, int PD, int NS, int NK, int NR, int SB>
 struct Layout {
+  using G = I8Geom<HD>;
+  static constexpr int img_bytes = G::img_bytes;
+  static constexpr int vstage_bytes = G::img_bytes + kStageScales;  // V image and both scale vectors of one tile
   static constexpr int kstages = 0;                                 // [NK] K images
-  static constexpr int vstages = kstages + NK * kImgBytes;          // [NS] V image + scales
-  static constexpr int qimg = vstages + NS * kVStageBytes;          // [slots][8][2 NPAD][16]
-  static constexpr int qimg_bytes = 8 * 2 * NPAD * 16;
+  static constexpr int vstages = kstages + NK * img_bytes;          // [NS] V image + scales
+  static constexpr int qimg = vstages + NS * vstage_bytes;          // [slots][HD / 16][2 NPAD][16]
+  static constexpr int qimg_bytes = G::chunks * 2 * NPAD * 16;
   static constexpr int pimg = qimg + kItemSlots * qimg_bytes;       // [2 groups][PD NPAD / 16][128][16]
   static constexpr int pimg_bytes = 2 * PD * NPAD * kKeys;
-  static constexpr int raw = pimg + pimg_bytes;                     // [NR][128][272] raw cells
-  static constexpr int wred = raw + NR * kRawStageBytes;            // float [2 groups][2][4][NPAD + 1]
+  static constexpr int raw = (pimg + pimg_bytes + 127) / 128 * 128; // [NR][128][raw row] raw cells (TMA destinations: 128-byte aligned)
+  static constexpr int wred = raw + NR * G::raw_stage;              // float [2 groups][2][4][NPAD + 1]
   static constexpr int mrun = wred + 2 * 2 * 4 * (NPAD + 1) * 4;    // float [2 groups][2 NPAD], first NPAD used
   static constexpr int sq = mrun + 2 * 2 * NPAD * 4;                // float [slots][NPAD]
   static constexpr int rlo = sq + kItemSlots * NPAD * 4;            // int [slots][NPAD]
@@ -104,12 +106,17 @@ struct Layout {
   static constexpr int misc = bars + n_bars * 8;                    // abort flag, TMEM slot, total work
   static constexpr int total = misc + 32;
   static constexpr int s_cols = 2 * NPAD;
-  static constexpr int o_cols = PD * NPAD;
+  static constexpr int o_cols = G::halves * PD * NPAD;              // one O^T accumulator per 128 dims of the head
   static constexpr int s_total = 2 * SB * s_cols;                   // [2 groups][SB] S^T buffers
   static constexpr int tmem_need = s_total + 2 * o_cols;
   static constexpr int tmem_alloc = tmem_need <= 32 ? 32 : tmem_need <= 64 ? 64 : tmem_need <= 128 ? 128
                                     : tmem_need <= 256 ? 256 : 512;
   static_assert(sizeof(ItemDesc) % 16 == 0, "descriptor slots stay 16-byte aligned");
+  static_assert(raw % 128 == 0 && G::raw_stage % 128 == 0 && (16 * G::raw_row) % 128 == 0,
+                "every page copy of 16 or more slots lands on a 128-byte boundary");
+  static_assert(vstages % 16 == 0 && vstage_bytes % 16 == 0 && qimg % 16 == 0 && qimg_bytes % 16 == 0 && pimg % 16 == 0,
+                "operand images start on 16-byte boundaries");
+  static_assert(wred % 16 == 0 && bars % 8 == 0, "reduction buffers and mbarriers are aligned");
 };
 
 // Barrier indices inside the barrier array.
@@ -149,11 +156,14 @@ __device__ __forceinline__ bool named_barrier_or(int id, int count, bool pred) {
   return r != 0;
 }
 
-template <int NPAD, int PD, int NS, int NK, int NR, int SB, int RQ, int NP>
+template <int HD, int NPAD, int PD, int NS, int NK, int NR, int SB, int RQ, int NP>
 __global__ void __launch_bounds__(threads_for(NP), 1)
 umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_constant__ CUtensorMap tmap) {
-  using L = Layout<NPAD, PD, NS, NK, NR, SB>;
+  using L = Layout<HD, NPAD, PD, NS, NK, NR, SB>;
   using B = Bars<NS, NR>;
+  using G = I8Geom<HD>;
+  constexpr int kRawRowHD = G::raw_row, kRawStageHD = G::raw_stage, kImgHD = G::img_bytes;
+  constexpr int kVStageHD = L::vstage_bytes, kHalves = G::halves;
   constexpr int kRawStages = NR;
   constexpr int XMAX = (1 << (7 * PD)) - 1;
   constexpr int kThreads = threads_for(NP);
@@ -163,8 +173,10 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
   // arrivals that free an item slot: every softmax and producer thread, the issuer, the loader
   constexpr int kItemReaders = kSoftmaxThreads + NP * kProducerThreads + 2;
   static_assert(RQ >= 1 && 4 * RQ <= NPAD, "RQ = groups of four rows the softmax handles (rows <= 4 RQ)");
-  static_assert(NS >= 2, "two image stages: one feeding the MMAs, one being filled");
-  static_assert(PD * NPAD >= 8 * RQ, "the P images hold the parked accumulator of one softmax group");
+  // QK runs two tiles ahead of PV (see the issuer): QK(i + 2) needs the V stage of tile i + 2
+  // filled, which with two stages would be the one PV(i), issued after it, has yet to free.
+  static_assert(NS >= 3, "QK(i + 2) is issued before PV(i): tile i + 2 needs a V stage of its own");
+  static_assert(PD * NPAD >= 8 * RQ, "the P images hold 128 dims of the parked accumulator of one softmax group");
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* pimg = smem + L::pimg;
   float* wred = reinterpret_cast<float*>(smem + L::wred);
@@ -319,9 +331,9 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
         mark_unused_splits();
         // No keys for this item: zero output, log-sum-exp -inf.
         if (S == 1) {
-          for (int i = lane; i < rows * kHeadDimI8; i += 32) {
-            const int n = i >> 7, token = tok0 + n / p.group, head = c.kvh * p.group + n % p.group;
-            store_out_elem(p.out + (int64_t)token * p.out_stride_token + (int64_t)head * p.out_stride_head, i & 127,
+          for (int i = lane; i < rows * HD; i += 32) {
+            const int n = i / HD, token = tok0 + n / p.group, head = c.kvh * p.group + n % p.group;
+            store_out_elem(p.out + (int64_t)token * p.out_stride_token + (int64_t)head * p.out_stride_head, i % HD,
                            p.out_dtype, 0.f);
           }
         }
@@ -366,9 +378,10 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
           rlo[n] = lo;
           rhi[n] = hi;
         }
-        // Q digits: 8 lanes per row, 16 elements each (4 rows per pass).
-        for (int nb = 0; nb < NPAD; nb += 4) {
-          const int n = nb + (lane >> 3), part = lane & 7;
+        // Q digits: HD / 16 lanes per row, 16 elements each (32 / (HD / 16) rows per pass).
+        constexpr int kQLanes = G::chunks, kQRows = 32 / kQLanes;
+        for (int nb = 0; nb < NPAD; nb += kQRows) {
+          const int n = nb + lane / kQLanes, part = lane % kQLanes;
           float v[16];
           if (n < rows) {
             const int token = tok0 + n / p.group, head = c.kvh * p.group + n % p.group;
@@ -397,9 +410,8 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
           float amax = 0.f;
 #pragma unroll
           for (int e = 0; e < 16; ++e) amax = fmaxf(amax, fabsf(v[e]));
-          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+#pragma unroll
+          for (int o = 1; o < kQLanes; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
           const bool finite_row = amax > 0.f && amax < INFINITY;
           const float inv = finite_row ? 32512.f / amax : 0.f;
           uint32_t hi_w[4] = {0, 0, 0, 0}, lo_w[4] = {0, 0, 0, 0};
@@ -479,12 +491,12 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
           if (g >= kRawStages) ok &= wait_or_abort(&bars[B::raw_free + rs], ((g / kRawStages) - 1) & 1, abort_flag);
           uint64_t* bar = &bars[B::raw_full + rs];
           if (blk >= 0 && ok) {
-            const uint32_t dst = raw_s + rs * kRawStageBytes + lane * bs * kRawRow;
+            const uint32_t dst = raw_s + rs * kRawStageHD + lane * bs * kRawRowHD;
             if (p.raw_mode == 1) {
-              mbar_arrive_expect_tx(bar, bs * kRawRow);
+              mbar_arrive_expect_tx(bar, bs * kRawRowHD);
               tma_load_3d(dst, &tmap, tma_x, 0, blk, bar);
             } else {
-              const uint32_t bytes = bs * (2 * kHeadDimI8 + 8);  // a multiple of 16, like the run's address
+              const uint32_t bytes = bs * G::cell;  // a multiple of 16, like the run's address
               mbar_arrive_expect_tx(bar, bytes);
               bulk_copy_g2s(dst, kb + (int64_t)blk * p.k.stride_block, bytes, bar);
             }
@@ -504,11 +516,11 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     const int pt = (tid - kSoftmaxThreads) & (kProducerThreads - 1);  // row of the operand images this thread fills
     // The raw bytes of a tile are brought in by the loader warp (above), page by page; when a
     // raw tile has landed, producer thread t moves the words of its key into the operand
-    // images: with delta = (cell address mod 16) in {0, 8}, word w of K block j is raw word
-    // delta / 4 + 4 j + w, of V block j raw word delta / 4 + 33 + 4 j + w; the scales are raw
-    // words delta / 4 + 32 and + 65.
+    // images: with delta = (cell address mod 16) in {0, 8} and D = head size, word w of K block
+    // j is raw word delta / 4 + 4 j + w, of V block j raw word delta / 4 + D / 4 + 1 + 4 j + w;
+    // the scales are raw words delta / 4 + D / 4 and + D / 2 + 1.
     const int bs = p.block_size;
-    const int row_pitch = p.raw_mode == 1 ? kRawRow : 2 * kHeadDimI8 + 8;
+    const int row_pitch = p.raw_mode == 1 ? kRawRowHD : G::cell;
     // Row pt of the operand images holds key `key` of the tile.  With a 264-byte pitch
     // (raw_mode 2) consecutive cells alternate between the two 8-byte alignments: taking the
     // even cells in the first two warps and the odd ones in the last two keeps a warp on one
@@ -528,7 +540,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
                 range_end = descs[slot].range_end;
       const uint8_t* kb = p.k.data + (int64_t)descs[slot].kvh * p.k.stride_head;
       const uint32_t delta = (uint32_t)(reinterpret_cast<uintptr_t>(kb) & 15);
-      const uint32_t cell_off = my_page * bs * kRawRow + my_slot * row_pitch + delta;  // inside a raw stage
+      const uint32_t cell_off = my_page * bs * kRawRowHD + my_slot * row_pitch + delta;  // inside a raw stage
       const bool odd = (cell_off & 8u) != 0;
       int j = pgrp - g0 % NP;  // first tile of the item whose running count is pgrp mod NP
       if (j < 0) j += NP;
@@ -546,26 +558,37 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
           if (g >= kRawStages) ok &= wait_or_abort(&bars[B::raw_free + rs], ((g / kRawStages) - 1) & 1, abort_flag);
         }
         ok &= wait_or_abort(&bars[B::raw_full + rs], (g / kRawStages) & 1, abort_flag);
-        uint32_t w[kRawRow / 4];
-        if (valid) {
-          const uint4* row = reinterpret_cast<const uint4*>(smem + L::raw + rs * kRawStageBytes + (cell_off & ~15u));
+        // The 16-byte pieces from the boundary below the cell: pieces 0 .. D / 16 hold K and
+        // k_scale, pieces D / 16 .. D / 8 hold k_scale, V and v_scale.  Up to head size 128 both
+        // sets are read before the raw stage is released; a 256-dim row is too long for that
+        // (132 words), so its V set is read after the K image has been written.
+        constexpr int PW = G::part_words, NCH = G::chunks;
+        constexpr bool kTwoPhase = HD > 128;
+        const uint4* row = reinterpret_cast<const uint4*>(smem + L::raw + rs * kRawStageHD + (cell_off & ~15u));
+        auto load_part = [&](const uint4* src, uint32_t (&w)[PW]) {
+          if (valid) {
 #pragma unroll
-          for (int c = 0; c < kRawRow / 16; ++c) {
-            const uint4 v = row[c];
-            w[4 * c] = v.x;
-            w[4 * c + 1] = v.y;
-            w[4 * c + 2] = v.z;
-            w[4 * c + 3] = v.w;
+            for (int c = 0; c < PW / 4; ++c) {
+              const uint4 v = src[c];
+              w[4 * c] = v.x;
+              w[4 * c + 1] = v.y;
+              w[4 * c + 2] = v.z;
+              w[4 * c + 3] = v.w;
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < PW; ++c) w[c] = 0u;
           }
-        } else {
-#pragma unroll
-          for (int c = 0; c < kRawRow / 4; ++c) w[c] = 0u;
+        };
+        uint32_t kw[PW], vw[PW];
+        load_part(row, kw);
+        if constexpr (!kTwoPhase) {
+          load_part(row + NCH, vw);
+          // this thread's row is in registers (the arrive orders the loads before it): once all
+          // producers of the tile have arrived the loader may refill the raw stage
+          mbar_arrive(&bars[B::raw_free + rs]);
         }
-        // this thread's row is in registers (the arrive orders the loads before it): once all
-        // 128 producers have arrived the loader may refill the raw stage
-        mbar_arrive(&bars[B::raw_free + rs]);
         const int st = g % NS;
-        if (g >= NS) ok &= wait_or_abort(&bars[B::empty + st], ((g / NS) - 1) & 1, abort_flag);
         // K image g % NK is free once QK(g - NK) has completed, which is what S^T of that tile
         // being ready means: the producers wait on the s_ready barrier the softmax group waits
         // on (one commit less per tile for the issuing thread).  That barrier completes next
@@ -574,29 +597,40 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
           const int q = g - NK, qk = q >> 1;
           ok &= wait_or_abort(&bars[B::s_ready + 2 * (q & 1) + qk % SB], (qk / SB) & 1, abort_flag);
         }
-        uint8_t* stage = smem + L::vstages + st * kVStageBytes;  // V image, then the scales
-        uint8_t* krow = smem + L::kstages + (g % NK) * kImgBytes + pt * 16;
+        uint8_t* stage = smem + L::vstages + st * kVStageHD;  // V image, then the scales
+        uint8_t* krow = smem + L::kstages + (g % NK) * kImgHD + pt * 16;
         uint8_t* vrow = stage + pt * 16;
+        const int ko = odd ? 2 : 0, vo = odd ? 3 : 1;  // first word of K / V inside their sets of pieces
         if (!odd) {
 #pragma unroll
-          for (int b = 0; b < 8; ++b) {
-            *reinterpret_cast<uint4*>(krow + b * kImgChunk) = make_uint4(w[4 * b], w[4 * b + 1], w[4 * b + 2], w[4 * b + 3]);
-            *reinterpret_cast<uint4*>(vrow + b * kImgChunk) =
-                make_uint4(w[33 + 4 * b], w[34 + 4 * b], w[35 + 4 * b], w[36 + 4 * b]);
-          }
-          *reinterpret_cast<uint32_t*>(stage + kImgBytes + pt * 4) = w[32];
-          *reinterpret_cast<uint32_t*>(stage + kImgBytes + kKeys * 4 + pt * 4) = w[65];
+          for (int b = 0; b < NCH; ++b)
+            *reinterpret_cast<uint4*>(krow + b * kImgChunk) = make_uint4(kw[4 * b], kw[4 * b + 1], kw[4 * b + 2], kw[4 * b + 3]);
         } else {
 #pragma unroll
-          for (int b = 0; b < 8; ++b) {
+          for (int b = 0; b < NCH; ++b)
             *reinterpret_cast<uint4*>(krow + b * kImgChunk) =
-                make_uint4(w[2 + 4 * b], w[3 + 4 * b], w[4 + 4 * b], w[5 + 4 * b]);
-            *reinterpret_cast<uint4*>(vrow + b * kImgChunk) =
-                make_uint4(w[35 + 4 * b], w[36 + 4 * b], w[37 + 4 * b], w[38 + 4 * b]);
-          }
-          *reinterpret_cast<uint32_t*>(stage + kImgBytes + pt * 4) = w[34];
-          *reinterpret_cast<uint32_t*>(stage + kImgBytes + kKeys * 4 + pt * 4) = w[67];
+                make_uint4(kw[2 + 4 * b], kw[3 + 4 * b], kw[4 + 4 * b], kw[5 + 4 * b]);
         }
+        const uint32_t k_scale_bits = odd ? kw[HD / 4 + 2] : kw[HD / 4];
+        (void)ko;
+        if constexpr (kTwoPhase) {
+          load_part(row + NCH, vw);
+          mbar_arrive(&bars[B::raw_free + rs]);
+        }
+        if (g >= NS) ok &= wait_or_abort(&bars[B::empty + st], ((g / NS) - 1) & 1, abort_flag);
+        if (!odd) {
+#pragma unroll
+          for (int b = 0; b < NCH; ++b)
+            *reinterpret_cast<uint4*>(vrow + b * kImgChunk) = make_uint4(vw[1 + 4 * b], vw[2 + 4 * b], vw[3 + 4 * b], vw[4 + 4 * b]);
+        } else {
+#pragma unroll
+          for (int b = 0; b < NCH; ++b)
+            *reinterpret_cast<uint4*>(vrow + b * kImgChunk) =
+                make_uint4(vw[3 + 4 * b], vw[4 + 4 * b], vw[5 + 4 * b], vw[6 + 4 * b]);
+        }
+        (void)vo;
+        *reinterpret_cast<uint32_t*>(stage + kImgHD + pt * 4) = k_scale_bits;
+        *reinterpret_cast<uint32_t*>(stage + kImgHD + kKeys * 4 + pt * 4) = odd ? vw[HD / 4 + 3] : vw[HD / 4 + 1];
         tc::fence_async_smem();
         mbar_arrive(&bars[B::full + st]);
       }
@@ -655,8 +689,8 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
         if (ready && elect_one()) {
           tc::fence_after_sync();
           DescWords kq = kd;
-          kq.lo += (uint32_t)(q % NK) * (kImgBytes >> 4);
-          issue_qk_i8_words<NPAD>(tmem_base + (g * SB + sb) * L::s_cols, kq, qd);
+          kq.lo += (uint32_t)(q % NK) * (kImgHD >> 4);
+          issue_qk_i8_words<NPAD, HD>(tmem_base + (g * SB + sb) * L::s_cols, kq, qd);
           tc::mma_commit_s(bars_s + 8u * (B::s_ready + 2 * g + sb));
         }
         return ready;
@@ -667,9 +701,9 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
         if (ready && elect_one()) {
           tc::fence_after_sync();
           DescWords vi = vd, pi = pd;
-          vi.lo += (uint32_t)(i % NS) * (kVStageBytes >> 4);
+          vi.lo += (uint32_t)(i % NS) * (kVStageHD >> 4);
           pi.lo += (uint32_t)g * ((PD * NPAD * kKeys) >> 4);
-          issue_pv_i8_words<NPAD, PD>(tmem_base + L::s_total + g * L::o_cols, vi, pi);
+          issue_pv_i8_words<NPAD, PD, HD>(tmem_base + L::s_total + g * L::o_cols, vi, pi);
           tc::mma_commit_s(bars_s + 8u * (B::o_ready + g));
           tc::mma_commit_s(bars_s + 8u * (B::empty + i % NS));
         }
@@ -719,10 +753,11 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       const int* rlo = reinterpret_cast<const int*>(smem + L::rlo) + slot * NPAD;
       const int* rhi = reinterpret_cast<const int*>(smem + L::rhi) + slot * NPAD;
 
-      float acc[NROW], l_part[NROW];
+      float acc[kHalves][NROW], l_part[NROW];  // thread t accumulates output columns t (and t + 128)
 #pragma unroll
       for (int n = 0; n < NROW; ++n) {
-        acc[n] = 0.f;
+#pragma unroll
+        for (int h = 0; h < kHalves; ++h) acc[h][n] = 0.f;
         l_part[n] = 0.f;
       }
       // Per-row softmax state lives in LANES, not in shared memory: lane l of every warp holds,
@@ -746,24 +781,27 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
         const uint32_t o_tmem = tmem_base + L::s_total + g * L::o_cols + lane_addr;
         constexpr int FB = RQ < 2 ? RQ : 2;  // eight rows per round trip to TMEM
 #pragma unroll
-        for (int qb = 0; qb < RQ; qb += FB) {
-          uint32_t d[FB][PD][4];
+        for (int h = 0; h < kHalves; ++h) {
 #pragma unroll
-          for (int c = 0; c < FB; ++c)
+          for (int qb = 0; qb < RQ; qb += FB) {
+            uint32_t d[FB][PD][4];
 #pragma unroll
-            for (int k = 0; k < PD; ++k) tmem_ld4(o_tmem + k * NPAD + (qb + c) * 4, d[c][k]);
-          tc::tmem_ld_wait();
+            for (int c = 0; c < FB; ++c)
 #pragma unroll
-          for (int c = 0; c < FB; ++c) {
+              for (int k = 0; k < PD; ++k) tmem_ld4(o_tmem + h * (PD * NPAD) + k * NPAD + (qb + c) * 4, d[c][k]);
+            tc::tmem_ld_wait();
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int n = (qb + c) * 4 + e;
-              const float alpha_n = __shfl_sync(0xffffffffu, a_l[n >> 5], n & 31);
-              const float unit_n = __shfl_sync(0xffffffffu, unit_l[n >> 5], n & 31);
-              float o = int_to_float(d[c][PD - 1][e]);
+            for (int c = 0; c < FB; ++c) {
 #pragma unroll
-              for (int k = PD - 2; k >= 0; --k) o = fmaf(o, 128.f, int_to_float(d[c][k][e]));
-              acc[n] = fmaf(acc[n], alpha_n, o * unit_n);
+              for (int e = 0; e < 4; ++e) {
+                const int n = (qb + c) * 4 + e;
+                const float alpha_n = __shfl_sync(0xffffffffu, a_l[n >> 5], n & 31);
+                const float unit_n = __shfl_sync(0xffffffffu, unit_l[n >> 5], n & 31);
+                float o = int_to_float(d[c][PD - 1][e]);
+#pragma unroll
+                for (int k = PD - 2; k >= 0; --k) o = fmaf(o, 128.f, int_to_float(d[c][k][e]));
+                acc[h][n] = fmaf(acc[h][n], alpha_n, o * unit_n);
+              }
             }
           }
         }
@@ -779,7 +817,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
         const int it = q >> 1;    // running count of this group's tiles; buffers alternate with it
         const int b = it & 1;
         float* wred_i = wred_g + b * 4 * (NPAD + 1);
-        const uint8_t* scales = smem + L::vstages + (q % NS) * kVStageBytes + kImgBytes;
+        const uint8_t* scales = smem + L::vstages + (q % NS) * kVStageHD + kImgHD;
         const int sb = it % SB;
         ok &= wait_or_abort(&bars[B::s_ready + 2 * g + sb], (it / SB) & 1, abort_flag);
         tc::fence_after_sync();
@@ -902,46 +940,55 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
           if (lane == (n & 31)) wsum[gw * (NPAD + 1) + n] = v;
         }
       }
+      // The P images hold 128 dims of a parked accumulator ([row][128] fp32): a head of 256 dims
+      // goes through them in two rounds.
       float* park = reinterpret_cast<float*>(pimg);
-      if (g == 1) {
 #pragma unroll
-        for (int n = 0; n < NROW; ++n)
-          if (n < rows) park[n * kKeys + gt] = acc[n];
-      }
-      named_barrier(4, kSoftmaxThreads);  // sums, maxima and the parked accumulator visible
-      if (g == 0) {
-        const float* w0 = wred;
-        const float* w1 = wred + 2 * 4 * (NPAD + 1);
-        const float* m0p = mrun;             // running maxima published by the two groups
-        const float* m1p = mrun + 2 * NPAD;
+      for (int h = 0; h < kHalves; ++h) {
+        if (h > 0) named_barrier(4, kSoftmaxThreads);  // the previous round's parked values have been read
+        if (g == 1) {
 #pragma unroll
-        for (int n = 0; n < NROW; ++n) {
-          if (n < rows) {
-            const float l0 = w0[n] + w0[(NPAD + 1) + n] + w0[2 * (NPAD + 1) + n] + w0[3 * (NPAD + 1) + n];
-            const float l1 = w1[n] + w1[(NPAD + 1) + n] + w1[2 * (NPAD + 1) + n] + w1[3 * (NPAD + 1) + n];
-            const float m0 = m0p[n], m1 = m1p[n];
-            const float m = fmaxf(m0, m1);
-            const float c0 = m0 == -INFINITY ? 0.f : fast_exp2(m0 - m);
-            const float c1 = m1 == -INFINITY ? 0.f : fast_exp2(m1 - m);
-            const float l = l0 * c0 + l1 * c1;
-            const float o = acc[n] * c0 + (c1 > 0.f ? park[n * kKeys + gt] * c1 : 0.f);
-            const float val = l > 0.f ? o / l : 0.f;
-            const int token = tok0 + n / p.group, head = kvh * p.group + n % p.group;
-            if (p.num_splits == 1) {
-              store_out_elem(p.out + (int64_t)token * p.out_stride_token + (int64_t)head * p.out_stride_head, gt,
-                             p.out_dtype, val);
-            } else {
-              reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.ws_o) + (int64_t)split * p.ws_o_stride_split +
-                                       (int64_t)token * p.ws_o_stride_token + (int64_t)head * p.ws_o_stride_head)[gt] = val;
-            }
-            if (gt == n) {
-              const float lse2 = l > 0.f ? m + log2f(l) : -INFINITY;
-              if (p.num_splits > 1) {
-                *reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.ws_lse) + (int64_t)split * p.ws_lse_stride_split +
-                                          (int64_t)token * p.ws_lse_stride_token + (int64_t)head * p.ws_lse_stride_head) = lse2;
-              } else if (p.lse_out != nullptr) {
-                *reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.lse_out) + (int64_t)token * p.lse_stride_token +
-                                          (int64_t)head * p.lse_stride_head) = lse2 * kLn2;
+          for (int n = 0; n < NROW; ++n)
+            if (n < rows) park[n * kKeys + gt] = acc[h][n];
+        }
+        named_barrier(4, kSoftmaxThreads);  // sums, maxima and the parked accumulator visible
+        const int d = h * kKeys + gt;       // output column of this thread in this round
+        if (g == 0) {
+          const float* w0 = wred;
+          const float* w1 = wred + 2 * 4 * (NPAD + 1);
+          const float* m0p = mrun;             // running maxima published by the two groups
+          const float* m1p = mrun + 2 * NPAD;
+#pragma unroll
+          for (int n = 0; n < NROW; ++n) {
+            if (n < rows) {
+              const float l0 = w0[n] + w0[(NPAD + 1) + n] + w0[2 * (NPAD + 1) + n] + w0[3 * (NPAD + 1) + n];
+              const float l1 = w1[n] + w1[(NPAD + 1) + n] + w1[2 * (NPAD + 1) + n] + w1[3 * (NPAD + 1) + n];
+              const float m0 = m0p[n], m1 = m1p[n];
+              const float m = fmaxf(m0, m1);
+              const float c0 = m0 == -INFINITY ? 0.f : fast_exp2(m0 - m);
+              const float c1 = m1 == -INFINITY ? 0.f : fast_exp2(m1 - m);
+              const float l = l0 * c0 + l1 * c1;
+              const float o = acc[h][n] * c0 + (c1 > 0.f ? park[n * kKeys + gt] * c1 : 0.f);
+              const float val = l > 0.f ? o / l : 0.f;
+              const int token = tok0 + n / p.group, head = kvh * p.group + n % p.group;
+              if (d < HD) {  // (a head of 64 dims uses half of the group's threads)
+                if (p.num_splits == 1) {
+                  store_out_elem(p.out + (int64_t)token * p.out_stride_token + (int64_t)head * p.out_stride_head, d,
+                                 p.out_dtype, val);
+                } else {
+                  reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.ws_o) + (int64_t)split * p.ws_o_stride_split +
+                                           (int64_t)token * p.ws_o_stride_token + (int64_t)head * p.ws_o_stride_head)[d] = val;
+                }
+              }
+              if (h == 0 && gt == n) {
+                const float lse2 = l > 0.f ? m + log2f(l) : -INFINITY;
+                if (p.num_splits > 1) {
+                  *reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.ws_lse) + (int64_t)split * p.ws_lse_stride_split +
+                                            (int64_t)token * p.ws_lse_stride_token + (int64_t)head * p.ws_lse_stride_head) = lse2;
+                } else if (p.lse_out != nullptr) {
+                  *reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.lse_out) + (int64_t)token * p.lse_stride_token +
+                                            (int64_t)head * p.lse_stride_head) = lse2 * kLn2;
+                }
               }
             }
           }
@@ -965,21 +1012,25 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
   (void)ok;
 }
 
-template <int NPAD, int PD, int NS, int NK, int NR, int SB, int RQ, int NP>
+template <int HD, int NPAD, int PD, int NS, int NK, int NR, int SB, int RQ, int NP>
 cudaError_t launch_cfg(const KernelParams& p, const CUtensorMap& map, int num_ctas, cudaStream_t stream) {
-  constexpr int smem = Layout<NPAD, PD, NS, NK, NR, SB>::total;
+  constexpr int smem = Layout<HD, NPAD, PD, NS, NK, NR, SB>::total;
   static_assert(smem <= 227 * 1024, "shared memory of one CTA");
-  static_assert(Layout<NPAD, PD, NS, NK, NR, SB>::tmem_need <= 512, "TMEM columns");
+  static_assert(Layout<HD, NPAD, PD, NS, NK, NR, SB>::tmem_need <= 512, "TMEM columns");
+  // a head of 64 dims makes the PV instruction read 64 image "rows" past the V image: they
+  // must still be shared memory of this CTA
+  static_assert(HD >= 128 || Layout<HD, NPAD, PD, NS, NK, NR, SB>::vstages + NS * Layout<HD, NPAD, PD, NS, NK, NR, SB>::vstage_bytes +
+                                     8 * kImgChunk <= smem, "reads past the last V image stay inside the CTA's shared memory");
   static bool configured[64] = {};
   int dev = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return err;
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    err = cudaFuncSetAttribute(umma_i8_attention_kernel<NPAD, PD, NS, NK, NR, SB, RQ, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    err = cudaFuncSetAttribute(umma_i8_attention_kernel<HD, NPAD, PD, NS, NK, NR, SB, RQ, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (err != cudaSuccess) return err;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  umma_i8_attention_kernel<NPAD, PD, NS, NK, NR, SB, RQ, NP><<<num_ctas, threads_for(NP), smem, stream>>>(p, map);
+  umma_i8_attention_kernel<HD, NPAD, PD, NS, NK, NR, SB, RQ, NP><<<num_ctas, threads_for(NP), smem, stream>>>(p, map);
   return cudaGetLastError();
 }
 
@@ -989,12 +1040,19 @@ cudaError_t launch_cfg(const KernelParams& p, const CUtensorMap& map, int num_ct
 // (K | k_scale | V | v_scale contiguous, 2 D + 8 bytes, 8-byte aligned), pages of 16 to 128
 // keys whose byte stride is a multiple of 16, and either a slot stride that is a multiple
 // of 16 or cells that are contiguous inside a page, on top of what the tcgen05 kernels
-// need in general.  Queries may be bf16 or fp16 (they become int8 digits either way).
+// need in general.  Queries may be bf16 or fp16 (they become int8 digits either way).  Head
+// sizes 64, 128 and 256; a head of 256 dims takes row tiles of at most 16 rows (its operand
+// images leave room for no more), so at most 16 query heads per KV head.
 bool umma_i8_supports(const KernelParams& p, const char** why) {
   KernelParams pq = p;
   if (pq.q_dtype == PTH_ATTN_F16) pq.q_dtype = PTH_ATTN_BF16;
+  if (pq.head_size == 64 || pq.head_size == 256) pq.head_size = 128;  // the other conditions are the same
   if (!umma_supports(pq, why)) return false;
   const int D = p.head_size;
+  if (p.group > umma_i8_max_rows(D)) {
+    *why = "more query heads per KV head than a row tile of this head size holds";
+    return false;
+  }
   if (p.ks.data != p.k.data + D || p.v.data != p.k.data + D + 4 || p.vs.data != p.k.data + 2 * D + 4 ||
       p.ks.stride_head != p.k.stride_head || p.v.stride_head != p.k.stride_head ||
       p.vs.stride_head != p.k.stride_head) {
@@ -1012,13 +1070,16 @@ bool umma_i8_supports(const KernelParams& p, const char** why) {
   return true;
 }
 
+// Rows (query tokens x query heads per KV head) of the tallest row tile for a head size.
+int umma_i8_max_rows(int head_size) { return head_size == 256 ? 16 : 64; }
+
 // Kernels this launch enqueues and the CTAs of the attention kernel (no device access).
 int umma_i8_num_ctas(const KernelParams& p_in, int sms) {
   KernelParams p = p_in;
   if (p.row_class == 1) {
     p.bq = p.class_rows / p.group > 0 ? p.class_rows / p.group : 1;
   } else {
-    const int cap = 64 / p.group;
+    const int cap = umma_i8_max_rows(p.head_size) / p.group;
     if (p.bq > cap) p.bq = cap;
   }
   const long long items = ((long long)p.num_tokens / p.bq + p.num_reqs) * p.num_kv_heads * p.num_splits;
@@ -1032,7 +1093,7 @@ cudaError_t launch_umma_i8_attention(const KernelParams& p_in, cudaStream_t stre
     // Only requests of at most class_rows rows: each is one row tile.
     p.bq = p.class_rows / p.group > 0 ? p.class_rows / p.group : 1;
   } else {
-    const int cap = 64 / p.group;
+    const int cap = umma_i8_max_rows(p.head_size) / p.group;
     if (p.bq > cap) p.bq = cap;
   }
   p.raw_mode = raw_mode_for(p);
@@ -1052,11 +1113,26 @@ cudaError_t launch_umma_i8_attention(const KernelParams& p_in, cudaStream_t stre
   // Instances by live rows: the softmax code of each handles exactly ceil(rows / 4) row
   // groups, which keeps the decode loop small enough for the instruction cache.
   // The decode instance (rows <= 4) needs few registers and runs two producer groups.
-  if (rows <= 4) return launch_cfg<16, 3, 4, 2, 3, 2, 1, 2>(p, *map, ctas, stream);
-  if (rows <= 8) return launch_cfg<16, 3, 4, 2, 3, 2, 2, 1>(p, *map, ctas, stream);
-  if (rows <= 16) return launch_cfg<16, 3, 4, 2, 3, 2, 4, 1>(p, *map, ctas, stream);
-  if (rows <= 32) return launch_cfg<32, 2, 3, 2, 3, 1, 8, 1>(p, *map, ctas, stream);
-  return launch_cfg<64, 2, 3, 2, 2, 1, 16, 1>(p, *map, ctas, stream);
+  if (p.head_size == 128) {
+    if (rows <= 4) return launch_cfg<128, 16, 3, 4, 2, 3, 2, 1, 2>(p, *map, ctas, stream);
+    if (rows <= 8) return launch_cfg<128, 16, 3, 4, 2, 3, 2, 2, 1>(p, *map, ctas, stream);
+    if (rows <= 16) return launch_cfg<128, 16, 3, 4, 2, 3, 2, 4, 1>(p, *map, ctas, stream);
+    if (rows <= 32) return launch_cfg<128, 32, 2, 3, 2, 3, 1, 8, 1>(p, *map, ctas, stream);
+    return launch_cfg<128, 64, 2, 3, 2, 2, 1, 16, 1>(p, *map, ctas, stream);
+  }
+  if (p.head_size == 64) {
+    // half the bytes per tile: deeper rings keep as many bytes in flight
+    if (rows <= 4) return launch_cfg<64, 16, 3, 4, 2, 6, 2, 1, 2>(p, *map, ctas, stream);
+    if (rows <= 8) return launch_cfg<64, 16, 3, 4, 2, 6, 2, 2, 1>(p, *map, ctas, stream);
+    if (rows <= 16) return launch_cfg<64, 16, 3, 4, 2, 6, 2, 4, 1>(p, *map, ctas, stream);
+    if (rows <= 32) return launch_cfg<64, 32, 2, 3, 2, 6, 1, 8, 1>(p, *map, ctas, stream);
+    return launch_cfg<64, 64, 2, 3, 2, 4, 1, 16, 1>(p, *map, ctas, stream);
+  }
+  // 256 dims: one K image, three V stages and one raw stage of 66 KB fill the shared memory
+  // (two digits of P instead of three make room for the third V stage)
+  if (rows <= 4) return launch_cfg<256, 16, 2, 3, 1, 1, 2, 1, 1>(p, *map, ctas, stream);
+  if (rows <= 8) return launch_cfg<256, 16, 2, 3, 1, 1, 2, 2, 1>(p, *map, ctas, stream);
+  return launch_cfg<256, 16, 2, 3, 1, 1, 2, 4, 1>(p, *map, ctas, stream);
 }
 
 // Reads and clears the integer kernel's status word (device must be idle).

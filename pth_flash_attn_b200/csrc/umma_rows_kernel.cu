@@ -648,6 +648,10 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
 // page copies) and takes bf16 queries.
 bool umma_rows_supports(const KernelParams& p, const char** why) {
   if (!umma_i8_supports(p, why)) return false;
+  if (p.head_size != 128) {
+    *why = "head_size is not 128";
+    return false;
+  }
   if (p.q_dtype != PTH_ATTN_BF16) {
     *why = "q is not bf16";  // the Q image is the query bits as they are, and K / V are widened to bf16
     return false;

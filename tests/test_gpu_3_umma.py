@@ -67,6 +67,26 @@ def test_seeded_shapes(S, qlen, G, bq, kernel):
         check_out(o, ref.out, max_tol=1e-2, mean_tol=1e-3, what="partials")
 
 
+@pytest.mark.parametrize("layout,kernel", [("NHD", k) for k in KERNELS] + [("HND", capi.KERNEL_AUTO)])
+def test_cache_that_starts_8_bytes_off_a_16_byte_boundary(kernel, layout):
+    """Cells are 8-byte aligned, the page copies 16-byte aligned: with the cache 8 bytes off,
+    the first head's cells are the odd ones and the last head's cell ends 8 bytes after the
+    slot stride counted from the copy's first byte.  (Contiguous page runs that are not 16-byte
+    aligned are refused by the TMA kernels: the library's own choice serves them elsewhere.)"""
+    from tests.gpu_util import run_case
+
+    lens, qlens = [700, 130, 20], [4, 4, 4]
+    c = orc.make_paged_cache(lens, 2, 128, 16, layout=layout, pad_page_bytes=64, seed=31, storage_offset_bytes=8)
+    rng = np.random.default_rng(32)
+    q = orc.round_to_bf16(rng.standard_normal((12, 8, 128), dtype=np.float32))
+    qsl = np.array([0, 4, 8, 12])
+    ref = orc.ref_attention_paged(q, c, qsl, 128 ** -0.5)
+    res = run_case(c, q, qsl, 128 ** -0.5, bq=4, num_splits=2, kernel=kernel)
+    assert capi.load_library().device_status() == 0
+    check_out(res["out"], ref.out, what=f"offset 8 {layout}")
+    check_lse(res["lse"], ref.lse, what=f"offset 8 {layout}")
+
+
 def test_matches_scalar_kernel_on_device():
     """The two kernel families agree on a case too large for a comfortable CPU oracle."""
     from tests.gpu_util import run_case
