@@ -45,7 +45,9 @@ sys.path.insert(0, str(REPO))
 HQ, HKV, D, BS = 32, 8, 128, 16
 CELL = 2 * D + 8
 HEADLINE = "long_decode"
-PER_CONFIG = ("decode_small", "long_decode", "verify4", "drafter16", "chunked_prefill", "mixed")
+# the six shapes the reference quotes its numbers on, then decode at the two other head sizes
+PER_CONFIG = ("decode_small", "long_decode", "verify4", "drafter16", "chunked_prefill", "mixed", "decode_d256",
+              "decode_d64")
 TENSOR_BOUND = ("chunked_prefill",)
 
 
@@ -64,6 +66,10 @@ def workload_launches(name: str, seed: int = 1001):
         return [dict(seq_lens=[131072], q_lens=[1], Hq=32, Hkv=8)]
     if name == "long_decode_b64":  # the second launch of the headline alone
         return [dict(seq_lens=[8192] * 64, q_lens=[1] * 64, Hq=32, Hkv=8)]
+    if name == "decode_d256":  # the reference's production shape: 256 dims, 6 query heads per KV head
+        return [dict(seq_lens=[8192] * 64, q_lens=[1] * 64, Hq=12, Hkv=2, D=256)]
+    if name == "decode_d64":  # 64 dims
+        return [dict(seq_lens=[8192] * 64, q_lens=[1] * 64, Hq=32, Hkv=8, D=64)]
     if name == "verify4":  # speculative verification, 4 draft tokens
         return [dict(seq_lens=rng.integers(16384, 32769, size=32).tolist(), q_lens=[4] * 32, Hq=32, Hkv=8)]
     if name == "drafter16":  # windowed drafter, 16 tokens, window 4096
@@ -83,7 +89,7 @@ def kv_bytes(launch, hkv_local):
     w = launch.get("window", 0)
     for L, ql in zip(launch["seq_lens"], launch["q_lens"]):
         vis = L if w <= 0 else min(L, w + ql - 1)
-        total += vis * hkv_local * CELL
+        total += vis * hkv_local * (2 * launch.get("D", D) + 8)
     return total
 
 
@@ -95,7 +101,7 @@ def attn_flops(launch, hq_local):
             pairs = ql * (L - ql) + ql * (ql + 1) // 2
         else:
             pairs = sum(min(L - ql + i + 1, w) for i in range(ql))
-        total += 4 * D * hq_local * pairs
+        total += 4 * launch.get("D", D) * hq_local * pairs
     return total
 
 
@@ -118,6 +124,8 @@ class DeviceLaunch:
         shard = sharding.head_shard(rank, world, launch["Hq"], launch["Hkv"])
         hkv, hq = shard.num_kv_heads, shard.num_q_heads
         self.hkv, self.hq, self.G = hkv, hq, hq // hkv
+        D = self.D = int(launch.get("D", globals()["D"]))
+        CELL = self.cell = 2 * D + 8
         gen = torch.Generator(device="cpu").manual_seed(seed)
         lens, qlens = launch["seq_lens"], launch["q_lens"]
         R, T = len(lens), int(sum(qlens))
@@ -162,7 +170,7 @@ class DeviceLaunch:
         page = BS * hkv * CELL
         self.sets = []
         for s in range(sets):
-            storage = self._quantised_cache(torch, need, hkv, device, seed + 7 * s)
+            storage = self._quantised_cache(torch, need, hkv, device, seed + 7 * s, D)
             perm = torch.randperm(need, generator=gen).to(torch.int32)
             bt = torch.zeros((R, width), dtype=torch.int32)
             k = 0
@@ -196,9 +204,10 @@ class DeviceLaunch:
         self.kernels = self.attention_kernels + self.combine_kernels
 
     @staticmethod
-    def _quantised_cache(torch, num_blocks, hkv, device, seed):
+    def _quantised_cache(torch, num_blocks, hkv, device, seed, D):
         """N(0, 1) K and V quantised per (token, KV head) like the cache writer does (scale =
         max(absmax / 127, 1e-6), round half away from zero), in the packed NHD page layout."""
+        CELL = 2 * D + 8
         gen = torch.Generator(device=device).manual_seed(seed)
         storage = torch.empty(num_blocks * BS * hkv * CELL, dtype=torch.uint8, device=device)
         cells = storage.view(num_blocks, BS, hkv, CELL)
@@ -219,7 +228,7 @@ class DeviceLaunch:
 
         s = self.sets[which % len(self.sets)]
         return host.fill_attn_args(s["q"], self.out if out is None else out, s["views"], s["bt"], s["lens"], s["qsl"],
-                                   bq=self.bq, num_splits=self.S, softmax_scale=D ** -0.5, ws_o=self.ws_o,
+                                   bq=self.bq, num_splits=self.S, softmax_scale=self.D ** -0.5, ws_o=self.ws_o,
                                    ws_lse=self.ws_lse, window=self.window, causal=self.causal)
 
     def launch(self, which=0, lse_out=None):
@@ -227,7 +236,7 @@ class DeviceLaunch:
 
         s = self.sets[which % len(self.sets)]
         host.attention_forward(s["q"], self.out, s["views"], s["bt"], s["lens"], s["qsl"], bq=self.bq,
-                               num_splits=self.S, softmax_scale=D ** -0.5, ws_o=self.ws_o, ws_lse=self.ws_lse,
+                               num_splits=self.S, softmax_scale=self.D ** -0.5, ws_o=self.ws_o, ws_lse=self.ws_lse,
                                window=self.window, causal=self.causal, flags=self.flags, lse_out=lse_out)
 
     def launch_attention_only(self, which=0):
@@ -270,6 +279,7 @@ class DeviceLaunch:
         self.launch(which, lse_out=lse)
         torch.cuda.synchronize()
         storage = s["storage"].cpu().numpy()
+        D, CELL = self.D, self.cell
         page = BS * self.hkv * CELL
         k, v, ks, vs = orc.stream_views(D, self.hkv, BS, "NHD", page, 0)
         lens = np.asarray(self.launch_spec["seq_lens"], dtype=np.int32)
@@ -321,7 +331,7 @@ class Workload:
             d.launch(0)
         torch.cuda.synchronize()
         # the copy ceiling follows the integer kernel: only where that kernel serves the whole launch
-        self.has_copy_ceiling = all(d.attention_kernels == 1 and d.bq * d.G <= 16 for d in self.dls)
+        self.has_copy_ceiling = all(d.attention_kernels == 1 and d.bq * d.G <= 16 and d.D == 128 for d in self.dls)
         if graphs:
             self.graphs = self._capture(lambda d, s: d.launch(s))
             self.attn_graphs = self._capture(lambda d, s: d.launch_attention_only(s))
@@ -359,7 +369,8 @@ class Workload:
 
     def describe(self):
         return [{"batch": len(l["seq_lens"]), "context_max": max(l["seq_lens"]), "q_len": max(l["q_lens"]),
-                 "window": l.get("window", 0), "num_splits_bound": d.S, "bq": d.bq}
+                 "window": l.get("window", 0), "num_splits_bound": d.S, "bq": d.bq, "Hq": l["Hq"], "Hkv": l["Hkv"],
+                 "D": d.D}
                 for l, d in zip(self.launches, self.dls)]
 
     def parity(self):
@@ -622,9 +633,10 @@ def roofline_of(wl, world, attn_ms, pass_ms, hbm_peak, tc_peak, tc_sustained, pe
         # kernel of the pair finds nothing to do)
         rows_kernel = all(d.bq * d.G > 16 and min(d.launch_spec["q_lens"]) * d.G > 16 for d in wl.dls)
         roof = {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
-                "traffic": None if rows_kernel else DRAM_BYTES_PER_ALGORITHMIC_BYTE * wl.bytes_local,
+                "traffic": (DRAM_BYTES_PER_ALGORITHMIC_BYTE * wl.bytes_local
+                            if not rows_kernel and all(d.D == 128 for d in wl.dls) else None),
                 "kernel": "umma_rows_attention_kernel" if rows_kernel else "umma_i8_attention_kernel"}
-        if not rows_kernel:
+        if roof["traffic"] is not None:
             roof["traffic_source"] = "ncu capture of long_decode_b64, scaled by bytes"
     roof.update({"peak_source": peak_src, "kernel_ms_per_pass": attn_ms, "pass_ms": pass_ms,
                  "algorithmic_bytes_per_pass": wl.bytes_local, "flops_per_pass": wl.flops_local,
@@ -733,7 +745,7 @@ def main():
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8" if roof["kernel"].startswith("umma_i8") else "bf16", "data": "synthetic",
         "config": {"workload": args.config, "launches": wl.describe(), "Hq": wl.launches[0]["Hq"],
-                   "Hkv": wl.launches[0]["Hkv"], "D": D, "block_size": BS, "sharding": f"kv_heads/{world}",
+                   "Hkv": wl.launches[0]["Hkv"], "D": wl.launches[0].get("D", D), "block_size": BS, "sharding": f"kv_heads/{world}",
                    "l2_policy": ("inputs larger than L2" if wl.num_sets == 1 else
                                  f"rotation over {wl.num_sets} cache sets (>= 4x L2)"),
                    "cuda_graph": True,
@@ -764,6 +776,9 @@ def main():
                 per[name] = {"ms_per_pass": ms_pass, "kv_gbs": value, "tflops": line["tflops"],
                              "roofline_frac": roof["frac"], "bound": roof["bound"], "kernel_ms_per_pass": attn_ms,
                              "parity_checked": parity["within_tolerance"]}
+                continue
+            if any(l["Hkv"] % world for l in workload_launches(name)):
+                per[name] = {"skipped": f"its KV heads do not divide over {world} ranks"}
                 continue
             w = Workload(torch, name, rank, world, device, num_sms, l2_bytes)
             p1 = timer.passes_per_step(w.run_pass, 5, 0.4)
