@@ -42,7 +42,7 @@ copy_ceiling_kernel(const __grid_constant__ KernelParams p, const __grid_constan
   shape.class_rows = p.class_rows;
   if (tid == 0) {
     for (int s = 0; s < kCopyStages; ++s) {
-      tc::mbar_init(&bars[s], kKvTile >> p.block_shift);
+      tc::mbar_init(&bars[s], kKvTile >> p.copy_shift);
       tc::mbar_init(&bars[kCopyStages + s], 1);
     }
     tc::mbar_init(&item_bar[0], 1);
@@ -70,8 +70,8 @@ copy_ceiling_kernel(const __grid_constant__ KernelParams p, const __grid_constan
 
   if (warp == 0) {
     // ---- items (as the attention kernel's scheduler finds them) and their page copies ----
-    const int S = p.num_splits, hkv = p.num_kv_heads, bs = p.block_size;
-    const int pages_per_tile = kKvTile >> p.block_shift;
+    const int S = p.num_splits, hkv = p.num_kv_heads, bs = p.copy_slots;
+    const int pages_per_tile = kKvTile >> p.copy_shift;
     const uint32_t raw_s = tc::smem_u32(smem);
     int base = 0, blk_total = 0, my_q0 = 0, my_qlen = 0, my_len = 0, my_splits = 1, my_n = 0, my_excl = 0;
     long long blk_first = 0;
@@ -138,7 +138,14 @@ copy_ceiling_kernel(const __grid_constant__ KernelParams p, const __grid_constan
       auto page_block = [&](int tile) -> int {
         const int pos0 = (tile_begin + tile) * kKvTile + lane * bs;
         if (lane >= pages_per_tile || tile >= n_tiles || pos0 >= range_end || pos0 + bs <= range_begin) return -1;
-        return __ldg(bt + (pos0 >> p.block_shift));
+        int page, slot;
+        page_and_slot(p, pos0, &page, &slot);
+        return __ldg(bt + page);
+      };
+      auto first_slot = [&](int tile) -> int {
+        int page, slot;
+        page_and_slot(p, (tile_begin + tile) * kKvTile + lane * bs, &page, &slot);
+        return slot;
       };
       int blk = page_block(0);
 #pragma unroll 1
@@ -152,11 +159,11 @@ copy_ceiling_kernel(const __grid_constant__ KernelParams p, const __grid_constan
             const uint32_t dst = raw_s + rs * kRawStageBytes + lane * bs * kRawRow;
             if (p.raw_mode == 1) {
               mbar_arrive_expect_tx(bar, bs * kRawRow);
-              tma_load_3d(dst, &tmap, tma_x, 0, blk, bar);
+              tma_load_3d(dst, &tmap, tma_x, first_slot(j), blk, bar);
             } else {
               const uint32_t bytes = bs * (2 * p.head_size + 8);
               mbar_arrive_expect_tx(bar, bytes);
-              bulk_copy_g2s(dst, kb + (int64_t)blk * p.k.stride_block, bytes, bar);
+              bulk_copy_g2s(dst, kb + (int64_t)blk * p.k.stride_block + (int64_t)first_slot(j) * (2 * p.head_size + 8), bytes, bar);
             }
           } else {
             mbar_arrive(bar);
@@ -200,6 +207,7 @@ cudaError_t launch_copy_ceiling(const KernelParams& p_in, cudaStream_t stream) {
     const int cap = 64 / p.group;
     if (p.bq > cap) p.bq = cap;
   }
+  set_copy_slots(p, 128);
   p.raw_mode = raw_mode_for(p);
   static const CUtensorMap no_map{};
   const CUtensorMap* map = &no_map;

@@ -25,6 +25,31 @@ constexpr int kRawStageBytes = kRawKeys * kRawRow;          // 34,816 B
 __host__ __device__ constexpr int raw_row_for(int head_size) { return (2 * head_size + 8 + 8 + 15) / 16 * 16; }
 static_assert(raw_row_for(128) == kRawRow, "raw row of head size 128");
 
+// Slots one page copy brings in: the largest power of two from 16 to `most` that divides the
+// page size (0 if there is none).  Pages of 16 to `most` slots that are a power of two are one
+// copy; a page of 816 slots is 51 copies of 16, one of 256 slots two of 128.
+__host__ __device__ inline int copy_slots_for(int block_size, int most) {
+  for (int c = most; c >= 16; c >>= 1)
+    if (block_size % c == 0) return c;
+  return 0;
+}
+inline void set_copy_slots(KernelParams& p, int most) {
+  p.copy_slots = copy_slots_for(p.block_size, most);
+  p.copy_shift = -1;
+  for (int sh = 4; sh <= 7; ++sh)
+    if ((1 << sh) == p.copy_slots) p.copy_shift = sh;
+}
+// Page (row of the block table) and first slot inside it of KV position `pos`.
+__device__ __forceinline__ void page_and_slot(const KernelParams& p, int pos, int* page, int* slot) {
+  if (p.block_shift >= 0) {
+    *page = pos >> p.block_shift;
+    *slot = pos & (p.block_size - 1);
+  } else {
+    *page = pos / p.block_size;
+    *slot = pos - *page * p.block_size;
+  }
+}
+
 __device__ __forceinline__ void named_barrier(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
@@ -129,8 +154,8 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 // Tensor map over the cache as 4-byte elements: [slot bytes / 4][block_size slots][num_blocks],
-// starting at the 16-byte boundary below head 0's first cell; one box = all slots of one page x
-// 272 bytes.  Returns false if the driver refuses the geometry.
+// starting at the 16-byte boundary below head 0's first cell; one box = copy_slots slots of one
+// page x the raw row of the head size.  Returns false if the driver refuses the geometry.
 bool make_page_map(const KernelParams& p, int num_blocks, CUtensorMap* map) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return false;
@@ -140,7 +165,7 @@ bool make_page_map(const KernelParams& p, int num_blocks, CUtensorMap* map) {
   const uintptr_t lead = reinterpret_cast<uintptr_t>(p.k.data) - base;
   const cuuint64_t dims[3] = {(cuuint64_t)((p.k.stride_slot + lead) / 4), (cuuint64_t)p.block_size, (cuuint64_t)num_blocks};
   const cuuint64_t strides[2] = {(cuuint64_t)p.k.stride_slot, (cuuint64_t)p.k.stride_block};
-  const cuuint32_t box[3] = {(cuuint32_t)(raw_row_for(p.head_size) / 4), (cuuint32_t)p.block_size, 1u};
+  const cuuint32_t box[3] = {(cuuint32_t)(raw_row_for(p.head_size) / 4), (cuuint32_t)p.copy_slots, 1u};
   const cuuint32_t elem[3] = {1u, 1u, 1u};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, reinterpret_cast<void*>(base), dims, strides, box, elem,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -158,7 +183,7 @@ const CUtensorMap* cached_page_map(const KernelParams& p) {
   struct Entry {
     uintptr_t base;
     int64_t stride_slot, stride_block;
-    int32_t block_size, num_blocks, head_size;
+    int32_t block_size, num_blocks, head_size, copy_slots;
     CUtensorMap map;
   };
   constexpr int kEntries = 64;
@@ -171,7 +196,8 @@ const CUtensorMap* cached_page_map(const KernelParams& p) {
     for (int i = 0; i < used; ++i) {
       const Entry& e = entries[i];
       if (e.base == base && e.stride_slot == p.k.stride_slot && e.stride_block == p.k.stride_block &&
-          e.block_size == p.block_size && e.num_blocks == p.num_blocks && e.head_size == p.head_size) {
+          e.block_size == p.block_size && e.num_blocks == p.num_blocks && e.head_size == p.head_size &&
+          e.copy_slots == p.copy_slots) {
         return &e.map;
       }
     }
@@ -184,6 +210,7 @@ const CUtensorMap* cached_page_map(const KernelParams& p) {
       e.block_size = p.block_size;
       e.num_blocks = p.num_blocks;
       e.head_size = p.head_size;
+      e.copy_slots = p.copy_slots;
       ++used;
       return &e.map;
     }
@@ -206,14 +233,15 @@ int sm_count() {
 
 // 1 = tiled TMA per page, 2 = bulk copy per contiguous page run, 0 = neither applies.
 int raw_mode_for(const KernelParams& p) {
-  if (p.block_shift < 4 || p.block_shift > 7) return 0;  // 16 .. 128 keys per page, a power of two
+  const int slots = copy_slots_for(p.block_size, 128);  // pages are made of runs of 16 slots or more
+  if (slots == 0) return 0;
   if (p.k.stride_block % 16 != 0) return 0;
   if (p.k.stride_slot == 2 * p.head_size + 8) {
     // A bulk copy starts and ends on 16-byte boundaries: the page run of every head must
     // itself be 16-byte aligned, so that the copy never reads a byte outside the run.
     const bool aligned_runs = reinterpret_cast<uintptr_t>(p.k.data) % 16 == 0 &&
                               (p.num_kv_heads == 1 || p.k.stride_head % 16 == 0) &&
-                              ((int64_t)p.block_size * p.k.stride_slot) % 16 == 0;
+                              ((int64_t)slots * p.k.stride_slot) % 16 == 0;
     return aligned_runs ? 2 : 0;
   }
   if (p.k.stride_slot % 16 == 0 && p.k.stride_slot >= raw_row_for(p.head_size)) return 1;

@@ -46,6 +46,9 @@ struct KernelParams {
   int32_t q_dtype, out_dtype;
   int32_t block_size, num_kv_heads, head_size;
   int32_t block_shift;  // log2(block_size) if it is a power of two, else -1
+  // TMA kernels: slots one page copy brings in (a power of two from 16 to 128 that divides
+  // block_size; a page of more slots is fetched in several copies) and its log2
+  int32_t copy_slots = 0, copy_shift = -1;
   int32_t num_reqs, num_tokens, num_q_heads, group;
   int32_t bq, num_q_tiles, num_splits;
   int32_t window, causal;

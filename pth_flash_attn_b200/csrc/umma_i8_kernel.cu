@@ -222,7 +222,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       tc::mbar_init(&bars[B::p_ready + b], kGroupThreads);
     }
     for (int s = 0; s < kRawStages; ++s) {
-      tc::mbar_init(&bars[B::raw_full + s], kKeys >> p.block_shift);
+      tc::mbar_init(&bars[B::raw_full + s], kKeys >> p.copy_shift);
       tc::mbar_init(&bars[B::raw_free + s], kProducerThreads);
     }
     for (int s = 0; s < kItemSlots; ++s) {
@@ -456,8 +456,8 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     // TMA writes shared memory directly (no L1 staging) and a handful of 4 KB copies per tile
     // keeps tens of KB in flight per SM.  The block id of the next tile's page is fetched
     // before waiting for the raw stage, so the block-table latency is off the refill path.
-    const int pages_per_tile = kKeys >> p.block_shift;
-    const int bs = p.block_size;
+    const int pages_per_tile = kKeys >> p.copy_shift;  // page copies of a tile
+    const int bs = p.copy_slots;                        // slots of one copy
     const uint32_t raw_s = tc::smem_u32(smem + L::raw);
     int g0 = 0;  // running tile count at the start of the item
 #pragma unroll 1
@@ -481,7 +481,15 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
         auto page_block = [&](int tile) -> int {
           const int pos0 = (tile_begin + tile) * kKeys + lane * bs;
           if (tile >= n_tiles || pos0 >= range_end || pos0 + bs <= range_begin) return -1;
-          return __ldg(bt + (pos0 >> p.block_shift));
+          int page, slot;
+          page_and_slot(p, pos0, &page, &slot);
+          return __ldg(bt + page);
+        };
+        // first slot, inside its page, of this lane's copy of a tile
+        auto first_slot = [&](int tile) -> int {
+          int page, slot;
+          page_and_slot(p, (tile_begin + tile) * kKeys + lane * bs, &page, &slot);
+          return slot;
         };
         int blk = page_block(0);
 #pragma unroll 1
@@ -494,11 +502,11 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
             const uint32_t dst = raw_s + rs * kRawStageHD + lane * bs * kRawRowHD;
             if (p.raw_mode == 1) {
               mbar_arrive_expect_tx(bar, bs * kRawRowHD);
-              tma_load_3d(dst, &tmap, tma_x, 0, blk, bar);
+              tma_load_3d(dst, &tmap, tma_x, first_slot(j), blk, bar);
             } else {
               const uint32_t bytes = bs * G::cell;  // a multiple of 16, like the run's address
               mbar_arrive_expect_tx(bar, bytes);
-              bulk_copy_g2s(dst, kb + (int64_t)blk * p.k.stride_block, bytes, bar);
+              bulk_copy_g2s(dst, kb + (int64_t)blk * p.k.stride_block + (int64_t)first_slot(j) * G::cell, bytes, bar);
             }
           } else {
             mbar_arrive(bar);
@@ -519,7 +527,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     // images: with delta = (cell address mod 16) in {0, 8} and D = head size, word w of K block
     // j is raw word delta / 4 + 4 j + w, of V block j raw word delta / 4 + D / 4 + 1 + 4 j + w;
     // the scales are raw words delta / 4 + D / 4 and + D / 2 + 1.
-    const int bs = p.block_size;
+    const int bs = p.copy_slots;  // slots of one page copy
     const int row_pitch = p.raw_mode == 1 ? kRawRowHD : G::cell;
     // Row pt of the operand images holds key `key` of the tile.  With a 264-byte pitch
     // (raw_mode 2) consecutive cells alternate between the two 8-byte alignments: taking the
@@ -527,7 +535,7 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     // code path and its 16-byte loads 528 bytes apart (free of bank conflicts).  The order of
     // the keys inside a tile has no effect on the integer sums; the softmax masks by `key`.
     const int key = tile_key(p, pt);
-    const int my_page = key >> p.block_shift, my_slot = key & (bs - 1);
+    const int my_page = key >> p.copy_shift, my_slot = key & (bs - 1);
     int g0 = 0;
 #pragma unroll 1
     for (int item = 0;; ++item) {
@@ -1037,8 +1045,8 @@ cudaError_t launch_cfg(const KernelParams& p, const CUtensorMap& map, int num_ct
 }  // namespace
 
 // The integer kernel reads whole cache cells through TMA: it needs vLLM's packed cell
-// (K | k_scale | V | v_scale contiguous, 2 D + 8 bytes, 8-byte aligned), pages of 16 to 128
-// keys whose byte stride is a multiple of 16, and either a slot stride that is a multiple
+// (K | k_scale | V | v_scale contiguous, 2 D + 8 bytes, 8-byte aligned), pages of a multiple
+// of 16 keys whose byte stride is a multiple of 16, and either a slot stride that is a multiple
 // of 16 or cells that are contiguous inside a page, on top of what the tcgen05 kernels
 // need in general.  Queries may be bf16 or fp16 (they become int8 digits either way).  Head
 // sizes 64, 128 and 256; a head of 256 dims takes row tiles of at most 16 rows (its operand
@@ -1096,6 +1104,7 @@ cudaError_t launch_umma_i8_attention(const KernelParams& p_in, cudaStream_t stre
     const int cap = umma_i8_max_rows(p.head_size) / p.group;
     if (p.bq > cap) p.bq = cap;
   }
+  set_copy_slots(p, 128);
   p.raw_mode = raw_mode_for(p);
   const CUtensorMap* map = nullptr;
   static const CUtensorMap no_map{};

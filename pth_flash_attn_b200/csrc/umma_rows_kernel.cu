@@ -221,7 +221,7 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
       tc::mbar_init(&bars[B::pv_done + g], 1);
     }
     for (int s = 0; s < kRNR; ++s) {
-      tc::mbar_init(&bars[B::raw_full + s], kHalfKeys >> p.block_shift);  // pages of a half stage
+      tc::mbar_init(&bars[B::raw_full + s], kHalfKeys >> p.copy_shift);  // page copies of a half stage
       tc::mbar_init(&bars[B::raw_free + s], kRProducers / 2);             // 64 K-set + 64 V-set threads
     }
     *abort_flag = 0;
@@ -245,14 +245,14 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
     // (and both scales) into the V stage; thread pt of either set owns key pt of the tile.
     const int pt = tid & 127;
     const bool v_part = warp >= 12;
-    const int bs = p.block_size;
+    const int bs = p.copy_slots;  // slots of one page copy
     const uint8_t* kb = p.k.data + (int64_t)kvh * p.k.stride_head;
     const uint32_t delta = (uint32_t)(reinterpret_cast<uintptr_t>(kb) & 15);
     const int row_pitch = p.raw_mode == 1 ? kRawRow : 2 * kHeadDim + 8;
     // the raw ring is made of half stages of 64 keys: keys 0-63 of tile j are half stage
     // u = 2 j, keys 64-127 are u = 2 j + 1; half stage u sits in slot u % kRNR
     const int half = pt >> 6;
-    const int my_page = (pt & (kHalfKeys - 1)) >> p.block_shift, my_slot = pt & (bs - 1);
+    const int my_page = (pt & (kHalfKeys - 1)) >> p.copy_shift, my_slot = pt & (bs - 1);
     const uint32_t cell_off = my_page * bs * kRawRow + my_slot * row_pitch + delta;  // inside a half stage
     const bool odd = (cell_off & 8u) != 0;
 #pragma unroll 1
@@ -329,9 +329,9 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
     // One TMA copy per KV page of a tile, issued by lane `page`: a tiled tensor-map box of
     // [block_size slots] x [272 bytes] (raw_mode 1) or one bulk copy of a contiguous page
     // run (raw_mode 2); the next tile's block ids are fetched before waiting for the stage.
-    const int pages_per_half = kHalfKeys >> p.block_shift;
+    const int pages_per_half = kHalfKeys >> p.copy_shift;
     if (lane < pages_per_half) {
-      const int bs = p.block_size;
+      const int bs = p.copy_slots;
       const int32_t* bt = p.block_table + (int64_t)t.req * p.block_table_row_stride;
       const uint8_t* kb = p.k.data + (int64_t)kvh * p.k.stride_head;
       const uint32_t delta = (uint32_t)(reinterpret_cast<uintptr_t>(kb) & 15);
@@ -343,7 +343,15 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
       auto page_block = [&](int u) -> int {
         const int pos0 = tile_begin * kTileKeys + u * kHalfKeys + lane * bs;
         if (u >= n_halves || pos0 >= range_end || pos0 + bs <= range_begin) return -1;
-        return __ldg(bt + (pos0 >> p.block_shift));
+        int page, slot;
+        page_and_slot(p, pos0, &page, &slot);
+        return __ldg(bt + page);
+      };
+      // first slot, inside its page, of this lane's copy of half stage u
+      auto first_slot = [&](int u) -> int {
+        int page, slot;
+        page_and_slot(p, tile_begin * kTileKeys + u * kHalfKeys + lane * bs, &page, &slot);
+        return slot;
       };
       int blk = page_block(0);
 #pragma unroll 1
@@ -356,11 +364,11 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
           const uint32_t dst = raw_s + rs * kRawHalfBytes + lane * bs * kRawRow;
           if (p.raw_mode == 1) {
             mbar_arrive_expect_tx(bar, bs * kRawRow);
-            tma_load_3d(dst, &tmap, tma_x, 0, blk, bar);
+            tma_load_3d(dst, &tmap, tma_x, first_slot(u), blk, bar);
           } else {
             const uint32_t bytes = bs * (2 * kHeadDim + 8);  // a multiple of 16, like the run's address
             mbar_arrive_expect_tx(bar, bytes);
-            bulk_copy_g2s(dst, kb + (int64_t)blk * p.k.stride_block, bytes, bar);
+            bulk_copy_g2s(dst, kb + (int64_t)blk * p.k.stride_block + (int64_t)first_slot(u) * (2 * kHeadDim + 8), bytes, bar);
           }
         } else {
           mbar_arrive(bar);
@@ -656,10 +664,6 @@ bool umma_rows_supports(const KernelParams& p, const char** why) {
     *why = "q is not bf16";  // the Q image is the query bits as they are, and K / V are widened to bf16
     return false;
   }
-  if (p.block_shift > 6) {
-    *why = "pages of more than 64 keys";  // a raw half stage holds whole pages of 64 keys in total
-    return false;
-  }
   return true;
 }
 
@@ -686,6 +690,7 @@ cudaError_t launch_umma_rows_attention(const KernelParams& p_in, cudaStream_t st
   // Row tiles of 128 rows, whatever tile height the caller planned with: the partition of
   // the query tokens into row tiles is internal to a launch.
   set_row_tile(p, 128 / p.group > 0 ? 128 / p.group : 1);
+  set_copy_slots(p, kHalfKeys);  // a raw half stage holds whole page copies
   p.raw_mode = raw_mode_for(p);
   p.num_sms = sm_count();
   if (p.num_sms <= 0) return cudaErrorInvalidDevice;

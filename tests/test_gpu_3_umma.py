@@ -196,17 +196,24 @@ def test_mixed_launch_runs_each_request_on_its_kernel(G, S):
             check_out(auto["out"][sl], want["out"][sl], max_tol=1e-2, mean_tol=1e-3, what=f"request {r}")
 
 
+@pytest.mark.parametrize("layout", ["NHD", "HND"])
 @pytest.mark.parametrize("bs,kernel", [(32, capi.KERNEL_UMMA), (64, capi.KERNEL_UMMA), (128, capi.KERNEL_UMMA),
                                        (32, capi.KERNEL_UMMA_ROWS), (64, capi.KERNEL_UMMA_ROWS),
-                                       (48, capi.KERNEL_AUTO), (528, capi.KERNEL_AUTO), (256, capi.KERNEL_AUTO)])
-def test_other_page_sizes(bs, kernel):
-    """Pages of 32, 64 and 128 slots run on the TMA page copies; other sizes (the reference's
-    grid also has 528, 816 and 864, tests/gpu/grid_cases.py:225-245) are served by the kernels
-    that gather key by key, chosen automatically."""
+                                       (128, capi.KERNEL_UMMA_ROWS), (256, capi.KERNEL_UMMA), (256, capi.KERNEL_UMMA_ROWS),
+                                       (528, capi.KERNEL_UMMA), (528, capi.KERNEL_UMMA_ROWS),
+                                       (816, capi.KERNEL_UMMA), (816, capi.KERNEL_UMMA_ROWS),
+                                       (864, capi.KERNEL_UMMA), (864, capi.KERNEL_UMMA_ROWS),
+                                       (48, capi.KERNEL_UMMA), (48, capi.KERNEL_AUTO), (40, capi.KERNEL_AUTO)])
+def test_other_page_sizes(bs, kernel, layout):
+    """Every page size that is a multiple of 16 runs on the TMA page copies: a page is fetched
+    in copies of 16 to 128 slots (the largest power of two that divides it), so the reference's
+    production pages of 816 slots and its grid's 528 and 864 (tests/gpu/grid_cases.py:225-245)
+    are 51, 33 and 27 copies; a tile of 128 keys may straddle two pages.  Other sizes are served
+    by the kernels that gather key by key, chosen automatically."""
     from tests.gpu_util import run_case
 
     lens, qlens = [1500, 257, 40], [4, 4, 4]
-    c = orc.make_paged_cache(lens, 2, 128, bs, seed=60 + bs)
+    c = orc.make_paged_cache(lens, 2, 128, bs, layout=layout, seed=60 + bs)
     rng = np.random.default_rng(61)
     q = orc.round_to_bf16(rng.standard_normal((sum(qlens), 8, 128), dtype=np.float32))
     qsl = np.concatenate([[0], np.cumsum(qlens)]).astype(np.int64)
