@@ -117,6 +117,32 @@ def attention_forward(q, out, cache: CacheViews, block_table, seq_lens, query_st
                 raise RuntimeError(f"pthb200_combine: {lib.last_error()} (code {rc})")
 
 
+def combine_partials(ws_o, ws_lse, out, query_start_loc, *, lse_out=None, lib: capi.B200Lib | None = None) -> None:
+    """Merges ``S`` pieces of every row (``ws_o [S, T, Hq, D]`` fp32, each normalised by its own
+    sum; ``ws_lse [S, T, Hq]`` in log2 units, -inf for a piece without keys) into ``out`` on the
+    current stream: the combine step on its own, for pieces that did not come from one launch."""
+    lib = lib or capi.load_library()
+    S, T, Hq, D = ws_o.shape
+    c = capi.new_combine_args()
+    c.ws_o = ws_o.data_ptr()
+    c.ws_o_stride_split, c.ws_o_stride_token, c.ws_o_stride_head = (s * 4 for s in ws_o.stride()[:3])
+    c.ws_lse = ws_lse.data_ptr()
+    c.ws_lse_stride_split, c.ws_lse_stride_token, c.ws_lse_stride_head = (s * 4 for s in ws_lse.stride()[:3])
+    c.out, c.out_dtype = out.data_ptr(), _DTYPE_CODE[out.dtype]
+    c.out_stride_token = out.stride(0) * out.element_size()
+    c.out_stride_head = out.stride(1) * out.element_size()
+    c.query_start_loc = query_start_loc.data_ptr()
+    c.num_reqs, c.num_tokens, c.num_q_heads, c.head_size, c.num_splits = query_start_loc.shape[0] - 1, T, Hq, D, S
+    opt = capi.make_options()
+    if lse_out is not None:
+        opt.lse_out = lse_out.data_ptr()
+        opt.lse_stride_token, opt.lse_stride_head = lse_out.stride(0) * 4, lse_out.stride(1) * 4
+    with torch.cuda.device(out.device):
+        rc = lib.combine(c, options=opt, stream=torch.cuda.current_stream(out.device).cuda_stream)
+    if rc != capi.OK:
+        raise RuntimeError(f"pthb200_combine: {lib.last_error()} (code {rc})")
+
+
 def write_kv(key, value, cache: CacheViews, slot_mapping, *, lib: capi.B200Lib | None = None) -> None:
     """Quantise ``key`` / ``value`` ``[T, Hkv, D]`` into the cache at ``slot_mapping`` (int64 ``[T]``;
     negative = skip) on the current stream, exactly as the cache format's own writer does."""
