@@ -26,24 +26,28 @@
 //              without keys, and for every other item publishes a descriptor together
 //              with the item's Q digit image, row scales and row masks (two slots, so the
 //              next item is staged while the current one runs);
-//   loader     (1 warp)  lane `page` issues one TMA copy per KV page of a tile - a
-//              [block_size slots] x [272 bytes] box of a tiled tensor map, or a bulk
-//              copy when a page's cells are contiguous - into a ring of NR raw stages;
-//              block ids are fetched one tile ahead;
+//   loader     (1 warp)  lane `c` issues page copy c of a tile - a [copy_slots slots] x
+//              [raw row] box of a tiled tensor map (raw row = the 16-byte aligned bytes
+//              that cover a cell: 144 / 272 / 528 for head sizes 64 / 128 / 256), or a bulk
+//              copy when the cells of a page are contiguous - into a ring of NR raw stages;
+//              copy_slots is the largest power of two from 16 to 128 that divides the page
+//              size, so a page of 816 slots is fetched 16 slots at a time and a tile may
+//              straddle two pages; block ids are fetched one tile ahead;
 //   producers  (NP groups of 4 warps; group k takes the tiles g with g % NP == k)
-//              thread t reads the 272 raw bytes around key t's cell into registers,
+//              thread t reads the raw bytes around key t's cell into registers,
 //              releases the raw stage, and writes them 16 bytes at a time into the
 //              canonical (no-swizzle) operand images: K into a ring of NK K images,
 //              V and the two scale vectors into a ring of NS V stages.  A cell is only
-//              8-byte aligned and V starts 132 bytes into it, which is why the bytes
-//              pass through registers once;
+//              8-byte aligned and V starts D + 4 bytes into it, which is why the bytes
+//              pass through registers once (a 256-dim row in two halves);
 //   MMA issuer (1 thread) per item, in a fixed order: QK(0), QK(1), then QK(i + 2), PV(i);
 //              S^T of a tile lands in one of SB buffers of the tile's softmax group, O^T in
 //              the group's O^T buffer; its commits signal the softmax and free the images;
 //   softmax    (2 groups of 4 warps; group g owns the tiles whose running count is g mod 2,
 //              with its own running maximum, sum and accumulator) thread t owns key t of
 //              S^T (scores -> tile maximum -> probabilities -> digits of P) and output
-//              column d = t of O^T, which it folds tile by tile into an fp32 register
+//              column d = t of O^T (and t + 128 of a 256-dim head, whose O^T is two
+//              accumulators of 128 dims), which it folds tile by tile into an fp32 register
 //              accumulator (acc = acc * alpha + O^T * u), so TMEM never holds a value
 //              that needs rescaling.  Per-row factors live in lanes and travel by
 //              shuffle.  The two groups' states are merged at the end of every item.
