@@ -98,8 +98,13 @@ struct Layout {
   static constexpr int qimg_bytes = G::chunks * 2 * NPAD * 16;
   static constexpr int pimg = qimg + kItemSlots * qimg_bytes;       // [2 groups][PD NPAD / 16][128][16]
   static constexpr int pimg_bytes = 2 * PD * NPAD * kKeys;
-  static constexpr int raw = (pimg + pimg_bytes + 127) / 128 * 128; // [NR][128][raw row] raw cells (TMA destinations: 128-byte aligned)
-  static constexpr int wred = raw + NR * G::raw_stage;              // float [2 groups][2][4][NPAD + 1]
+  // The raw ring is made of NR units of unit_keys keys: whole tiles, or - for 256 dims, whose
+  // tile of raw rows is 66 KB - half tiles, so that a tile and a half can be in flight.
+  static constexpr int raw_units = HD > 128 ? 2 : 1;                // units per tile
+  static constexpr int unit_keys = kKeys / raw_units;
+  static constexpr int unit_bytes = unit_keys * G::raw_row;
+  static constexpr int raw = (pimg + pimg_bytes + 127) / 128 * 128; // [NR] raw units (TMA destinations: 128-byte aligned)
+  static constexpr int wred = raw + NR * unit_bytes;                // float [2 groups][2][4][NPAD + 1]
   static constexpr int mrun = wred + 2 * 2 * 4 * (NPAD + 1) * 4;    // float [2 groups][2 NPAD], first NPAD used
   static constexpr int sq = mrun + 2 * 2 * NPAD * 4;                // float [slots][NPAD]
   static constexpr int rlo = sq + kItemSlots * NPAD * 4;            // int [slots][NPAD]
@@ -116,7 +121,7 @@ struct Layout {
   static constexpr int tmem_alloc = tmem_need <= 32 ? 32 : tmem_need <= 64 ? 64 : tmem_need <= 128 ? 128
                                     : tmem_need <= 256 ? 256 : 512;
   static_assert(sizeof(ItemDesc) % 16 == 0, "descriptor slots stay 16-byte aligned");
-  static_assert(raw % 128 == 0 && G::raw_stage % 128 == 0 && (16 * G::raw_row) % 128 == 0,
+  static_assert(raw % 128 == 0 && unit_bytes % 128 == 0 && (16 * G::raw_row) % 128 == 0,
                 "every page copy of 16 or more slots lands on a 128-byte boundary");
   static_assert(vstages % 16 == 0 && vstage_bytes % 16 == 0 && qimg % 16 == 0 && qimg_bytes % 16 == 0 && pimg % 16 == 0,
                 "operand images start on 16-byte boundaries");
@@ -166,7 +171,10 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
   using L = Layout<HD, NPAD, PD, NS, NK, NR, SB>;
   using B = Bars<NS, NR>;
   using G = I8Geom<HD>;
-  constexpr int kRawRowHD = G::raw_row, kRawStageHD = G::raw_stage, kImgHD = G::img_bytes;
+  constexpr int kRawRowHD = G::raw_row, kRawStageHD = L::unit_bytes, kImgHD = G::img_bytes;
+  constexpr int RU = L::raw_units, kUnitKeys = L::unit_keys;  // raw units per tile, keys per unit
+  // QK runs LA tiles ahead of PV: two when there is a V stage for it, else one
+  constexpr int LA = NS >= 3 ? 2 : 1;
   constexpr int kVStageHD = L::vstage_bytes, kHalves = G::halves;
   constexpr int kRawStages = NR;
   constexpr int XMAX = (1 << (7 * PD)) - 1;
@@ -177,9 +185,9 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
   // arrivals that free an item slot: every softmax and producer thread, the issuer, the loader
   constexpr int kItemReaders = kSoftmaxThreads + NP * kProducerThreads + 2;
   static_assert(RQ >= 1 && 4 * RQ <= NPAD, "RQ = groups of four rows the softmax handles (rows <= 4 RQ)");
-  // QK runs two tiles ahead of PV (see the issuer): QK(i + 2) needs the V stage of tile i + 2
-  // filled, which with two stages would be the one PV(i), issued after it, has yet to free.
-  static_assert(NS >= 3, "QK(i + 2) is issued before PV(i): tile i + 2 needs a V stage of its own");
+  // QK(i + LA) is issued before PV(i) (see the issuer) and needs the V stage of tile i + LA
+  // filled: with LA + 1 stages or more that is never the one PV(i) has yet to free.
+  static_assert(NS >= LA + 1 && NS >= 2, "tile i + LA needs a V stage of its own");
   static_assert(PD * NPAD >= 8 * RQ, "the P images hold 128 dims of the parked accumulator of one softmax group");
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* pimg = smem + L::pimg;
@@ -226,8 +234,8 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       tc::mbar_init(&bars[B::p_ready + b], kGroupThreads);
     }
     for (int s = 0; s < kRawStages; ++s) {
-      tc::mbar_init(&bars[B::raw_full + s], kKeys >> p.copy_shift);
-      tc::mbar_init(&bars[B::raw_free + s], kProducerThreads);
+      tc::mbar_init(&bars[B::raw_full + s], kUnitKeys >> p.copy_shift);  // page copies of a unit
+      tc::mbar_init(&bars[B::raw_free + s], kProducerThreads / RU);       // the threads whose keys are in the unit
     }
     for (int s = 0; s < kItemSlots; ++s) {
       tc::mbar_init(&bars[B::item_full + s], 32);
@@ -460,8 +468,8 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     // TMA writes shared memory directly (no L1 staging) and a handful of 4 KB copies per tile
     // keeps tens of KB in flight per SM.  The block id of the next tile's page is fetched
     // before waiting for the raw stage, so the block-table latency is off the refill path.
-    const int pages_per_tile = kKeys >> p.copy_shift;  // page copies of a tile
-    const int bs = p.copy_slots;                        // slots of one copy
+    const int pages_per_unit = kUnitKeys >> p.copy_shift;  // page copies of a raw unit (a tile, or half of one)
+    const int bs = p.copy_slots;                            // slots of one copy
     const uint32_t raw_s = tc::smem_u32(smem + L::raw);
     int g0 = 0;  // running tile count at the start of the item
 #pragma unroll 1
@@ -471,9 +479,10 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
       if (!ok) break;
       const int n_tiles = descs[slot].n_tiles;
       if (n_tiles == 0) break;
-      if (lane < pages_per_tile) {
+      if (lane < pages_per_unit) {
         const int tile_begin = descs[slot].tile_begin, range_begin = descs[slot].range_begin,
                   range_end = descs[slot].range_end;
+        const int n_units = n_tiles * RU;
         const int32_t* bt = p.block_table + (int64_t)descs[slot].req * p.block_table_row_stride;
         const uint8_t* kb = p.k.data + (int64_t)descs[slot].kvh * p.k.stride_head;
         const uint32_t delta = (uint32_t)(reinterpret_cast<uintptr_t>(kb) & 15);
@@ -481,36 +490,36 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
         // 16-byte boundary below head 0's first cell
         const int tma_x = (int)((reinterpret_cast<uintptr_t>(kb) - delta -
                                  (reinterpret_cast<uintptr_t>(p.k.data) & ~(uintptr_t)15)) >> 2);
-        // block id of this lane's page of a tile, -1 if no key of the page is in range
-        auto page_block = [&](int tile) -> int {
-          const int pos0 = (tile_begin + tile) * kKeys + lane * bs;
-          if (tile >= n_tiles || pos0 >= range_end || pos0 + bs <= range_begin) return -1;
+        // block id of this lane's copy of unit v of the item, -1 if no key of the copy is in range
+        auto page_block = [&](int v) -> int {
+          const int pos0 = tile_begin * kKeys + v * kUnitKeys + lane * bs;
+          if (v >= n_units || pos0 >= range_end || pos0 + bs <= range_begin) return -1;
           int page, slot;
           page_and_slot(p, pos0, &page, &slot);
           return __ldg(bt + page);
         };
-        // first slot, inside its page, of this lane's copy of a tile
-        auto first_slot = [&](int tile) -> int {
+        // first slot, inside its page, of this lane's copy of unit v
+        auto first_slot = [&](int v) -> int {
           int page, slot;
-          page_and_slot(p, (tile_begin + tile) * kKeys + lane * bs, &page, &slot);
+          page_and_slot(p, tile_begin * kKeys + v * kUnitKeys + lane * bs, &page, &slot);
           return slot;
         };
         int blk = page_block(0);
 #pragma unroll 1
-        for (int j = 0; j < n_tiles; ++j) {
-          const int blk_next = page_block(j + 1);
-          const int g = g0 + j, rs = g % kRawStages;
-          if (g >= kRawStages) ok &= wait_or_abort(&bars[B::raw_free + rs], ((g / kRawStages) - 1) & 1, abort_flag);
+        for (int v = 0; v < n_units; ++v) {
+          const int blk_next = page_block(v + 1);
+          const int u = g0 * RU + v, rs = u % kRawStages;  // running unit count, ring slot
+          if (u >= kRawStages) ok &= wait_or_abort(&bars[B::raw_free + rs], ((u / kRawStages) - 1) & 1, abort_flag);
           uint64_t* bar = &bars[B::raw_full + rs];
           if (blk >= 0 && ok) {
             const uint32_t dst = raw_s + rs * kRawStageHD + lane * bs * kRawRowHD;
             if (p.raw_mode == 1) {
               mbar_arrive_expect_tx(bar, bs * kRawRowHD);
-              tma_load_3d(dst, &tmap, tma_x, first_slot(j), blk, bar);
+              tma_load_3d(dst, &tmap, tma_x, first_slot(v), blk, bar);
             } else {
               const uint32_t bytes = bs * G::cell;  // a multiple of 16, like the run's address
               mbar_arrive_expect_tx(bar, bytes);
-              bulk_copy_g2s(dst, kb + (int64_t)blk * p.k.stride_block + (int64_t)first_slot(j) * G::cell, bytes, bar);
+              bulk_copy_g2s(dst, kb + (int64_t)blk * p.k.stride_block + (int64_t)first_slot(v) * G::cell, bytes, bar);
             }
           } else {
             mbar_arrive(bar);
@@ -539,7 +548,8 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     // code path and its 16-byte loads 528 bytes apart (free of bank conflicts).  The order of
     // the keys inside a tile has no effect on the integer sums; the softmax masks by `key`.
     const int key = tile_key(p, pt);
-    const int my_page = key >> p.copy_shift, my_slot = key & (bs - 1);
+    const int unit_of_key = key / kUnitKeys;  // raw unit of the tile that holds this key (warp-uniform)
+    const int my_page = (key % kUnitKeys) >> p.copy_shift, my_slot = key & (bs - 1);
     int g0 = 0;
 #pragma unroll 1
     for (int item = 0;; ++item) {
@@ -559,17 +569,19 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
 #pragma unroll 1
       for (; j < n_tiles; j += NP) {
         const int g = g0 + j;  // running tile count: indexes every ring
-        const int rs = g % kRawStages;
+        const int u = g * RU + unit_of_key;  // running count of raw units
+        const int rs = u % kRawStages;
         const int pos = (tile_begin + j) * kKeys + key;
         const bool valid = pos >= range_begin && pos < range_end;
-        if constexpr (NP > 1) {
-          // A raw stage is shared by the producer groups in turn (NR is not a multiple of NP).
-          // A parity wait only tells apart two consecutive phases, so this group must not look
-          // at raw_full[rs] while the stage's PREVIOUS tile (another group's) is still pending:
-          // first wait until that tile has been taken out of the stage.
-          if (g >= kRawStages) ok &= wait_or_abort(&bars[B::raw_free + rs], ((g / kRawStages) - 1) & 1, abort_flag);
+        if constexpr (NP > 1 || RU > 1) {
+          // A raw slot is used in turn by the producer groups (NR is not a multiple of NP) or by
+          // the threads of the two half tiles (NR is odd).  A parity wait only tells apart two
+          // consecutive phases, so these threads must not look at raw_full[rs] while the slot's
+          // PREVIOUS occupant (somebody else's) is still pending: first wait until that one
+          // has been taken out of the slot.
+          if (u >= kRawStages) ok &= wait_or_abort(&bars[B::raw_free + rs], ((u / kRawStages) - 1) & 1, abort_flag);
         }
-        ok &= wait_or_abort(&bars[B::raw_full + rs], (g / kRawStages) & 1, abort_flag);
+        ok &= wait_or_abort(&bars[B::raw_full + rs], (u / kRawStages) & 1, abort_flag);
         // The 16-byte pieces from the boundary below the cell: pieces 0 .. D / 16 hold K and
         // k_scale, pieces D / 16 .. D / 8 hold k_scale, V and v_scale.  Up to head size 128 both
         // sets are read before the raw stage is released; a 256-dim row is too long for that
@@ -654,7 +666,8 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
     // ONE thread (the lane elect.sync picks) issues every tcgen05.mma of the CTA, item after item, inside an item
     // in a fixed order (two issuing threads, one for QK and one for PV, produced rare
     // run-to-run differences):
-    //   QK(0), QK(1), then for i = 0, 1, ...: QK(i + 2), PV(i).
+    //   QK(0), QK(1), then for i = 0, 1, ...: QK(i + 2), PV(i)
+    // (with only two V stages - the 256-dim instances - QK runs one tile ahead instead of two).
     // With g = running tile count of tile i:
     //   QK(i): the tile belongs to softmax group g & 1, is that group's k-th tile (k = g >> 1)
     //          and lands in its S^T buffer k % SB; needs the tile's images (full) and that
@@ -721,11 +734,12 @@ umma_i8_attention_kernel(const __grid_constant__ KernelParams p, const __grid_co
         }
         return ready;
       };
-      go = qk_step(g0);
-      if (go && n_tiles > 1) go = qk_step(g0 + 1);
+#pragma unroll
+      for (int a = 0; a < LA; ++a)
+        if (go && a < n_tiles) go = qk_step(g0 + a);
 #pragma unroll 1
       for (int i = 0; i < n_tiles && go; ++i) {
-        if (i + 2 < n_tiles) go = qk_step(g0 + i + 2);
+        if (i + LA < n_tiles) go = qk_step(g0 + i + LA);
         if (go) go = pv_step(g0 + i);
       }
       g0 += n_tiles;
@@ -1108,7 +1122,7 @@ cudaError_t launch_umma_i8_attention(const KernelParams& p_in, cudaStream_t stre
     const int cap = umma_i8_max_rows(p.head_size) / p.group;
     if (p.bq > cap) p.bq = cap;
   }
-  set_copy_slots(p, 128);
+  set_copy_slots(p, p.head_size == 256 ? 64 : 128);  // a raw unit (a tile; half a tile at 256 dims) holds whole copies
   p.raw_mode = raw_mode_for(p);
   const CUtensorMap* map = nullptr;
   static const CUtensorMap no_map{};
@@ -1141,11 +1155,11 @@ cudaError_t launch_umma_i8_attention(const KernelParams& p_in, cudaStream_t stre
     if (rows <= 32) return launch_cfg<64, 32, 2, 3, 2, 6, 1, 8, 1>(p, *map, ctas, stream);
     return launch_cfg<64, 64, 2, 3, 2, 4, 1, 16, 1>(p, *map, ctas, stream);
   }
-  // 256 dims: one K image, three V stages and one raw stage of 66 KB fill the shared memory
-  // (two digits of P instead of three make room for the third V stage)
-  if (rows <= 4) return launch_cfg<256, 16, 2, 3, 1, 1, 2, 1, 1>(p, *map, ctas, stream);
-  if (rows <= 8) return launch_cfg<256, 16, 2, 3, 1, 1, 2, 2, 1>(p, *map, ctas, stream);
-  return launch_cfg<256, 16, 2, 3, 1, 1, 2, 4, 1>(p, *map, ctas, stream);
+  // 256 dims: one K image, two V stages (QK one tile ahead of PV) and a raw ring of three half
+  // tiles of 33 KB - a tile and a half of cache bytes in flight - fill the shared memory
+  if (rows <= 4) return launch_cfg<256, 16, 2, 2, 1, 3, 2, 1, 1>(p, *map, ctas, stream);
+  if (rows <= 8) return launch_cfg<256, 16, 2, 2, 1, 3, 2, 2, 1>(p, *map, ctas, stream);
+  return launch_cfg<256, 16, 2, 2, 1, 3, 2, 4, 1>(p, *map, ctas, stream);
 }
 
 // Reads and clears the integer kernel's status word (device must be idle).
