@@ -66,8 +66,8 @@ def workload_launches(name: str, seed: int = 1001):
         return [dict(seq_lens=[131072], q_lens=[1], Hq=32, Hkv=8)]
     if name == "long_decode_b64":  # the second launch of the headline alone
         return [dict(seq_lens=[8192] * 64, q_lens=[1] * 64, Hq=32, Hkv=8)]
-    if name == "decode_d256":  # the reference's production shape: 256 dims, 6 query heads per KV head
-        return [dict(seq_lens=[8192] * 64, q_lens=[1] * 64, Hq=12, Hkv=2, D=256)]
+    if name == "decode_d256":  # the reference's production shape: 256 dims, 6 query heads per KV head, pages of 816 slots
+        return [dict(seq_lens=[8192] * 64, q_lens=[1] * 64, Hq=12, Hkv=2, D=256, block_size=816)]
     if name == "decode_d64":  # 64 dims
         return [dict(seq_lens=[8192] * 64, q_lens=[1] * 64, Hq=32, Hkv=8, D=64)]
     if name == "verify4":  # speculative verification, 4 draft tokens
@@ -126,6 +126,7 @@ class DeviceLaunch:
         self.hkv, self.hq, self.G = hkv, hq, hq // hkv
         D = self.D = int(launch.get("D", globals()["D"]))
         CELL = self.cell = 2 * D + 8
+        BS = self.block_size = int(launch.get("block_size", globals()["BS"]))
         gen = torch.Generator(device="cpu").manual_seed(seed)
         lens, qlens = launch["seq_lens"], launch["q_lens"]
         R, T = len(lens), int(sum(qlens))
@@ -170,7 +171,7 @@ class DeviceLaunch:
         page = BS * hkv * CELL
         self.sets = []
         for s in range(sets):
-            storage = self._quantised_cache(torch, need, hkv, device, seed + 7 * s, D)
+            storage = self._quantised_cache(torch, need, hkv, device, seed + 7 * s, D, BS)
             perm = torch.randperm(need, generator=gen).to(torch.int32)
             bt = torch.zeros((R, width), dtype=torch.int32)
             k = 0
@@ -204,7 +205,7 @@ class DeviceLaunch:
         self.kernels = self.attention_kernels + self.combine_kernels
 
     @staticmethod
-    def _quantised_cache(torch, num_blocks, hkv, device, seed, D):
+    def _quantised_cache(torch, num_blocks, hkv, device, seed, D, BS):
         """N(0, 1) K and V quantised per (token, KV head) like the cache writer does (scale =
         max(absmax / 127, 1e-6), round half away from zero), in the packed NHD page layout."""
         CELL = 2 * D + 8
@@ -279,7 +280,7 @@ class DeviceLaunch:
         self.launch(which, lse_out=lse)
         torch.cuda.synchronize()
         storage = s["storage"].cpu().numpy()
-        D, CELL = self.D, self.cell
+        D, CELL, BS = self.D, self.cell, self.block_size
         page = BS * self.hkv * CELL
         k, v, ks, vs = orc.stream_views(D, self.hkv, BS, "NHD", page, 0)
         lens = np.asarray(self.launch_spec["seq_lens"], dtype=np.int32)
@@ -370,7 +371,7 @@ class Workload:
     def describe(self):
         return [{"batch": len(l["seq_lens"]), "context_max": max(l["seq_lens"]), "q_len": max(l["q_lens"]),
                  "window": l.get("window", 0), "num_splits_bound": d.S, "bq": d.bq, "Hq": l["Hq"], "Hkv": l["Hkv"],
-                 "D": d.D}
+                 "D": d.D, "block_size": d.block_size}
                 for l, d in zip(self.launches, self.dls)]
 
     def parity(self):
@@ -745,7 +746,7 @@ def main():
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8" if roof["kernel"].startswith("umma_i8") else "bf16", "data": "synthetic",
         "config": {"workload": args.config, "launches": wl.describe(), "Hq": wl.launches[0]["Hq"],
-                   "Hkv": wl.launches[0]["Hkv"], "D": wl.launches[0].get("D", D), "block_size": BS, "sharding": f"kv_heads/{world}",
+                   "Hkv": wl.launches[0]["Hkv"], "D": wl.launches[0].get("D", D), "block_size": wl.launches[0].get("block_size", BS), "sharding": f"kv_heads/{world}",
                    "l2_policy": ("inputs larger than L2" if wl.num_sets == 1 else
                                  f"rotation over {wl.num_sets} cache sets (>= 4x L2)"),
                    "cuda_graph": True,
