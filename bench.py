@@ -66,8 +66,8 @@ def workload_launches(name: str, seed: int = 1001):
         return [dict(seq_lens=[131072], q_lens=[1], Hq=32, Hkv=8)]
     if name == "long_decode_b64":  # the second launch of the headline alone
         return [dict(seq_lens=[8192] * 64, q_lens=[1] * 64, Hq=32, Hkv=8)]
-    if name == "decode_d256":  # the reference's production shape: 256 dims, 6 query heads per KV head, pages of 816 slots
-        return [dict(seq_lens=[8192] * 64, q_lens=[1] * 64, Hq=12, Hkv=2, D=256, block_size=816)]
+    if name == "decode_d256":  # the reference's production shape: 256 dims, 6 query heads per KV head, HND pages of 816 slots
+        return [dict(seq_lens=[8192] * 64, q_lens=[1] * 64, Hq=12, Hkv=2, D=256, block_size=816, layout="HND")]
     if name == "decode_d64":  # 64 dims
         return [dict(seq_lens=[8192] * 64, q_lens=[1] * 64, Hq=32, Hkv=8, D=64)]
     if name == "verify4":  # speculative verification, 4 draft tokens
@@ -127,6 +127,7 @@ class DeviceLaunch:
         D = self.D = int(launch.get("D", globals()["D"]))
         CELL = self.cell = 2 * D + 8
         BS = self.block_size = int(launch.get("block_size", globals()["BS"]))
+        self.layout = launch.get("layout", "NHD")   # HND: the slots of a head together (vLLM's packed page)
         gen = torch.Generator(device="cpu").manual_seed(seed)
         lens, qlens = launch["seq_lens"], launch["q_lens"]
         R, T = len(lens), int(sum(qlens))
@@ -187,7 +188,7 @@ class DeviceLaunch:
             stage_dev = stage_host.to(device)
             dq, dbt, dlen, dqsl = carve(stage_dev)
             base = storage.data_ptr()
-            slot, head = hkv * CELL, CELL
+            slot, head = (hkv * CELL, CELL) if self.layout == "NHD" else (CELL, BS * CELL)
             views = host.CacheViews((base, page, slot, head), (base + D + 4, page, slot, head),
                                     (base + D, page, slot, head), (base + 2 * D + 4, page, slot, head),
                                     need, BS, hkv, D)
@@ -207,7 +208,9 @@ class DeviceLaunch:
     @staticmethod
     def _quantised_cache(torch, num_blocks, hkv, device, seed, D, BS):
         """N(0, 1) K and V quantised per (token, KV head) like the cache writer does (scale =
-        max(absmax / 127, 1e-6), round half away from zero), in the packed NHD page layout."""
+        max(absmax / 127, 1e-6), round half away from zero), one packed cell per (block, slot,
+        head); the cells are independent random rows, so the same bytes serve as an NHD or an
+        HND page (the views decide which cell is which slot and head)."""
         CELL = 2 * D + 8
         gen = torch.Generator(device=device).manual_seed(seed)
         storage = torch.empty(num_blocks * BS * hkv * CELL, dtype=torch.uint8, device=device)
@@ -282,11 +285,11 @@ class DeviceLaunch:
         storage = s["storage"].cpu().numpy()
         D, CELL, BS = self.D, self.cell, self.block_size
         page = BS * self.hkv * CELL
-        k, v, ks, vs = orc.stream_views(D, self.hkv, BS, "NHD", page, 0)
+        k, v, ks, vs = orc.stream_views(D, self.hkv, BS, self.layout, page, 0)
         lens = np.asarray(self.launch_spec["seq_lens"], dtype=np.int32)
         cache = orc.PagedInt8Cache(storage=storage, k=k, v=v, ks=ks, vs=vs, block_table=s["bt"].cpu().numpy(),
                                    seq_lens=lens, num_blocks=s["views"].num_blocks, block_size=BS, Hkv=self.hkv,
-                                   D=D, layout="NHD", page_bytes=page, storage_offset_bytes=0)
+                                   D=D, layout=self.layout, page_bytes=page, storage_offset_bytes=0)
         qsl = s["qsl"].cpu().numpy().astype(np.int64)
         rng = np.random.default_rng(seed)
         reqs = {int(np.argmax(lens)), int(np.argmin(lens)), 0, self.R - 1}
@@ -371,7 +374,7 @@ class Workload:
     def describe(self):
         return [{"batch": len(l["seq_lens"]), "context_max": max(l["seq_lens"]), "q_len": max(l["q_lens"]),
                  "window": l.get("window", 0), "num_splits_bound": d.S, "bq": d.bq, "Hq": l["Hq"], "Hkv": l["Hkv"],
-                 "D": d.D, "block_size": d.block_size}
+                 "D": d.D, "block_size": d.block_size, "layout": d.layout}
                 for l, d in zip(self.launches, self.dls)]
 
     def parity(self):

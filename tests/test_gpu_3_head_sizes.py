@@ -89,8 +89,9 @@ def test_page_sizes(D, block_size):
     """816 slots per page, 256 dims and 6 query heads per KV head is the reference's production
     shape (README.md:279-289)."""
     lens = [1000, 300]
-    c, q, qsl = _seeded(lens, [1, 3], 12, 2, D, seed=600 + block_size, block_size=block_size)
-    _check(c, q, qsl, D, f"D{D} pages of {block_size}", bq=2, S=2)
+    for layout in ("NHD", "HND"):
+        c, q, qsl = _seeded(lens, [1, 3], 12, 2, D, seed=600 + block_size, block_size=block_size, layout=layout)
+        _check(c, q, qsl, D, f"D{D} {layout} pages of {block_size}", bq=2, S=2)
 
 
 @pytest.mark.parametrize("D", [64, 256])
