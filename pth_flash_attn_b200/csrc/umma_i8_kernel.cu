@@ -1067,8 +1067,8 @@ cudaError_t launch_cfg(const KernelParams& p, const CUtensorMap& map, int num_ct
 // of 16 keys whose byte stride is a multiple of 16, and either a slot stride that is a multiple
 // of 16 or cells that are contiguous inside a page, on top of what the tcgen05 kernels
 // need in general.  Queries may be bf16 or fp16 (they become int8 digits either way).  Head
-// sizes 64, 128 and 256; a head of 256 dims takes row tiles of at most 16 rows (its operand
-// images leave room for no more), so at most 16 query heads per KV head.
+// sizes 64, 128 and 256; a head of 256 dims takes row tiles of at most 32 rows (its operand
+// images leave room for no more), so at most 32 query heads per KV head.
 bool umma_i8_supports(const KernelParams& p, const char** why) {
   KernelParams pq = p;
   if (pq.q_dtype == PTH_ATTN_F16) pq.q_dtype = PTH_ATTN_BF16;
@@ -1097,7 +1097,7 @@ bool umma_i8_supports(const KernelParams& p, const char** why) {
 }
 
 // Rows (query tokens x query heads per KV head) of the tallest row tile for a head size.
-int umma_i8_max_rows(int head_size) { return head_size == 256 ? 16 : 64; }
+int umma_i8_max_rows(int head_size) { return head_size == 256 ? 32 : 64; }
 
 // Kernels this launch enqueues and the CTAs of the attention kernel (no device access).
 int umma_i8_num_ctas(const KernelParams& p_in, int sms) {
@@ -1159,7 +1159,10 @@ cudaError_t launch_umma_i8_attention(const KernelParams& p_in, cudaStream_t stre
   // tiles of 33 KB - a tile and a half of cache bytes in flight - fill the shared memory
   if (rows <= 4) return launch_cfg<256, 16, 2, 2, 1, 3, 2, 1, 1>(p, *map, ctas, stream);
   if (rows <= 8) return launch_cfg<256, 16, 2, 2, 1, 3, 2, 2, 1>(p, *map, ctas, stream);
-  return launch_cfg<256, 16, 2, 2, 1, 3, 2, 4, 1>(p, *map, ctas, stream);
+  if (rows <= 16) return launch_cfg<256, 16, 2, 2, 1, 3, 2, 4, 1>(p, *map, ctas, stream);
+  // up to 32 rows (prefill chunks cut into row tiles of 32 / G tokens): the wider Q and P images
+  // leave room for two raw half tiles, one S^T buffer per group
+  return launch_cfg<256, 32, 2, 2, 1, 2, 1, 8, 1>(p, *map, ctas, stream);
 }
 
 // Reads and clears the integer kernel's status word (device must be idle).

@@ -7,8 +7,8 @@ D = 256 with 6 query heads per KV head.  The cases here force the integer kernel
 the same gate against the fp64 oracle as head size 128: decode, verification and drafter
 shapes, split-KV partials, sliding windows and non-causal ranges, both page layouts and both
 TMA paths (tensor-map boxes and bulk copies of a contiguous page run), fp16 queries, page
-sizes 16 to 128, and row tiles up to what each head size holds (64 rows at D = 64, 16 at
-D = 256).
+sizes that are multiples of 16, and row tiles up to what each head size holds (64 rows at
+D = 64, 32 at D = 256).
 """
 import numpy as np
 import pytest
@@ -65,8 +65,8 @@ def test_tall_row_tiles_at_64_dims(qlen, G, bq):
     _check(c, q, qsl, 64, f"D64 rows {bq * G}", bq=bq, S=2)
 
 
-def test_prefill_chunk_at_256_dims_is_cut_into_row_tiles_of_16_rows():
-    """A chunk of 37 tokens x 6 heads: the kernel lowers the tile height to two tokens."""
+def test_prefill_chunk_at_256_dims_is_cut_into_row_tiles_of_32_rows():
+    """A chunk of 37 tokens x 6 heads: the kernel lowers the tile height to five tokens."""
     lens = [500, 90]
     c, q, qsl = _seeded(lens, [37, 5], 12, 2, 256, seed=77)
     _check(c, q, qsl, 256, "D256 chunk", bq=8, S=1)
@@ -140,11 +140,18 @@ def test_results_do_not_change_from_run_to_run(D):
         assert (res["out_bytes"] == first).all()
 
 
-def test_head_size_256_refuses_more_than_16_query_heads_per_kv_head():
+def test_head_size_256_refuses_more_than_32_query_heads_per_kv_head():
     from tests.gpu_util import run_case
 
-    c, q, qsl = _seeded([100], [1], 32, 1, 256, seed=5)
+    c, q, qsl = _seeded([100], [1], 64, 1, 256, seed=5)
     with pytest.raises(Exception, match="row tile"):
         run_case(c, q, qsl, 256 ** -0.5, bq=1, kernel=capi.KERNEL_UMMA)
     # the library's own choice serves the launch on CUDA cores
-    _check(c, q, qsl, 256, "G 32", bq=1, kernel=capi.KERNEL_AUTO)
+    _check(c, q, qsl, 256, "G 64", bq=1, kernel=capi.KERNEL_AUTO)
+
+
+@pytest.mark.parametrize("qlen,G,bq", [(1, 32, 1), (5, 6, 5), (8, 4, 8), (3, 8, 3)])
+def test_row_tiles_of_17_to_32_rows_at_256_dims(qlen, G, bq):
+    lens = [900, 300 + qlen, qlen]
+    c, q, qsl = _seeded(lens, [qlen] * 3, 2 * G, 2, 256, seed=1200 + qlen)
+    _check(c, q, qsl, 256, f"D256 rows {bq * G}", bq=bq, S=2)
