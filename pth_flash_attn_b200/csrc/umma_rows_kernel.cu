@@ -656,8 +656,8 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
 // page copies) and takes bf16 queries.
 bool umma_rows_supports(const KernelParams& p, const char** why) {
   if (!umma_i8_supports(p, why)) return false;
-  if (p.head_size != 128) {
-    *why = "head_size is not 128";
+  if (p.head_size != 128 && p.head_size != 256) {
+    *why = "head_size is not 128 or 256";  // (256 dims: umma_rows256_kernel.cu)
     return false;
   }
   if (p.q_dtype != PTH_ATTN_BF16) {
@@ -686,6 +686,7 @@ cudaError_t launch_rows(const KernelParams& p, const CUtensorMap& map, dim3 grid
 }  // namespace
 
 cudaError_t launch_umma_rows_attention(const KernelParams& p_in, cudaStream_t stream) {
+  if (p_in.head_size == 256) return launch_umma_rows256_attention(p_in, stream);
   KernelParams p = p_in;
   // Row tiles of 128 rows, whatever tile height the caller planned with: the partition of
   // the query tokens into row tiles is internal to a launch.
