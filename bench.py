@@ -45,9 +45,10 @@ sys.path.insert(0, str(REPO))
 HQ, HKV, D, BS = 32, 8, 128, 16
 CELL = 2 * D + 8
 HEADLINE = "long_decode"
-# the six shapes the reference quotes its numbers on, then decode at the two other head sizes
+# the six shapes the reference quotes its numbers on, then the reference's production shape (256 dims, 12 / 2
+# heads, HND pages of 816 slots) in decode and chunked prefill, and decode at 64 dims
 PER_CONFIG = ("decode_small", "long_decode", "verify4", "drafter16", "chunked_prefill", "mixed", "decode_d256",
-              "decode_d64")
+              "prefill_d256", "decode_d64")
 TENSOR_BOUND = ("chunked_prefill", "prefill_d256")
 
 
@@ -68,7 +69,7 @@ def workload_launches(name: str, seed: int = 1001):
         return [dict(seq_lens=[8192] * 64, q_lens=[1] * 64, Hq=32, Hkv=8)]
     if name == "decode_d256":  # the reference's production shape: 256 dims, 6 query heads per KV head, HND pages of 816 slots
         return [dict(seq_lens=[8192] * 64, q_lens=[1] * 64, Hq=12, Hkv=2, D=256, block_size=816, layout="HND")]
-    if name == "prefill_d256":  # chunked prefill at the production shape (integer kernel, row tiles of 12 rows)
+    if name == "prefill_d256":  # chunked prefill at the production shape (the row-major kernel for 256 dims)
         return [dict(seq_lens=[32768] * 4, q_lens=[2048] * 4, Hq=12, Hkv=2, D=256, block_size=816, layout="HND",
                      prefill=True)]
     if name == "decode_d64":  # 64 dims
@@ -626,7 +627,7 @@ def roofline_of(wl, world, attn_ms, pass_ms, hbm_peak, tc_peak, tc_sustained, pe
     if wl.name in TENSOR_BOUND:
         roof = {"bound": "tensor", "achieved": tfs, "peak": tc_peak, "unit": "TFLOP/s", "frac": tfs / tc_peak,
                 "frac_of_sustained_peak": tfs / tc_sustained if tc_sustained else None, "traffic": None,
-                "kernel": "umma_rows_attention_kernel" if all(d.D == 128 for d in wl.dls) else "umma_i8_attention_kernel"}
+                "kernel": "umma_rows_attention_kernel" if all(d.D == 128 for d in wl.dls) else "umma_rows256_attention_kernel"}
     elif wl.name == "mixed":
         # two kernels one after the other: the integer kernel reads the decode and verify requests'
         # cache (HBM-bound), the row-major kernel computes the prefill chunks (tensor-bound); the
