@@ -262,7 +262,10 @@ umma_rows256_attention_kernel(const __grid_constant__ KernelParams p, const __gr
     // scale right behind their bytes.
     const int pt = tid & 127;
     const bool v_part = warp >= 12;
-    const int key = pt & (kWKeys - 1), upper = pt >> 6;
+    // Contiguous cells (raw_mode 2) alternate between the two 8-byte alignments: a warp takes
+    // the even keys or the odd ones, so that it runs one instance of the widening below.
+    const int slot_in_set = pt & (kWKeys - 1), upper = pt >> 6;
+    const int key = p.raw_mode == 2 ? 2 * (slot_in_set & 31) + (slot_in_set >> 5) : slot_in_set;
     const int bs = p.copy_slots;  // slots of one page copy
     const uint8_t* kb = p.k.data + (int64_t)kvh * p.k.stride_head;
     const uint32_t delta = (uint32_t)(reinterpret_cast<uintptr_t>(kb) & 15);
