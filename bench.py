@@ -49,7 +49,7 @@ HEADLINE = "long_decode"
 # heads, HND pages of 816 slots) in decode and chunked prefill, and decode at 64 dims
 PER_CONFIG = ("decode_small", "long_decode", "verify4", "drafter16", "chunked_prefill", "mixed", "decode_d256",
               "prefill_d256", "decode_d64")
-TENSOR_BOUND = ("chunked_prefill", "prefill_d256")
+TENSOR_BOUND = ("chunked_prefill", "chunked_prefill_hnd", "prefill_d256")
 
 
 # --------------------------------------------------------------------------
@@ -81,6 +81,8 @@ def workload_launches(name: str, seed: int = 1001):
                      Hkv=8, window=4096)]
     if name == "chunked_prefill":  # 4 chunks of 2048 tokens over 30720 cached tokens
         return [dict(seq_lens=[32768] * 4, q_lens=[2048] * 4, Hq=64, Hkv=8, prefill=True)]
+    if name == "chunked_prefill_hnd":  # the same chunks over HND pages (the slots of a head together)
+        return [dict(seq_lens=[32768] * 4, q_lens=[2048] * 4, Hq=64, Hkv=8, prefill=True, layout="HND")]
     if name == "mixed":  # 48 decode + 8 verify + 2 prefill requests in one launch
         dec = rng.integers(4096, 131073, size=48).tolist()
         return [dict(seq_lens=dec + [32768] * 8 + [17408] * 2, q_lens=[1] * 48 + [4] * 8 + [1024] * 2,

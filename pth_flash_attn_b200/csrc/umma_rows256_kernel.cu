@@ -81,6 +81,9 @@ struct WBars {
   static constexpr int raw_free = raw_full + kWNR;     // [NR] producers -> loader
 };
 
+// Key of a tile held by row `r` of its images: with contiguous cells the even keys, then the odd ones.
+__device__ __forceinline__ int tile_key_w(int raw_mode, int r) { return raw_mode == 2 ? 2 * (r & 31) + (r >> 5) : r; }
+
 __device__ __forceinline__ uint32_t pack_bf16_w(float a, float b) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<const uint32_t*>(&v);
@@ -263,9 +266,11 @@ umma_rows256_attention_kernel(const __grid_constant__ KernelParams p, const __gr
     const int pt = tid & 127;
     const bool v_part = warp >= 12;
     // Contiguous cells (raw_mode 2) alternate between the two 8-byte alignments: a warp takes
-    // the even keys or the odd ones, so that it runs one instance of the widening below.
-    const int slot_in_set = pt & (kWKeys - 1), upper = pt >> 6;
-    const int key = p.raw_mode == 2 ? 2 * (slot_in_set & 31) + (slot_in_set >> 5) : slot_in_set;
+    // the even keys or the odd ones, so that it runs one instance of the widening below.  Row r
+    // of the images (and of the scale vectors) then holds key tile_key_w(r): the order of the
+    // keys inside a tile changes no sum, and the softmax masks by that key.
+    const int img_row = pt & (kWKeys - 1), upper = pt >> 6;
+    const int key = tile_key_w(p.raw_mode, img_row);
     const int bs = p.copy_slots;  // slots of one page copy
     const uint8_t* kb = p.k.data + (int64_t)kvh * p.k.stride_head;
     const uint32_t delta = (uint32_t)(reinterpret_cast<uintptr_t>(kb) & 15);
@@ -305,7 +310,7 @@ umma_rows256_attention_kernel(const __grid_constant__ KernelParams p, const __gr
         if (j >= kWNS) ok &= wait_or_abort(&bars[B::vempty + j % kWNS], ((j / kWNS) - 1) & 1, abort_flag);
         dst = smem + L::vst + (j % kWNS) * kWVStage;
       }
-      uint8_t* out16 = dst + (upper * 16) * kWChunkStride + key * 16;  // column blocks 16 upper .. 16 upper + 15
+      uint8_t* out16 = dst + (upper * 16) * kWChunkStride + img_row * 16;  // column blocks 16 upper .. 16 upper + 15
       uint32_t scale_bits;
       // (one instance per alignment: the words of w must be compile-time indices)
       auto widen_piece = [&](auto first_word) {
@@ -321,9 +326,9 @@ umma_rows256_attention_kernel(const __grid_constant__ KernelParams p, const __gr
       else widen_piece(std::integral_constant<int, 3>{});
       if (upper) {
         if (!v_part) {
-          reinterpret_cast<float*>(smem + L::ksc)[(j % kWKsRing) * kWKeys + key] = __uint_as_float(scale_bits) * p.scale_log2;
+          reinterpret_cast<float*>(smem + L::ksc)[(j % kWKsRing) * kWKeys + img_row] = __uint_as_float(scale_bits) * p.scale_log2;
         } else {
-          *reinterpret_cast<uint32_t*>(dst + kWImage + key * 4) = scale_bits;
+          *reinterpret_cast<uint32_t*>(dst + kWImage + img_row * 4) = scale_bits;
         }
       }
       tc::fence_async_smem();
@@ -469,7 +474,6 @@ umma_rows256_attention_kernel(const __grid_constant__ KernelParams p, const __gr
       const uint32_t s_tmem = s_part + (i & 1) * kWKeys;
       const int pos0 = key_begin + i * kWKeys;
       const bool interior = pos0 >= mask_lo && pos0 + (kWKeys - 1) <= mask_hi;
-      const int c0 = pos0 + g * kWGroupKeys;  // first key position of this group's part
       ok &= wait_or_abort(&bars[B::s_ready + (i & 1)], (i >> 1) & 1, abort_flag);
       tc::fence_after_sync();
       uint32_t r[kWGroupKeys];  // the scores of this row and part, read once
@@ -490,7 +494,7 @@ umma_rows256_attention_kernel(const __grid_constant__ KernelParams p, const __gr
             const int n = n4 * 4 + e;
             float sc = __uint_as_float(r[n]) * kk[e];
             if constexpr (kMask) {
-              const int pos = c0 + n;
+              const int pos = pos0 + tile_key_w(p.raw_mode, g * kWGroupKeys + n);  // key held by this column
               sc = (pos >= rlo && pos <= rhi) ? sc : -INFINITY;
             }
             r[n] = __float_as_uint(sc);

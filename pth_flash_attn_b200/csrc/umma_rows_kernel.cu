@@ -88,6 +88,12 @@ struct RBars {
   static constexpr int raw_free = raw_full + kRNR;     // [NR] producers -> loader, 128 arrivals
 };
 
+// Key of a tile held by row `r` of its images: with contiguous cells the rows of a half tile
+// hold its even keys, then its odd ones (see the producers).
+__device__ __forceinline__ int tile_key_rows(int raw_mode, int r) {
+  return raw_mode == 2 ? (r & 64) + 2 * (r & 31) + ((r >> 5) & 1) : r;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<const uint32_t*>(&v);
@@ -252,14 +258,19 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
     // the raw ring is made of half stages of 64 keys: keys 0-63 of tile j are half stage
     // u = 2 j, keys 64-127 are u = 2 j + 1; half stage u sits in slot u % kRNR
     const int half = pt >> 6;
-    const int my_page = (pt & (kHalfKeys - 1)) >> p.copy_shift, my_slot = pt & (bs - 1);
+    // Contiguous cells (raw_mode 2) alternate between the two 8-byte alignments: a warp takes the
+    // even keys or the odd ones of its half stage, so that it runs one of the two code paths
+    // below.  Row pt of the images (and of the scale vectors) then holds key tile_key_rows(pt):
+    // the order of the keys inside a tile changes no sum, and the softmax masks by that key.
+    const int key = tile_key_rows(p.raw_mode, pt);
+    const int my_page = (key & (kHalfKeys - 1)) >> p.copy_shift, my_slot = key & (bs - 1);
     const uint32_t cell_off = my_page * bs * kRawRow + my_slot * row_pitch + delta;  // inside a half stage
     const bool odd = (cell_off & 8u) != 0;
 #pragma unroll 1
     for (int j = 0; j < n_tiles; ++j) {
       const int u = 2 * j + half;
       const int rs = u % kRNR;
-      const int pos = (tile_begin + j) * kTileKeys + pt;
+      const int pos = (tile_begin + j) * kTileKeys + key;
       const bool valid = pos >= range_begin && pos < range_end;
       // A raw slot is used by the two halves in turn (kRNR is odd), and a parity wait only
       // tells apart two consecutive phases: this thread must not look at raw_full[rs] while
@@ -471,7 +482,6 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
       const uint32_t s_tmem = s_half + (i & 1) * 128;
       const int pos0 = (tile_begin + i) * kTileKeys;
       const bool interior = pos0 >= mask_lo && pos0 + (kTileKeys - 1) <= mask_hi;
-      const int c0 = pos0 + g * 64;  // first key position of this group's half
       ok &= wait_or_abort(&bars[B::s_ready + (i & 1)], (i >> 1) & 1, abort_flag);
       tc::fence_after_sync();
       // the 64 scores of this row and half, read once
@@ -495,7 +505,7 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
             const int n = n4 * 4 + e;
             float sc = __uint_as_float(r[n]) * kk[e];
             if constexpr (kMask) {
-              const int pos = c0 + n;
+              const int pos = pos0 + tile_key_rows(p.raw_mode, g * 64 + n);  // key held by column g 64 + n
               sc = (pos >= rlo && pos <= rhi) ? sc : -INFINITY;
             }
             r[n] = __float_as_uint(sc);
