@@ -49,7 +49,7 @@ HEADLINE = "long_decode"
 # heads, HND pages of 816 slots) in decode and chunked prefill, and decode at 64 dims
 PER_CONFIG = ("decode_small", "long_decode", "verify4", "drafter16", "chunked_prefill", "mixed", "decode_d256",
               "prefill_d256", "decode_d64")
-TENSOR_BOUND = ("chunked_prefill", "chunked_prefill_hnd", "prefill_d256")
+TENSOR_BOUND = ("chunked_prefill", "chunked_prefill_hnd", "prefill_d256", "prefill_d256_nhd")
 
 
 # --------------------------------------------------------------------------
@@ -72,6 +72,8 @@ def workload_launches(name: str, seed: int = 1001):
     if name == "prefill_d256":  # chunked prefill at the production shape (the row-major kernel for 256 dims)
         return [dict(seq_lens=[32768] * 4, q_lens=[2048] * 4, Hq=12, Hkv=2, D=256, block_size=816, layout="HND",
                      prefill=True)]
+    if name == "prefill_d256_nhd":  # the same chunks over NHD pages of 16 slots
+        return [dict(seq_lens=[32768] * 4, q_lens=[2048] * 4, Hq=12, Hkv=2, D=256, prefill=True)]
     if name == "decode_d64":  # 64 dims
         return [dict(seq_lens=[8192] * 64, q_lens=[1] * 64, Hq=32, Hkv=8, D=64)]
     if name == "verify4":  # speculative verification, 4 draft tokens
