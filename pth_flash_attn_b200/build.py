@@ -20,7 +20,7 @@ LIB = HERE / "libpthb200_attn.so"
 OP_LIB = HERE / "_C.abi3.so"
 
 CUDA_SOURCES = ["launcher.cu", "scalar_kernel.cu", "combine_kernel.cu", "umma_kernel.cu", "umma_i8_kernel.cu",
-                "umma_rows_kernel.cu", "umma_rows256_kernel.cu", "writer_kernel.cu", "copy_ceiling_kernel.cu"]
+                "umma_rows_kernel.cu", "umma_rows256_kernel.cu", "umma_rows2_kernel.cu", "writer_kernel.cu", "copy_ceiling_kernel.cu"]
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fno-gnu-unique", "-rdc=false",

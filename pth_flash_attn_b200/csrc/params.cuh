@@ -213,6 +213,8 @@ int umma_i8_num_ctas(const KernelParams& p, int sms);
 cudaError_t read_i8_status(unsigned int* v);
 cudaError_t read_rows_status(unsigned int* v);
 cudaError_t read_rows256_status(unsigned int* v);
+cudaError_t read_rows2_status(unsigned int* v);
+cudaError_t launch_umma_rows2_attention(const KernelParams& p, cudaStream_t stream);
 cudaError_t launch_umma_rows256_attention(const KernelParams& p, cudaStream_t stream);
 cudaError_t launch_combine_kernel(const CombineParams& p, cudaStream_t stream);
 cudaError_t launch_copy_ceiling(const KernelParams& p, cudaStream_t stream);

@@ -697,6 +697,10 @@ cudaError_t launch_rows(const KernelParams& p, const CUtensorMap& map, dim3 grid
 
 cudaError_t launch_umma_rows_attention(const KernelParams& p_in, cudaStream_t stream) {
   if (p_in.head_size == 256) return launch_umma_rows256_attention(p_in, stream);
+  // Launches whose requests have 256 rows or more on average (prefill chunks) run two row tiles
+  // per CTA, which share every widened K / V tile (umma_rows2_kernel.cu); shorter ones (wide
+  // verification, drafter steps) would leave its second row tile empty.
+  if ((int64_t)p_in.num_tokens * p_in.group >= 256 * (int64_t)p_in.num_reqs) return launch_umma_rows2_attention(p_in, stream);
   KernelParams p = p_in;
   // Row tiles of 128 rows, whatever tile height the caller planned with: the partition of
   // the query tokens into row tiles is internal to a launch.

@@ -106,6 +106,8 @@ extern "C" int32_t pthb200_device_status(int32_t* status) {
   v |= w;
   if (pthb200::read_rows256_status(&w) != cudaSuccess) return PTH_ATTN_ECUDA;
   v |= w;
+  if (pthb200::read_rows2_status(&w) != cudaSuccess) return PTH_ATTN_ECUDA;
+  v |= w;
   if (status) *status = (int32_t)v;
   return PTH_ATTN_OK;
 }
