@@ -10,8 +10,10 @@
 //   MMAs       per KV tile two QK (M 128, N 64, eight steps of 16 dims, Q images in shared
 //              memory) on ONE K image and two PV (M 128, N 128, four steps of 16 keys, P from
 //              TMEM) on ONE V stage;
-//   producers  thread (key, half) of the K set / V set widens 64 of the key's 128 dims; the
-//              threads of the upper halves also carry the key's scale;
+//   producers  thread (key, half) of the K set / V set widens 64 of the key's 128 dims; the K
+//              set's upper halves carry k_scale to the softmax, the V set multiplies its rows
+//              by v_scale as it widens them (x * v_scale rounded once to bf16), so P is the
+//              bare probability and the softmax spends nothing on v_scale;
 //   softmax    256 threads, one per row: the row's maximum, sum and reference never leave the
 //              thread, and there is nothing to merge at the end.
 // Raw ring: four units of 64 keys x 272 bytes.  Every mbarrier wait is bounded (page_copy.cuh).
@@ -40,7 +42,7 @@ constexpr int kXQStride = 128 * 16 + 16;            // 2,064 B: one column block
 constexpr int kXQImage = kXChunks * kXQStride;      // 33,024 B
 constexpr int kXRawRow = raw_row_for(kXDim);        // 272 B
 constexpr int kXRawUnit = kXKeys * kXRawRow;        // 17,408 B: raw cells of a tile
-constexpr int kXVStage = kXImage + kXKeys * 4;      // V image + v_scale[64]
+constexpr int kXVStage = kXImage;                   // V image (rows already multiplied by v_scale)
 constexpr int kXNK = 2, kXNS = 2, kXNR = 4;         // K images, V stages, raw units
 constexpr int kXKsRing = 4;                         // tiles of scaled k_scale vectors kept
 constexpr int kXSoftmax = 256;                      // warps 0-3 (row tile 0), 4-7 (row tile 1)
@@ -288,6 +290,12 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
 #pragma unroll
         for (int c = 0; c < 20; ++c) w[c] = 0u;
       }
+      // The V set multiplies its row by the key's v_scale as it widens it (below): the scale word
+      // sits behind the upper half of V, which only half of the threads of a key have read.
+      float v_scale = 0.f;
+      if (v_part && valid)
+        v_scale = *reinterpret_cast<const float*>(smem + L::raw + rs * kXRawUnit + my_page * bs * kXRawRow + my_slot * row_pitch +
+                                                  delta + 2 * kXDim + 4);
       mbar_arrive(&bars[B::raw_free + rs]);  // the bytes are in registers: the unit may be refilled
       uint8_t* dst;
       if (!v_part) {
@@ -300,24 +308,32 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
       uint8_t* out16 = dst + (upper * 8) * kXChunkStride + img_row * 16;  // column blocks 8 upper .. 8 upper + 7
       uint32_t scale_bits;
       // (one instance per alignment: the words of w must be compile-time indices)
+      // v_scale as the sum of two bf16 (hi + lo carries 16 bits of it): x * lo rounds a term 2^-9
+      // of the product, the fused multiply-add then rounds x * v_scale once
+      const __nv_bfloat16 vs_hi = __float2bfloat16_rn(v_scale);
+      const __nv_bfloat162 hi2 = __bfloat162bfloat162(vs_hi);
+      const __nv_bfloat162 lo2 = __bfloat162bfloat162(__float2bfloat16_rn(v_scale - __bfloat162float(vs_hi)));
+      auto scale2 = [&](uint32_t x) -> uint32_t {
+        const __nv_bfloat162 xv = *reinterpret_cast<const __nv_bfloat162*>(&x);
+        const __nv_bfloat162 y = __hfma2(xv, hi2, __hmul2(xv, lo2));
+        return *reinterpret_cast<const uint32_t*>(&y);
+      };
       auto widen_piece = [&](auto first_word) {
         constexpr int kW0 = decltype(first_word)::value;
 #pragma unroll
-        for (int c = 0; c < 8; ++c)
-          *reinterpret_cast<uint4*>(out16 + c * kXChunkStride) = widen8_bf16(make_uint2(w[kW0 + 2 * c], w[kW0 + 2 * c + 1]));
+        for (int c = 0; c < 8; ++c) {
+          uint4 x = widen8_bf16(make_uint2(w[kW0 + 2 * c], w[kW0 + 2 * c + 1]));
+          if (v_part) x = make_uint4(scale2(x.x), scale2(x.y), scale2(x.z), scale2(x.w));
+          *reinterpret_cast<uint4*>(out16 + c * kXChunkStride) = x;
+        }
         scale_bits = w[kW0 + 16];
       };
       if (wo == 0) widen_piece(std::integral_constant<int, 0>{});
       else if (wo == 1) widen_piece(std::integral_constant<int, 1>{});
       else if (wo == 2) widen_piece(std::integral_constant<int, 2>{});
       else widen_piece(std::integral_constant<int, 3>{});
-      if (upper) {
-        if (!v_part) {
-          reinterpret_cast<float*>(smem + L::ksc)[(j % kXKsRing) * kXKeys + img_row] = __uint_as_float(scale_bits) * p.scale_log2;
-        } else {
-          *reinterpret_cast<uint32_t*>(dst + kXImage + img_row * 4) = scale_bits;
-        }
-      }
+      if (upper && !v_part)
+        reinterpret_cast<float*>(smem + L::ksc)[(j % kXKsRing) * kXKeys + img_row] = __uint_as_float(scale_bits) * p.scale_log2;
       tc::fence_async_smem();
       mbar_arrive(&bars[(v_part ? B::vfull + j % kXNS : B::kfull + j % kXNK)]);
     }
@@ -458,7 +474,6 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
     for (int i = 0; i < n_tiles; ++i) {
       const int b = i & 1;
       const float* ksp = reinterpret_cast<const float*>(smem + L::ksc) + (i % kXKsRing) * kXKeys;
-      const float* vsp = reinterpret_cast<const float*>(smem + L::vst + (i % kXNS) * kXVStage + kXImage);
       const uint32_t s_tmem = s_rt + b * kXKeys;
       const int pos0 = key_begin + i * kXKeys;
       const bool interior = pos0 >= mask_lo && pos0 + (kXKeys - 1) <= mask_hi;
@@ -518,23 +533,19 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
       }
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
 
-      // ---- pass 2: p * v_scale as packed bf16 over the first 32 columns of S ----
+      // ---- pass 2: p as packed bf16 over the first 32 columns of S (the V image carries v_scale) ----
       // (a masked score is -inf: its p is exp2(-inf) = 0)
-      ok &= wait_or_abort(&bars[B::vfull + i % kXNS], (i / kXNS) & 1, abort_flag);  // v_scale of tile i
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         uint32_t pk[16];
 #pragma unroll
         for (int n4 = 0; n4 < 8; ++n4) {
-          const float4 vs4 = reinterpret_cast<const float4*>(vsp)[j * 8 + n4];
-          const float vv[4] = {vs4.x, vs4.y, vs4.z, vs4.w};
           float pv[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float pr = ex2f_x(__uint_as_float(r[j * 32 + n4 * 4 + e]) - m_use);
-            ls[e] += pr;
-            pv[e] = pr * vv[e];
+            pv[e] = ex2f_x(__uint_as_float(r[j * 32 + n4 * 4 + e]) - m_use);
+            ls[e] += pv[e];
           }
           pk[n4 * 2] = pack_bf16_x(pv[0], pv[1]);
           pk[n4 * 2 + 1] = pack_bf16_x(pv[2], pv[3]);
