@@ -631,7 +631,7 @@ def roofline_of(wl, world, attn_ms, pass_ms, hbm_peak, tc_peak, tc_sustained, pe
     if wl.name in TENSOR_BOUND:
         roof = {"bound": "tensor", "achieved": tfs, "peak": tc_peak, "unit": "TFLOP/s", "frac": tfs / tc_peak,
                 "frac_of_sustained_peak": tfs / tc_sustained if tc_sustained else None, "traffic": None,
-                "kernel": "umma_rows_attention_kernel" if all(d.D == 128 for d in wl.dls) else "umma_rows256_attention_kernel"}
+                "kernel": "umma_rows2_attention_kernel" if all(d.D == 128 for d in wl.dls) else "umma_rows256_attention_kernel"}
     elif wl.name == "mixed":
         # two kernels one after the other: the integer kernel reads the decode and verify requests'
         # cache (HBM-bound), the row-major kernel computes the prefill chunks (tensor-bound); the
