@@ -479,10 +479,10 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
       const bool interior = pos0 >= mask_lo && pos0 + (kXKeys - 1) <= mask_hi;
       ok &= wait_or_abort(&bars[B::s_ready + 2 * rt + b], (i >> 1) & 1, abort_flag);
       tc::fence_after_sync();
-      uint32_t r[kXKeys];  // the row's scores of this tile, read once
-      tc::tmem_ld32(s_tmem, r);
-      tc::tmem_ld32(s_tmem + 32, r + 32);
+      uint32_t r[kXKeys];  // the row's scores of this tile, read once: the second half arrives while
+      tc::tmem_ld32(s_tmem, r);  // pass 1 works on the first
       tc::tmem_ld_wait();
+      tc::tmem_ld32(s_tmem + 32, r + 32);
 
       // ---- pass 1: scores in log2 units (kept in the registers) and their maximum ----
       float m_t;
@@ -491,6 +491,7 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
         float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
         for (int n4 = 0; n4 < kXKeys / 4; ++n4) {
+          if (n4 == kXKeys / 8) tc::tmem_ld_wait();
           const float4 ks4 = reinterpret_cast<const float4*>(ksp)[n4];  // k_scale * scale * log2 e
           const float kk[4] = {ks4.x, ks4.y, ks4.z, ks4.w};
 #pragma unroll
