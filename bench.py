@@ -46,10 +46,10 @@ HQ, HKV, D, BS = 32, 8, 128, 16
 CELL = 2 * D + 8
 HEADLINE = "long_decode"
 # the six shapes the reference quotes its numbers on, then the reference's production shape (256 dims, 12 / 2
-# heads, HND pages of 816 slots) in decode and chunked prefill, and decode at 64 dims
+# heads, HND pages of 816 slots) in decode and chunked prefill, and decode and chunked prefill at 64 dims
 PER_CONFIG = ("decode_small", "long_decode", "verify4", "drafter16", "chunked_prefill", "mixed", "decode_d256",
-              "prefill_d256", "decode_d64")
-TENSOR_BOUND = ("chunked_prefill", "chunked_prefill_hnd", "prefill_d256", "prefill_d256_nhd")
+              "prefill_d256", "decode_d64", "prefill_d64")
+TENSOR_BOUND = ("chunked_prefill", "chunked_prefill_hnd", "prefill_d256", "prefill_d256_nhd", "prefill_d64")
 
 
 # --------------------------------------------------------------------------
@@ -74,6 +74,8 @@ def workload_launches(name: str, seed: int = 1001):
                      prefill=True)]
     if name == "prefill_d256_nhd":  # the same chunks over NHD pages of 16 slots
         return [dict(seq_lens=[32768] * 4, q_lens=[2048] * 4, Hq=12, Hkv=2, D=256, prefill=True)]
+    if name == "prefill_d64":  # chunked prefill at 64 dims
+        return [dict(seq_lens=[32768] * 4, q_lens=[2048] * 4, Hq=32, Hkv=8, D=64, prefill=True)]
     if name == "decode_d64":  # 64 dims
         return [dict(seq_lens=[8192] * 64, q_lens=[1] * 64, Hq=32, Hkv=8, D=64)]
     if name == "verify4":  # speculative verification, 4 draft tokens
@@ -631,7 +633,7 @@ def roofline_of(wl, world, attn_ms, pass_ms, hbm_peak, tc_peak, tc_sustained, pe
     if wl.name in TENSOR_BOUND:
         roof = {"bound": "tensor", "achieved": tfs, "peak": tc_peak, "unit": "TFLOP/s", "frac": tfs / tc_peak,
                 "frac_of_sustained_peak": tfs / tc_sustained if tc_sustained else None, "traffic": None,
-                "kernel": "umma_rows2_attention_kernel" if all(d.D == 128 for d in wl.dls) else "umma_rows256_attention_kernel"}
+                "kernel": "umma_rows256_attention_kernel" if wl.dls[0].D == 256 else "umma_rows2_attention_kernel"}
     elif wl.name == "mixed":
         # two kernels one after the other: the integer kernel reads the decode and verify requests'
         # cache (HBM-bound), the row-major kernel computes the prefill chunks (tensor-bound); the

@@ -1,5 +1,6 @@
-// Row-major tcgen05 attention kernel, head size 128, TWO row tiles per CTA: 256 query rows share
-// every widened K / V tile.
+// Row-major tcgen05 attention kernel, head sizes 128 and 64, TWO row tiles per CTA: 256 query rows
+// share every widened K / V tile.  (The shapes below are those of 128 dims; at 64 dims the images,
+// the accumulators and the contraction steps over the head are half as large.)
 //
 // In the one-tile kernel (umma_rows_kernel.cu) every row tile of 128 rows widens the int8 keys
 // and values of its whole context to bf16 for itself, and that widening and the shared-memory
@@ -32,17 +33,23 @@ __device__ unsigned int g_rows2_status = 0;
 
 namespace {
 
-constexpr int kXDim = 128;                          // head size
 constexpr int kXKeys = 64;                          // keys of a tile
 constexpr int kXRows = 256;                         // rows of a CTA: two MMA row tiles
-constexpr int kXChunks = kXDim / 8;                 // 16-byte column blocks of a widened row: 8 bf16 each
 constexpr int kXChunkStride = kXKeys * 16 + 16;     // 1,040 B: one column block of all keys, padded
-constexpr int kXImage = kXChunks * kXChunkStride;   // 16,640 B: widened K or V of a tile
 constexpr int kXQStride = 128 * 16 + 16;            // 2,064 B: one column block of the 128 rows of a Q image
-constexpr int kXQImage = kXChunks * kXQStride;      // 33,024 B
-constexpr int kXRawRow = raw_row_for(kXDim);        // 272 B
-constexpr int kXRawUnit = kXKeys * kXRawRow;        // 17,408 B: raw cells of a tile
-constexpr int kXVStage = kXImage;                   // V image (rows already multiplied by v_scale)
+// Sizes that follow the head size HD (figures for 128).
+template <int HD>
+struct XG {
+  static_assert(HD == 64 || HD == 128, "head size");
+  static constexpr int chunks = HD / 8;                    // 16-byte column blocks of a widened row: 8 bf16 each
+  static constexpr int image = chunks * kXChunkStride;     // 16,640 B: widened K or V of a tile (V rows times v_scale)
+  static constexpr int qimage = chunks * kXQStride;        // 33,024 B
+  static constexpr int raw_row = raw_row_for(HD);          // 272 B
+  static constexpr int raw_unit = kXKeys * raw_row;        // 17,408 B: raw cells of a tile
+  static constexpr int piece = HD / 2;                     // bytes of a key a producer thread widens
+  static constexpr int piece_chunks = piece / 8;           // column blocks it writes
+  static constexpr int load_chunks = piece / 16 + 1;       // 16-byte chunks it reads: the piece, its misalignment, the scale
+};
 constexpr int kXNK = 2, kXNS = 2, kXNR = 4;         // K images, V stages, raw units
 constexpr int kXKsRing = 4;                         // tiles of scaled k_scale vectors kept
 constexpr int kXSoftmax = 256;                      // warps 0-3 (row tile 0), 4-7 (row tile 1)
@@ -53,12 +60,14 @@ constexpr int kXProducerRegs = 72, kXSoftmaxRegs = 120;  // of the 96 per thread
 constexpr int kXOCol = 256;                         // TMEM columns: S(rt, b) at (2 rt + b) 64, O(rt) at 256 + 128 rt
 constexpr float kXRescaleGap = 8.0f;                // log2 units a row maximum may outgrow its reference
 
+template <int HD>
 struct XLayout {
+  using G = XG<HD>;
   static constexpr int kimg = 0;
-  static constexpr int vst = kimg + kXNK * kXImage;
-  static constexpr int qimg = vst + kXNS * kXVStage;                 // [2 row tiles] Q images
-  static constexpr int raw = (qimg + 2 * kXQImage + 127) / 128 * 128;
-  static constexpr int ksc = raw + kXNR * kXRawUnit;                 // float [kXKsRing][64]: k_scale * scale * log2 e
+  static constexpr int vst = kimg + kXNK * G::image;
+  static constexpr int qimg = vst + kXNS * G::image;                 // [2 row tiles] Q images
+  static constexpr int raw = (qimg + 2 * G::qimage + 127) / 128 * 128;
+  static constexpr int ksc = raw + kXNR * G::raw_unit;               // float [kXKsRing][64]: k_scale * scale * log2 e
   static constexpr int bars = ksc + kXKsRing * kXKeys * 4;           // uint64 [...]
   static constexpr int n_bars = 2 * kXNS + 2 * kXNK + 12 + 2 * kXNR;
   static constexpr int misc = bars + n_bars * 8;
@@ -89,25 +98,31 @@ __device__ __forceinline__ float ex2f_x(float x) {
 // Key of a tile held by row `r` of its images: with contiguous cells the even keys, then the odd ones.
 __device__ __forceinline__ int tile_key_x(int raw_mode, int r) { return raw_mode == 2 ? 2 * (r & 31) + (r >> 5) : r; }
 
-// S = Q K^T for one row tile: eight steps of 16 dims = two column blocks of either image each.
+// S = Q K^T for one row tile: HD / 16 steps of 16 dims = two column blocks of either image each.
+template <int HD>
 __device__ __forceinline__ void issue_qk_x(uint32_t s_tmem, RowsDesc q, RowsDesc k) {
   constexpr uint32_t idesc = tc::instr_desc(128, kXKeys, tc::kFmtBF16, tc::kFmtBF16, 0, 0);
   constexpr uint32_t qstep = (2 * kXQStride) >> 4, kstep = (2 * kXChunkStride) >> 4;
   mma_ss_words<false>(s_tmem, q.lo, q.hi, k.lo, k.hi, idesc);
 #pragma unroll
-  for (int kk = 1; kk < kXDim / 16; ++kk) mma_ss_words<true>(s_tmem, q.lo + kk * qstep, q.hi, k.lo + kk * kstep, k.hi, idesc);
+  for (int kk = 1; kk < HD / 16; ++kk) mma_ss_words<true>(s_tmem, q.lo + kk * qstep, q.hi, k.lo + kk * kstep, k.hi, idesc);
 }
 // O += P V for one row tile: P (64 keys, two bf16 per column) in the first 32 columns of its S buffer.
+template <int HD>
 __device__ __forceinline__ void issue_pv_x(uint32_t o_tmem, uint32_t p_tmem, RowsDesc v, bool accumulate) {
-  constexpr uint32_t idesc = tc::instr_desc(128, kXDim, tc::kFmtBF16, tc::kFmtBF16, 0, 1);
+  constexpr uint32_t idesc = tc::instr_desc(128, HD, tc::kFmtBF16, tc::kFmtBF16, 0, 1);
 #pragma unroll
   for (int kk = 0; kk < kXKeys / 16; ++kk) mma_ts_words(o_tmem, p_tmem + kk * 8, v.lo + kk * (256 >> 4), v.hi, idesc, accumulate || kk > 0);
 }
 
+template <int HD>
 __global__ void __launch_bounds__(kXThreads, 1)
 umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid_constant__ CUtensorMap tmap) {
-  using L = XLayout;
+  using L = XLayout<HD>;
   using B = XBars;
+  using G = XG<HD>;
+  constexpr int kXDim = HD, kXChunks = G::chunks, kXImage = G::image, kXVStage = G::image, kXQImage = G::qimage;
+  constexpr int kXRawRow = G::raw_row, kXRawUnit = G::raw_unit;
   static_assert(L::raw % 128 == 0 && kXRawUnit % 128 == 0 && (16 * kXRawRow) % 128 == 0, "TMA destinations");
   static_assert(L::vst % 16 == 0 && kXVStage % 16 == 0 && kXImage % 16 == 0 && L::qimg % 16 == 0 && kXQImage % 16 == 0,
                 "image alignment");
@@ -251,7 +266,7 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
     // =========================== producers ====================================
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kXProducerRegs));
     // Warps 8-11 widen K, warps 12-15 V.  Thread pt of a set owns row pt % 64 of the images and
-    // dims 64 (pt / 64) .. + 63 of its key: 64 bytes of the raw cell, which start 0 or 8 (K) or
+    // half of its key's dims (the lower or the upper): HD / 2 bytes of the raw cell, which start 0 or 8 (K) or
     // 4 or 12 (V) bytes after a 16-byte boundary; the threads of the upper halves find the key's
     // scale right behind their bytes.  Contiguous cells (raw_mode 2) alternate between the two
     // 8-byte alignments: a warp takes the even keys or the odd ones (one widening path per warp),
@@ -265,8 +280,8 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
     const uint32_t delta = (uint32_t)(reinterpret_cast<uintptr_t>(kb) & 15);
     const int row_pitch = p.raw_mode == 1 ? kXRawRow : 2 * kXDim + 8;
     const int my_page = key >> p.copy_shift, my_slot = key & (bs - 1);
-    // first byte of this thread's 64 bytes inside a raw unit
-    const uint32_t piece = my_page * bs * kXRawRow + my_slot * row_pitch + delta + (v_part ? kXDim + 4 : 0) + upper * 64;
+    // first byte of this thread's bytes inside a raw unit
+    const uint32_t piece = my_page * bs * kXRawRow + my_slot * row_pitch + delta + (v_part ? kXDim + 4 : 0) + upper * G::piece;
     const int wo = (int)((piece & 15u) >> 2);  // first word of the piece in the 16-byte chunks read: 0 / 2 (K), 1 / 3 (V)
 #pragma unroll 1
     for (int j = 0; j < n_tiles; ++j) {
@@ -274,12 +289,12 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
       const int pos = key_begin + j * kXKeys + key;
       const bool valid = pos >= range_begin && pos < range_end;
       ok &= wait_or_abort(&bars[B::raw_full + rs], (j / kXNR) & 1, abort_flag);
-      // five 16-byte chunks from the boundary below the piece: its 16 words and the scale behind them
-      uint32_t w[20];
+      // the 16-byte chunks from the boundary below the piece: its words and the scale behind them
+      uint32_t w[4 * G::load_chunks];
       if (valid) {
         const uint4* row = reinterpret_cast<const uint4*>(smem + L::raw + rs * kXRawUnit + (piece & ~15u));
 #pragma unroll
-        for (int c = 0; c < 5; ++c) {
+        for (int c = 0; c < G::load_chunks; ++c) {
           const uint4 v = row[c];
           w[4 * c] = v.x;
           w[4 * c + 1] = v.y;
@@ -288,7 +303,7 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
         }
       } else {
 #pragma unroll
-        for (int c = 0; c < 20; ++c) w[c] = 0u;
+        for (int c = 0; c < 4 * G::load_chunks; ++c) w[c] = 0u;
       }
       // The V set multiplies its row by the key's v_scale as it widens it (below): the scale word
       // sits behind the upper half of V, which only half of the threads of a key have read.
@@ -305,7 +320,7 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
         if (j >= kXNS) ok &= wait_or_abort(&bars[B::vempty + j % kXNS], ((j / kXNS) - 1) & 1, abort_flag);
         dst = smem + L::vst + (j % kXNS) * kXVStage;
       }
-      uint8_t* out16 = dst + (upper * 8) * kXChunkStride + img_row * 16;  // column blocks 8 upper .. 8 upper + 7
+      uint8_t* out16 = dst + (upper * G::piece_chunks) * kXChunkStride + img_row * 16;  // this half's column blocks
       uint32_t scale_bits;
       // (one instance per alignment: the words of w must be compile-time indices)
       // v_scale as the sum of two bf16 (hi + lo carries 16 bits of it): x * lo rounds a term 2^-9
@@ -321,12 +336,12 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
       auto widen_piece = [&](auto first_word) {
         constexpr int kW0 = decltype(first_word)::value;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < G::piece_chunks; ++c) {
           uint4 x = widen8_bf16(make_uint2(w[kW0 + 2 * c], w[kW0 + 2 * c + 1]));
           if (v_part) x = make_uint4(scale2(x.x), scale2(x.y), scale2(x.z), scale2(x.w));
           *reinterpret_cast<uint4*>(out16 + c * kXChunkStride) = x;
         }
-        scale_bits = w[kW0 + 16];
+        scale_bits = w[kW0 + G::piece / 4];
       };
       if (wo == 0) widen_piece(std::integral_constant<int, 0>{});
       else if (wo == 1) widen_piece(std::integral_constant<int, 1>{});
@@ -409,7 +424,7 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
             RowsDesc k = kd, qq = qd;
             k.lo += (uint32_t)(q % kXNK) * (kXImage >> 4);
             qq.lo += (uint32_t)rt * (kXQImage >> 4);
-            issue_qk_x(tmem_base + (2 * rt + b) * kXKeys, qq, k);
+            issue_qk_x<HD>(tmem_base + (2 * rt + b) * kXKeys, qq, k);
             tc::mma_commit(&bars[B::s_ready + 2 * rt + b]);
             tc::mma_commit(&bars[B::kempty + q % kXNK]);  // (free once both row tiles' QK have read the K image)
           }
@@ -429,7 +444,7 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
             tc::fence_after_sync();
             RowsDesc v = vd;
             v.lo += (uint32_t)(i % kXNS) * (kXVStage >> 4);
-            issue_pv_x(tmem_base + kXOCol + rt * kXDim, tmem_base + (2 * rt + b) * kXKeys, v, i > 0);
+            issue_pv_x<HD>(tmem_base + kXOCol + rt * kXDim, tmem_base + (2 * rt + b) * kXKeys, v, i > 0);
             tc::mma_commit(&bars[B::pv_done + 2 * rt + b]);
             tc::mma_commit(&bars[B::vempty + i % kXNS]);  // (free once both row tiles' PV have read the V stage)
           }
@@ -615,6 +630,24 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
 
 }  // namespace
 
+namespace {
+template <int HD>
+cudaError_t launch_rows2(const KernelParams& p, const CUtensorMap& map, cudaStream_t stream) {
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    err = cudaFuncSetAttribute(umma_rows2_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, XLayout<HD>::total);
+    if (err != cudaSuccess) return err;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  const dim3 grid(p.num_q_tiles, p.num_kv_heads, p.num_splits);
+  umma_rows2_attention_kernel<HD><<<grid, kXThreads, XLayout<HD>::total, stream>>>(p, map);
+  return cudaGetLastError();
+}
+}  // namespace
+
 cudaError_t launch_umma_rows2_attention(const KernelParams& p_in, cudaStream_t stream) {
   KernelParams p = p_in;
   // Row tiles of 256 rows, whatever tile height the caller planned with.
@@ -629,18 +662,7 @@ cudaError_t launch_umma_rows2_attention(const KernelParams& p_in, cudaStream_t s
     mapp = cached_page_map(p);
     if (mapp == nullptr) return cudaErrorInvalidValue;
   }
-  static bool configured[64] = {};
-  int dev = 0;
-  cudaError_t err = cudaGetDevice(&dev);
-  if (err != cudaSuccess) return err;
-  if (dev < 0 || dev >= 64 || !configured[dev]) {
-    err = cudaFuncSetAttribute(umma_rows2_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, XLayout::total);
-    if (err != cudaSuccess) return err;
-    if (dev >= 0 && dev < 64) configured[dev] = true;
-  }
-  const dim3 grid(p.num_q_tiles, p.num_kv_heads, p.num_splits);
-  umma_rows2_attention_kernel<<<grid, kXThreads, XLayout::total, stream>>>(p, *mapp);
-  return cudaGetLastError();
+  return p.head_size == 64 ? launch_rows2<64>(p, *mapp, stream) : launch_rows2<128>(p, *mapp, stream);
 }
 
 // Reads and clears this kernel's status word (device must be idle).

@@ -666,10 +666,7 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
 // page copies) and takes bf16 queries.
 bool umma_rows_supports(const KernelParams& p, const char** why) {
   if (!umma_i8_supports(p, why)) return false;
-  if (p.head_size != 128 && p.head_size != 256) {
-    *why = "head_size is not 128 or 256";  // (256 dims: umma_rows256_kernel.cu)
-    return false;
-  }
+  // (this file: 128 dims; 256 dims: umma_rows256_kernel.cu; 64 dims: umma_rows2_kernel.cu)
   if (p.q_dtype != PTH_ATTN_BF16) {
     *why = "q is not bf16";  // the Q image is the query bits as they are, and K / V are widened to bf16
     return false;
@@ -697,6 +694,7 @@ cudaError_t launch_rows(const KernelParams& p, const CUtensorMap& map, dim3 grid
 
 cudaError_t launch_umma_rows_attention(const KernelParams& p_in, cudaStream_t stream) {
   if (p_in.head_size == 256) return launch_umma_rows256_attention(p_in, stream);
+  if (p_in.head_size == 64) return launch_umma_rows2_attention(p_in, stream);  // the only row-major kernel for 64 dims
   // Launches whose requests have 256 rows or more on average (prefill chunks) run two row tiles
   // per CTA, which share every widened K / V tile (umma_rows2_kernel.cu); shorter ones (wide
   // verification, drafter steps) would leave its second row tile empty.

@@ -200,3 +200,25 @@ def test_rows_kernel_at_256_dims_is_deterministic():
         if first is None:
             first = res["out_bytes"].copy()
         assert (res["out_bytes"] == first).all()
+
+
+# ---- the two-row-tile row-major kernel at 64 dims (every tall launch at that head size) ----
+@pytest.mark.parametrize("S", [1, 3])
+@pytest.mark.parametrize("layout,block_size", [("NHD", 16), ("HND", 816), ("NHD", 64)])
+def test_rows_kernel_at_64_dims_prefill_chunk(S, layout, block_size):
+    lens = [700, 1500, 90, 64]
+    qlens = [300, 37, 1, 64]
+    c, q, qsl = _seeded(lens, qlens, 16, 2, 64, seed=1700 + block_size, block_size=block_size, layout=layout)
+    _check(c, q, qsl, 64, f"rows2 D64 {layout} {block_size} S{S}", bq=8, S=S, kernel=capi.KERNEL_UMMA_ROWS)
+
+
+def test_rows_kernel_at_64_dims_window_noncausal_offset_and_mixed():
+    lens = [3000, 700]
+    c, q, qsl = _seeded(lens, [40, 40], 8, 2, 64, seed=1800, pad_page_bytes=64, storage_offset_bytes=8)
+    _check(c, q, qsl, 64, "rows2 D64 window", bq=8, S=2, window=512, kernel=capi.KERNEL_UMMA_ROWS)
+    _check(c, q, qsl, 64, "rows2 D64 non-causal", bq=8, S=1, causal=False, kernel=capi.KERNEL_UMMA_ROWS)
+    lens = [5000, 800, 2000, 300, 1]
+    qlens = [1, 2, 200, 64, 1]
+    c, q, qsl = _seeded(lens, qlens, 16, 2, 64, seed=1900)
+    _check(c, q, qsl, 64, "mixed D64", bq=10, S=1, kernel=capi.KERNEL_AUTO)
+    _check(c, q, qsl, 64, "mixed D64 split", bq=10, S=4, kernel=capi.KERNEL_AUTO)
