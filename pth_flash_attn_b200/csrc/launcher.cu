@@ -173,6 +173,9 @@ int32_t build_attention(const PthAttnArgs* a, const PthB200Options* opt, KernelP
 // launch, then the row-major kernel for the others.
 constexpr int32_t kFamilyPair = 100;
 
+// Rows up to which a request of a pair launch belongs to the integer kernel.
+int32_t pair_class_rows(const KernelParams& p) { return p.group > 16 ? p.group : 16; }
+
 // Kernel family for these parameters (a PTHB200_KERNEL_* value other than AUTO, or kFamilyPair).
 int32_t choose_family(const KernelParams& p, const PthB200Options* opt, int32_t* family) {
   const int32_t want = opt ? opt->kernel : PTHB200_KERNEL_AUTO;
@@ -198,9 +201,15 @@ int32_t choose_family(const KernelParams& p, const PthB200Options* opt, int32_t*
     // token-major integer kernel.  A launch that may hold both (its tile height only bounds
     // the longest request) runs the two kernels one after the other, each serving its own
     // requests: a decode request inside a prefill batch is not padded to a 128-row tile.
+    // A launch whose requests all hold the same number of tokens as far as the host can tell
+    // (tokens = requests x q, q within one row tile, more than 16 rows each: a drafter or wide
+    // verification step) has nothing for the integer kernel: the row-major kernel serves it
+    // alone.  A shorter request hiding behind such numbers is still served, only on the taller tile.
     const char* why_rows = "";
     const bool tall = (int64_t)p.bq * p.group > 16;
-    *family = (tall && umma_rows_supports(p, &why_rows)) ? (i8_ok ? kFamilyPair : PTHB200_KERNEL_UMMA_ROWS)
+    const int64_t q_each = p.num_reqs > 0 && p.num_tokens % p.num_reqs == 0 ? p.num_tokens / p.num_reqs : 0;
+    const bool all_tall = q_each > 0 && q_each <= p.bq && q_each * p.group > pair_class_rows(p);
+    *family = (tall && umma_rows_supports(p, &why_rows)) ? (i8_ok && !all_tall ? kFamilyPair : PTHB200_KERNEL_UMMA_ROWS)
               : i8_ok                                   ? PTHB200_KERNEL_UMMA
               : umma_ok                                 ? PTHB200_KERNEL_UMMA_BF16
                                                         : PTHB200_KERNEL_SCALAR;
@@ -221,7 +230,7 @@ int32_t attention_impl(const PthAttnArgs* a, const PthB200Options* opt, void* st
   if (family == kFamilyPair) {
     KernelParams ps = p;
     ps.row_class = 1;
-    ps.class_rows = p.group > 16 ? p.group : 16;
+    ps.class_rows = pair_class_rows(p);
     err = launch_umma_i8_attention(ps, static_cast<cudaStream_t>(stream));
     if (err == cudaSuccess) {
       ps.row_class = 2;

@@ -26,6 +26,14 @@ What is planned differs, because the kernels differ:
 * ``wm`` keeps its meaning of "16 * wm rows per tile" because it is an argument of the
   op's frozen schema; rows per tile are 16, 32 or 64 and the kernels pad to those.
 * A sliding window caps the pieces at the number of 128-key tiles a row tile can touch.
+* Tall row tiles (more than 16 rows) run on the row-major kernels, which launch one CTA per
+  (row tile, KV head, piece of the bound): there a generous bound does cost time - CTAs of
+  unused pieces that start only to leave, fp32 partials and a combine for requests the
+  device left whole (a drafter step of 32 requests: 183 us at a bound of 10, 146 us at 1).
+  Under a sliding window every request longer than the window holds the same work per row
+  tile, so pieces only serve to fill the SMs: the bound of a tall windowed launch is
+  ``ceil(SMs / unsplit)``.  Without a window the lengths may differ by orders of magnitude
+  and the bound stays generous.
 """
 
 from __future__ import annotations
@@ -50,6 +58,7 @@ DESCRIPTOR_FIELDS = (
 B200_NUM_SMS = 148
 KV_TILE_TOKENS = 128               # keys per KV tile of every kernel family
 ROWS_PER_WM = 16
+SHORT_TILE_ROWS = 16               # row tiles up to this height run on the persistent token-major kernel
 WM_CHOICES = (1, 2, 4)
 MAX_ROWS_PER_CTA = ROWS_PER_WM * max(WM_CHOICES)
 CTAS_PER_SM = {64: 4, 128: 1, 256: 2}   # resident CTAs per SM by head size
@@ -226,6 +235,8 @@ def plan_launch(
         # a row tile sees at most win + longest - 1 keys; at the worst alignment they touch
         touched = _ceil_div(win + longest - 2, KV_TILE_TOKENS) + 1
         pieces = min(pieces, touched)
+        if ROWS_PER_WM * wm > SHORT_TILE_ROWS:
+            pieces = min(pieces, _ceil_div(sms, heads * row_tiles))
     return LaunchPlan(wm=wm, bq=bq, q_tiles_upper=tokens // bq + requests, num_splits=max(1, pieces),
                       num_tokens=tokens, G=group, Hkv=heads, D=head_size, is_prefill=is_prefill)
 

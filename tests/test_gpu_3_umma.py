@@ -225,3 +225,24 @@ def test_other_page_sizes(bs, kernel, layout):
         check_out(res["out"], ref.out, what=f"block size {bs} S{S}")
         check_lse(res["lse"], ref.lse, what=f"block size {bs} S{S}")
         assert res["tail_intact"]
+
+
+def test_launch_count_of_tall_launches():
+    """Tall row tiles: the integer kernel (short requests) and the row-major kernel (the others)
+    one after the other, unless the launch's numbers leave no room for a short request.  (The
+    count is computed without touching the pointers; it needs the driver's tensor-map encoder.)"""
+    from tests.test_capi_cpu import _valid_args
+
+    lib = capi.load_library()
+    a, keep = _valid_args()
+    cells = a.k_cache.data            # one cell per slot and head: K | k_scale | V | v_scale
+    for s, off in ((a.k_cache, 0), (a.k_scale, 128), (a.v_cache, 132), (a.v_scale, 260)):
+        s.data = cells + off
+    a.bq, a.num_reqs, a.num_tokens = 16, 2, 31
+    assert lib.launch_count(a) == (2, 0), lib.last_error()
+    a.num_tokens = 32          # 2 requests x 16 tokens x 4 heads per KV head: 64 rows each
+    assert lib.launch_count(a) == (1, 0), lib.last_error()
+    a.num_tokens = 8           # 4 tokens each: 16 rows, the integer kernel's own
+    assert lib.launch_count(a) == (2, 0), lib.last_error()
+    a.bq, a.num_tokens = 4, 8  # short tiles
+    assert lib.launch_count(a) == (1, 0), lib.last_error()

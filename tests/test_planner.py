@@ -78,6 +78,11 @@ def test_baseline_shapes():
     d = _plan(num_tokens=512, num_reqs=32, max_query_len=16, window=4096)
     assert d.wm == 4 and d.bq == 16
     assert d.num_splits <= -(-(4096 + 16 - 2) // planner.KV_TILE_TOKENS) + 1
+    # tall windowed tiles: pieces only to fill the SMs (256 unsplit items already do)
+    assert d.num_splits == 1
+    assert _plan(num_tokens=64, num_reqs=4, max_query_len=16, window=4096).num_splits == -(-148 // 32) == 5
+    # short windowed tiles keep the generous bound of the persistent kernel
+    assert _plan(num_tokens=128, num_reqs=32, max_query_len=4, window=4096).num_splits == 10
     tight = _plan(num_tokens=1, num_reqs=1, window=200)
     assert tight.num_splits == -(-(200 + 1 - 2) // planner.KV_TILE_TOKENS) + 1 == 3
     # prefill
