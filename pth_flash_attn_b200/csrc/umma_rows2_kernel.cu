@@ -230,13 +230,16 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
   const int key_begin = tile_begin * 128;
   const int key_end = min(tile_end * 128, range_end);
   const int n_tiles = (key_end - key_begin + kXKeys - 1) / kXKeys;
+  // Row tiles with live rows: a CTA of at most 128 rows (the end of a chunk, a short request
+  // inside a prefill launch) issues no MMA for its second row tile, whose softmax warps idle.
+  const int n_rt = rows > 128 ? 2 : 1;
   if (tid == 0) {
     for (int s = 0; s < kXNS; ++s) {
       tc::mbar_init(&bars[B::vfull + s], kXProducers / 2);
-      tc::mbar_init(&bars[B::vempty + s], 2);  // one commit per row tile's PV
+      tc::mbar_init(&bars[B::vempty + s], n_rt);  // one commit per row tile's PV
     }
     for (int s = 0; s < kXNK; ++s) {
-      tc::mbar_init(&bars[B::kempty + s], 2);  // one commit per row tile's QK
+      tc::mbar_init(&bars[B::kempty + s], n_rt);  // one commit per row tile's QK
       tc::mbar_init(&bars[B::kfull + s], kXProducers / 2);
     }
     for (int g = 0; g < 4; ++g) {
@@ -408,7 +411,9 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
     // QK(i + 2) overwrites the S buffer its P(i) was written over: it waits for its PV(i) to have
     // finished reading it, a whole tile of softmax after it is issued.
     named_barrier(5, kXSoftmax + 32);  // wait for the Q images
-    {
+    // (one instance per number of live row tiles: the loops over them unroll as constants)
+    auto issue_all = [&](auto live_row_tiles) {
+      constexpr int kRowTiles = decltype(live_row_tiles)::value;
       const RowsDesc qd = rows_desc(tc::smem_u32(smem + L::qimg), kXQStride, 128);
       const RowsDesc kd = rows_desc(kimg_s, kXChunkStride, 128);
       const RowsDesc vd = rows_desc(vst_s, 128, kXChunkStride);
@@ -417,7 +422,7 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
         const int b = q & 1;
         ok &= wait_or_abort(&bars[B::kfull + q % kXNK], (q / kXNK) & 1, abort_flag);
 #pragma unroll
-        for (int rt = 0; rt < 2; ++rt) {
+        for (int rt = 0; rt < kRowTiles; ++rt) {
           if (after_pv) ok &= wait_or_abort(&bars[B::pv_done + 2 * rt + b], ((q - 2) >> 1) & 1, abort_flag);
           if (ok && elect_one()) {
             tc::fence_after_sync();
@@ -438,7 +443,7 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
         const int b = i & 1;
         ok &= wait_or_abort(&bars[B::vfull + i % kXNS], (i / kXNS) & 1, abort_flag);
 #pragma unroll
-        for (int rt = 0; rt < 2; ++rt) {
+        for (int rt = 0; rt < kRowTiles; ++rt) {
           ok &= wait_or_abort(&bars[B::p_ready + 2 * rt + b], (i >> 1) & 1, abort_flag);
           if (ok && elect_one()) {
             tc::fence_after_sync();
@@ -452,7 +457,8 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
         }
         if (i + 2 < n_tiles) issue_qk_pair(i + 2, true);
       }
-    }
+    };
+    if (n_rt == 2) issue_all(std::integral_constant<int, 2>{}); else issue_all(std::integral_constant<int, 1>{});
   } else if (warp < 8) {
     // =========================== softmax ======================================
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kXSoftmaxRegs));
@@ -485,6 +491,22 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
     visible_range(p, t, t.first_idx, &tmp, &mask_hi);
     float m_ref = -INFINITY;  // reference maximum of the row's exponentials (log2 units)
     float l = 0.f;            // sum of exp2(score - m_ref)
+    // A warp whose 32 rows are all padding (the last row tile of a chunk, a short request inside
+    // a prefill launch) leaves the issue slots to the others; its rows end as rows without keys
+    // (m = -inf, l = 0), which the epilogue never writes.
+    // (Their loop is a separate one: the live warps' loop carries no trace of the case.)  A row
+    // tile without any live row is never computed: its warps wait for nothing.
+    if ((row & ~31) >= rows) {
+      if (rt < n_rt) {
+#pragma unroll 1
+        for (int i = 0; i < n_tiles; ++i) {
+          // the arrival keeps the barrier's count and, behind the wait, its phase: S(rt, i + 2) is
+          // not ready before P(rt, i) has been used
+          ok &= wait_or_abort(&bars[B::s_ready + 2 * rt + (i & 1)], (i >> 1) & 1, abort_flag);
+          mbar_arrive(&bars[B::p_ready + 2 * rt + (i & 1)]);
+        }
+      }
+    } else {
 #pragma unroll 1
     for (int i = 0; i < n_tiles; ++i) {
       const int b = i & 1;
@@ -573,9 +595,10 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
       tc::fence_before_sync();
       mbar_arrive(&bars[B::p_ready + 2 * rt + b]);  // P(rt, i) is complete
     }
+    }
 
     // ---- epilogue: the row's output (the commit after the last PV covers every MMA issued before it) ----
-    ok &= wait_or_abort(&bars[B::pv_done + 2 * rt + ((n_tiles - 1) & 1)], ((n_tiles - 1) >> 1) & 1, abort_flag);
+    if (rt < n_rt) ok &= wait_or_abort(&bars[B::pv_done + 2 * rt + ((n_tiles - 1) & 1)], ((n_tiles - 1) >> 1) & 1, abort_flag);
     tc::fence_after_sync();
     const float inv = l > 0.f ? 1.0f / l : 0.f;
     int token, head;

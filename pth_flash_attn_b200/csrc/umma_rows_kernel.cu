@@ -475,6 +475,19 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
     visible_range(p, t, t.first_idx, &tmp, &mask_hi);
     float m_ref = -INFINITY;  // reference maximum of the row's exponentials (log2 units)
     float l = 0.f;            // sum of exp2(score - m_ref)
+    // A warp whose 32 rows are all padding (a drafter step fills 64 of the 128 rows, a wide
+    // verification step 32) leaves the issue slots to the others; its rows end as rows without
+    // keys (m = -inf, l = 0), which the epilogue never writes.
+    // (Their loop is a separate one: the live warps' loop carries no trace of the case.)
+    if ((row & ~31) >= rows) {
+#pragma unroll 1
+      for (int i = 0; i < n_tiles; ++i) {
+        // the arrival keeps the barrier's count and, behind the wait, its phase: S(i + 2) is not
+        // ready before P(i) has been used
+        ok &= wait_or_abort(&bars[B::s_ready + (i & 1)], (i >> 1) & 1, abort_flag);
+        mbar_arrive(&bars[B::p_ready + (i & 1)]);
+      }
+    } else {
 #pragma unroll 1
     for (int i = 0; i < n_tiles; ++i) {
       const float* ksp = reinterpret_cast<const float*>(smem + L::ksc) + (i % kRKsRing) * kTileKeys + g * 64;
@@ -567,6 +580,7 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
       tc::tmem_st_wait();
       tc::fence_before_sync();
       mbar_arrive(&bars[B::p_ready + (i & 1)]);  // this group's half of P(i) is complete
+    }
     }
 
     // ---- epilogue: merge the two groups' (m, l, O) and write the rows ----
