@@ -22,7 +22,7 @@ What is planned differs, because the kernels differ:
 
   ``s_alone`` = ``ceil(2 * SMs / Hkv)``: a single request is cut so that every SM gets two
   pieces of it.  The kernel never uses more pieces than keep a piece above a few KV tiles,
-  so a generous bound costs workspace, not time.
+  so for this kernel a generous bound costs workspace, not time.
 * ``wm`` keeps its meaning of "16 * wm rows per tile" because it is an argument of the
   op's frozen schema; rows per tile are 16, 32 or 64 and the kernels pad to those.
 * A sliding window caps the pieces at the number of 128-key tiles a row tile can touch.
