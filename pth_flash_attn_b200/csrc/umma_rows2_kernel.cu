@@ -506,7 +506,7 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
           mbar_arrive(&bars[B::p_ready + 2 * rt + (i & 1)]);
         }
       }
-    } else {
+    } else {  // warps with live rows (the loop keeps its indentation)
 #pragma unroll 1
     for (int i = 0; i < n_tiles; ++i) {
       const int b = i & 1;
@@ -595,7 +595,7 @@ umma_rows2_attention_kernel(const __grid_constant__ KernelParams p, const __grid
       tc::fence_before_sync();
       mbar_arrive(&bars[B::p_ready + 2 * rt + b]);  // P(rt, i) is complete
     }
-    }
+    }  // warps with live rows
 
     // ---- epilogue: the row's output (the commit after the last PV covers every MMA issued before it) ----
     if (rt < n_rt) ok &= wait_or_abort(&bars[B::pv_done + 2 * rt + ((n_tiles - 1) & 1)], ((n_tiles - 1) >> 1) & 1, abort_flag);

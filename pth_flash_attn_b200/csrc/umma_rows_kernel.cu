@@ -487,7 +487,7 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
         ok &= wait_or_abort(&bars[B::s_ready + (i & 1)], (i >> 1) & 1, abort_flag);
         mbar_arrive(&bars[B::p_ready + (i & 1)]);
       }
-    } else {
+    } else {  // warps with live rows (the loop keeps its indentation)
 #pragma unroll 1
     for (int i = 0; i < n_tiles; ++i) {
       const float* ksp = reinterpret_cast<const float*>(smem + L::ksc) + (i % kRKsRing) * kTileKeys + g * 64;
@@ -581,7 +581,7 @@ umma_rows_attention_kernel(const __grid_constant__ KernelParams p, const __grid_
       tc::fence_before_sync();
       mbar_arrive(&bars[B::p_ready + (i & 1)]);  // this group's half of P(i) is complete
     }
-    }
+    }  // warps with live rows
 
     // ---- epilogue: merge the two groups' (m, l, O) and write the rows ----
     // (the commit after the last PV covers every MMA issued before it)
