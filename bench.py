@@ -641,10 +641,10 @@ def roofline_of(wl, world, attn_ms, pass_ms, hbm_peak, tc_peak, tc_sustained, pe
         bound_ms = max(t_bytes, t_flops)
         roof = {"bound": "hbm" if t_bytes >= t_flops else "tensor", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s",
                 "frac": bound_ms / attn_ms, "tflops": tfs, "bound_ms": bound_ms, "traffic": None,
-                "kernel": "umma_i8_attention_kernel + umma_rows_attention_kernel"}
+                "kernel": "umma_i8_attention_kernel + umma_rows2_attention_kernel"}
     else:
-        # tall row tiles whose requests are all tall run on the row-major kernel (the integer
-        # kernel of the pair finds nothing to do)
+        # tall row tiles whose requests are all tall run on the one-tile row-major kernel (alone
+        # when the launch is uniform, else behind an integer kernel that finds nothing to do)
         rows_kernel = all(d.bq * d.G > 16 and min(d.launch_spec["q_lens"]) * d.G > 16 for d in wl.dls)
         roof = {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
                 "traffic": (DRAM_BYTES_PER_ALGORITHMIC_BYTE * wl.bytes_local
